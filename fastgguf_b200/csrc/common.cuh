@@ -1,0 +1,71 @@
+// Shared helpers of every kernel file: dtype codes, f32 <-> storage conversion, block
+// reductions with a fixed order, and the launch-error convention (each extern "C" launcher
+// returns the cudaError_t of its launch as an int; 0 is success).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+// dtype codes shared with the Python side (fastgguf_b200/ops/lib.py)
+#define FG_F32 0
+#define FG_BF16 1
+
+// error codes above the CUDA range, returned by launchers for refused arguments
+#define FG_ERR_BAD_DTYPE 10001
+#define FG_ERR_BAD_SIZE 10002
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// store a float into a buffer whose dtype is only known at run time
+__device__ __forceinline__ void store_as(void *base, int dtype, size_t idx, float v) {
+    if (dtype == FG_F32) ((float *)base)[idx] = v;
+    else ((bf16 *)base)[idx] = __float2bfloat16_rn(v);
+}
+__device__ __forceinline__ float load_as(const void *base, int dtype, size_t idx) {
+    return dtype == FG_F32 ? ((const float *)base)[idx] : __bfloat162float(((const bf16 *)base)[idx]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum / max with a fixed order: xor-shuffle tree inside each warp, then the warp
+// totals are added in warp order by every thread.  `scratch` holds at least 32 floats.  The
+// result is the same in every thread.  Contains two __syncthreads().
+__device__ __forceinline__ float block_sum(float v, float *scratch) {
+    v = warp_sum(v);
+    int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[w] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int i = 0; i < nw; i++) t += scratch[i];
+    return t;
+}
+__device__ __forceinline__ float block_max(float v, float *scratch) {
+    v = warp_max(v);
+    int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[w] = v;
+    __syncthreads();
+    float t = -INFINITY;
+    for (int i = 0; i < nw; i++) t = fmaxf(t, scratch[i]);
+    return t;
+}
+
+#define FG_LAUNCH_CHECK() ((int)cudaGetLastError())

@@ -1,0 +1,151 @@
+// Row-wise kernels of the decoder: embedding gather, RMSNorm, rotary encoding with cache
+// append, SiLU-multiply.  Each takes both storage dtypes (f32, bf16) and computes in f32.
+//
+// Reference formulas (file fastgguf.c of the reference engine):
+//   embedding  read_embedding            :4576-4581   x = Emb[token, :]
+//   RMSNorm    rmsnorm_w                 :3100-3105   y = x * (1/sqrt(mean(x^2) + eps)) * w
+//   RoPE       apply_rope                :3123-3145   (a, b) <- (a cos - b sin, a sin + b cos)
+//   cache      forward                   :4720, 4738-4739   K stored after RoPE, V raw
+//   SiLU-mul   silu_f, forward           :3118, 4876  t = g / (1 + exp(-g)) * u
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding gather
+template <typename TW>
+__global__ void embed_gather_kernel(const TW *__restrict__ table, const int *__restrict__ tokens,
+                                    float *__restrict__ x, int E) {
+    int m = blockIdx.x;
+    const TW *row = table + (size_t)tokens[m] * E;
+    float *out = x + (size_t)m * E;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) out[i] = to_f32<TW>(row[i]);
+}
+
+extern "C" int fg_embed_gather(const void *table, int table_dtype, const int *tokens, float *x,
+                               int M, int E, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    int threads = E >= 1024 ? 256 : 128;
+    if (table_dtype == FG_F32)
+        embed_gather_kernel<float><<<M, threads, 0, stream>>>((const float *)table, tokens, x, E);
+    else if (table_dtype == FG_BF16)
+        embed_gather_kernel<bf16><<<M, threads, 0, stream>>>((const bf16 *)table, tokens, x, E);
+    else return FG_ERR_BAD_DTYPE;
+    return FG_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// One block per output row.  `rows` (optional) names the input row of each output row, so the
+// final norm runs only on the rows whose logits are wanted.  Statistics in f32 with a fixed
+// reduction order: a row's result does not depend on what else is in the batch.
+template <typename TO>
+__global__ void rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ w,
+                               const int *__restrict__ rows, TO *__restrict__ out, int E, float eps) {
+    __shared__ float scratch[32];
+    int r = blockIdx.x;
+    const float *xi = x + (size_t)(rows ? rows[r] : r) * E;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) { float v = xi[i]; ss += v * v; }
+    ss = block_sum(ss, scratch);
+    float inv = 1.0f / sqrtf(ss / (float)E + eps);
+    TO *o = out + (size_t)r * E;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) o[i] = from_f32<TO>(xi[i] * inv * w[i]);
+}
+
+extern "C" int fg_rmsnorm(const float *x, const float *w, const int *rows, void *out, int out_dtype,
+                          int R, int E, float eps, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : 128);
+    if (out_dtype == FG_F32)
+        rmsnorm_kernel<float><<<R, threads, 0, stream>>>(x, w, rows, (float *)out, E, eps);
+    else if (out_dtype == FG_BF16)
+        rmsnorm_kernel<bf16><<<R, threads, 0, stream>>>(x, w, rows, (bf16 *)out, E, eps);
+    else return FG_ERR_BAD_DTYPE;
+    return FG_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ RoPE + cache append
+// qkv: [M, ld] rows of (q heads | k heads | v heads).  q is rotated in place; k is rotated and
+// written, v copied, into the sequence's page at the row's position.  Pairs are (j, j + hd/2).
+// cos/sin: [max_pos, hd/2] f32, built on the host in double.  Page pools: [n_pages, KV, P, hd].
+template <typename T>
+__global__ void rope_append_kernel(T *__restrict__ qkv, int ld, const int *__restrict__ positions,
+                                   const int *__restrict__ row_seq, const int *__restrict__ block_table,
+                                   int table_width, T *__restrict__ k_pool, T *__restrict__ v_pool,
+                                   const float *__restrict__ cos_t, const float *__restrict__ sin_t,
+                                   int H, int KV, int hd, int page_size, int write_kv) {
+    int m = blockIdx.x;
+    int pos = positions[m];
+    int half = hd >> 1;
+    T *row = qkv + (size_t)m * ld;
+    const float *cs = cos_t + (size_t)pos * half, *sn = sin_t + (size_t)pos * half;
+    // q heads
+    for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
+        int h = i / half, j = i - h * half;
+        T *p = row + h * hd;
+        float a = to_f32<T>(p[j]), b = to_f32<T>(p[j + half]);
+        float c = cs[j], s = sn[j];
+        p[j] = from_f32<T>(a * c - b * s);
+        p[j + half] = from_f32<T>(a * s + b * c);
+    }
+    if (!write_kv) return;
+    int page = block_table[(size_t)row_seq[m] * table_width + pos / page_size];
+    int off = pos % page_size;
+    const T *krow = row + H * hd, *vrow = krow + KV * hd;
+    for (int i = threadIdx.x; i < KV * half; i += blockDim.x) {
+        int h = i / half, j = i - h * half;
+        const T *p = krow + h * hd;
+        float a = to_f32<T>(p[j]), b = to_f32<T>(p[j + half]);
+        float c = cs[j], s = sn[j];
+        T *dst = k_pool + (((size_t)page * KV + h) * page_size + off) * hd;
+        dst[j] = from_f32<T>(a * c - b * s);
+        dst[j + half] = from_f32<T>(a * s + b * c);
+    }
+    for (int i = threadIdx.x; i < KV * hd; i += blockDim.x) {
+        int h = i / hd, d = i - h * hd;
+        v_pool[(((size_t)page * KV + h) * page_size + off) * hd + d] = vrow[i];
+    }
+}
+
+extern "C" int fg_rope_append(void *qkv, int dtype, int ld, const int *positions, const int *row_seq,
+                              const int *block_table, int table_width, void *k_pool, void *v_pool,
+                              const float *cos_t, const float *sin_t, int M, int H, int KV, int hd,
+                              int page_size, int write_kv, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (hd % 2) return FG_ERR_BAD_SIZE;
+    int work = H * hd / 2;
+    int threads = work >= 1024 ? 256 : (work >= 128 ? 128 : 64);
+    if (dtype == FG_F32)
+        rope_append_kernel<float><<<M, threads, 0, stream>>>((float *)qkv, ld, positions, row_seq, block_table,
+            table_width, (float *)k_pool, (float *)v_pool, cos_t, sin_t, H, KV, hd, page_size, write_kv);
+    else if (dtype == FG_BF16)
+        rope_append_kernel<bf16><<<M, threads, 0, stream>>>((bf16 *)qkv, ld, positions, row_seq, block_table,
+            table_width, (bf16 *)k_pool, (bf16 *)v_pool, cos_t, sin_t, H, KV, hd, page_size, write_kv);
+    else return FG_ERR_BAD_DTYPE;
+    return FG_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ SiLU(g) * u
+// gu: [M, 2F] rows of (gate | up); out: [M, F].
+template <typename T>
+__global__ void silu_mul_kernel(const T *__restrict__ gu, T *__restrict__ out, size_t total, int F) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        size_t m = i / F;
+        int f = (int)(i - m * F);
+        float g = to_f32<T>(gu[m * 2 * F + f]), u = to_f32<T>(gu[m * 2 * F + F + f]);
+        out[i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+extern "C" int fg_silu_mul(const void *gu, void *out, int dtype, int M, int F, cudaStream_t stream) {
+    size_t total = (size_t)M * F;
+    if (total == 0) return 0;
+    int threads = 256;
+    size_t want = (total + threads - 1) / threads;
+    int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
+    if (dtype == FG_F32)
+        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float *)gu, (float *)out, total, F);
+    else if (dtype == FG_BF16)
+        silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16 *)gu, (bf16 *)out, total, F);
+    else return FG_ERR_BAD_DTYPE;
+    return FG_LAUNCH_CHECK();
+}

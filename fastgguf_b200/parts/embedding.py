@@ -1,0 +1,50 @@
+"""TokenEmbedding(vocab_size, hidden_size) and LMHead(vocab_size, hidden_size, tied).
+
+Reference: ``read_embedding`` copies row ``token`` of ``token_embd`` into the residual stream
+with scale 1 for Llama (fastgguf.c:4576-4581, :4652, :4219); the head is ``output.weight`` or,
+when that tensor is absent, the embedding table again (:4269-4270); logits are float
+(:4900).  Here tied-ness comes from the configuration, and a tied head shares the embedding's
+storage.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .. import ops
+from .base import Part, Runtime, TensorSpec
+from .linear import Linear
+
+
+class TokenEmbedding(Part):
+    def __init__(self, runtime: Runtime, vocab_size: int, hidden_size: int):
+        super().__init__(runtime)
+        self.vocab_size, self.hidden_size = vocab_size, hidden_size
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {"weight": TensorSpec((self.vocab_size, self.hidden_size))}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors["weight"].contiguous()
+
+    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+        return ops.embed_gather(self.weight, tokens)
+
+
+class LMHead(Part):
+    def __init__(self, runtime: Runtime, vocab_size: int, hidden_size: int):
+        super().__init__(runtime)
+        self.vocab_size, self.hidden_size = vocab_size, hidden_size
+        self.linear: Optional[Linear] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {"weight": TensorSpec((self.vocab_size, self.hidden_size))}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.linear = Linear(tensors["weight"])
+
+    def forward(self, xn: torch.Tensor) -> torch.Tensor:
+        """Float32 logits [rows, vocab] of normalized rows."""
+        return self.linear.forward(xn, out_dtype=torch.float32)
