@@ -29,6 +29,7 @@ CSRC_DIR = os.path.dirname(os.path.abspath(__file__))
 #: module name -> source files.  Headers every module depends on are listed in HEADERS.
 MODULES = {
     "core": ["elementwise.cu", "gemm_generic.cu", "attention_generic.cu", "sampling.cu"],
+    "tc": ["gemm_tc.cu"],
 }
 HEADERS = ["common.cuh"]
 

@@ -1,8 +1,118 @@
-"""bfloat16 tensor-core contractions (tcgen05 / TMA).  ``plan_for_weight`` returns an object
-whose ``run`` either performs the contraction or returns None when the sizes are outside what
-the fast kernels take, in which case the caller uses the plain kernel."""
+"""bfloat16 tensor-core contractions (tcgen05 / TMA).
+
+``plan_for_weight`` returns an object whose ``run`` either performs the contraction or returns
+None when the sizes are outside what the fast kernel takes (a reduction length that is no
+multiple of 8, unaligned rows), in which case the caller uses the plain kernel.
+
+The split-K path of the kernel sums partial tiles through a float32 workspace and per-tile
+arrival counters; one workspace per device is allocated when the first plan is made (before any
+stream capture) and shared by every contraction on that device, which run one after another on
+the stream.
+"""
 from __future__ import annotations
 
+from ctypes import c_int, c_longlong, c_void_p
+from typing import Optional
 
-def plan_for_weight(weight):
-    return None
+import torch
+
+from .lib import KernelError, check, lib, ptr, register_signatures, stream
+
+EPI_BF16, EPI_F32, EPI_ADD_F32, EPI_SILU_MUL = 0, 1, 2, 3
+_BAD_SIZE = 10002
+
+register_signatures("tc", {
+    "fg_gemm_tc": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                   c_void_p, c_void_p, c_int, c_void_p],
+    "fg_gemm_tc_error": [],
+    "fg_gemm_tc_counter_count": [],
+})
+
+_workspaces: dict = {}
+
+
+def _workspace(device: torch.device):
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(key)
+    if ws is None:
+        l = lib("tc")
+        l.fg_gemm_tc_workspace_floats.restype = c_longlong
+        l.fg_gemm_tc_workspace_floats.argtypes = []
+        n = int(l.fg_gemm_tc_workspace_floats())
+        ws = (torch.empty(n, dtype=torch.float32, device=device),
+              torch.zeros(int(l.fg_gemm_tc_counter_count()), dtype=torch.int32, device=device))
+        _workspaces[key] = ws
+    return ws
+
+
+def pipeline_error() -> int:
+    """0, or the code of the first bounded wait that ran out since the last call (clears it)."""
+    return int(lib("tc").fg_gemm_tc_error())
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+            out_dtype: Optional[torch.dtype] = None, accumulate: bool = False, silu_rows: Optional[int] = None,
+            force_splits: int = 0) -> Optional[torch.Tensor]:
+    """out[m, n] (+)= sum_k a[m, k] w[n, k] on the tensor cores; None if the sizes are refused.
+
+    ``silu_rows=F``: ``w`` is [2F, K] (gate rows then up rows) and the result is
+    ``silu(a gate^T) * (a up^T)`` as bfloat16 [M, F].
+    """
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc takes bfloat16 operands")
+    M, K = a.shape
+    rows, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"gemm_tc: a is [{M}, {K}] but w is [{rows}, {K2}]")
+    if a.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError("gemm_tc: the reduction dimension must be contiguous in both operands")
+    if silu_rows is not None:
+        N, epi, dt, up = silu_rows, EPI_SILU_MUL, torch.bfloat16, silu_rows
+        if rows != 2 * silu_rows or accumulate:
+            raise KernelError("gemm_tc: the silu epilogue needs w = [2F, K] and no accumulation")
+    else:
+        N, up = rows, 0
+        if accumulate:
+            epi, dt = EPI_ADD_F32, torch.float32
+        else:
+            dt = out_dtype or (out.dtype if out is not None else torch.bfloat16)
+            if dt == torch.bfloat16:
+                epi = EPI_BF16
+            elif dt == torch.float32:
+                epi = EPI_F32
+            else:
+                raise KernelError(f"gemm_tc: cannot write {dt}")
+    if out is None:
+        if accumulate:
+            raise KernelError("gemm_tc: accumulate needs the tensor to accumulate into")
+        out = torch.empty((M, N), dtype=dt, device=a.device)
+    if out.shape != (M, N) or out.stride(1) != 1 or out.dtype != dt:
+        raise KernelError(f"gemm_tc: out must be [{M}, {N}] {dt} with contiguous rows")
+    ws, counters = _workspace(a.device)
+    code = lib("tc").fg_gemm_tc(ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out.stride(0), epi,
+                                M, N, K, rows, up, ptr(ws), ptr(counters), int(force_splits), stream())
+    if code == _BAD_SIZE:
+        return None
+    check(code, "gemm_tc")
+    return out
+
+
+class _Plan:
+    def __init__(self, weight: torch.Tensor):
+        self.weight = weight
+        _workspace(weight.device)
+
+    def run(self, a, out=None, out_dtype=None, accumulate=False):
+        return gemm_tc(a, self.weight, out=out, out_dtype=out_dtype, accumulate=accumulate)
+
+    def run_silu(self, a, d_ff: int):
+        return gemm_tc(a, self.weight, silu_rows=d_ff)
+
+
+def plan_for_weight(weight: torch.Tensor) -> Optional[_Plan]:
+    """A plan for a bfloat16 weight on a CUDA device whose rows TMA can address; else None."""
+    if weight.dtype != torch.bfloat16 or not weight.is_cuda:
+        return None
+    if weight.shape[1] % 8 or weight.stride(0) % 8 or weight.data_ptr() % 16 or weight.stride(1) != 1:
+        return None
+    return _Plan(weight)

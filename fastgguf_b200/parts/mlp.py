@@ -36,8 +36,11 @@ class SwiGLU(FeedForward):
         self.down = Linear(tensors["down_proj.weight"].contiguous())
 
     def forward(self, xn: torch.Tensor, batch, residual: torch.Tensor) -> None:
-        gu = self.gate_up.forward(xn, out_dtype=self.runtime.dtype)
-        t = ops.silu_mul(gu)
+        t = None
+        if self.gate_up._fast is not None and xn.dtype == torch.bfloat16:
+            t = self.gate_up._fast.run_silu(xn, self.d_ff)      # gate, up and SiLU-mul in one kernel
+        if t is None:
+            t = ops.silu_mul(self.gate_up.forward(xn, out_dtype=self.runtime.dtype))
         self.down.forward(t, out=residual, accumulate=True)
 
 

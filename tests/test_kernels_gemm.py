@@ -1,0 +1,95 @@
+"""The contraction kernels alone, against float64 matrix products of the same operands, at sizes
+other than any model's (odd row counts, feature counts that are no multiple of the tile, a
+reduction length that is no multiple of the K-block)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _operands(M, N, K, dtype, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    a = (torch.randn(M, K, generator=g) * 0.5).to(dtype).cuda()
+    w = (torch.randn(N, K, generator=g) * 0.5).to(dtype).cuda()
+    return a, w
+
+
+def _check(got, a, w, want, out_is_bf16):
+    bound = (a.double().abs() @ w.double().abs().T).max().item()
+    err = (got.double() - want).abs().max().item()
+    tol = 2e-6 * bound + (want.abs().max().item() * 2 ** -8 if out_is_bf16 else 0.0)
+    assert err <= tol, (err, tol)
+
+
+@pytest.mark.parametrize("adt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                     (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 200, 72), (70, 130, 257), (129, 65, 64)])
+def test_gemm_generic(M, N, K, adt, wdt):
+    from fastgguf_b200 import ops
+    a, _ = _operands(M, N, K, adt, 1)
+    _, w = _operands(M, N, K, wdt, 1)
+    want = a.double() @ w.double().T
+    got = ops.gemm_generic(a, w, out_dtype=torch.float32)
+    _check(got, a, w, want, False)
+    res = torch.randn(M, N, device="cuda")
+    acc = res.clone()
+    ops.gemm_generic(a, w, out=acc, accumulate=True)
+    _check(acc, a, w, want + res.double(), False)
+    if adt == torch.bfloat16:
+        _check(ops.gemm_generic(a, w), a, w, want, True)
+
+
+@pytest.mark.parametrize("M", [1, 5, 16, 33, 64, 100, 300, 700])
+@pytest.mark.parametrize("N,K", [(200, 72), (384, 2048), (1000, 520)])
+def test_gemm_tc_epilogues(M, N, K):
+    from fastgguf_b200.ops import fast_gemm
+    a, w = _operands(M, N, K, torch.bfloat16, 2)
+    want = a.double() @ w.double().T
+    got = fast_gemm.gemm_tc(a, w, out_dtype=torch.float32)
+    assert got is not None
+    _check(got, a, w, want, False)
+    _check(fast_gemm.gemm_tc(a, w), a, w, want, True)
+    res = torch.randn(M, N, device="cuda")
+    acc = res.clone()
+    fast_gemm.gemm_tc(a, w, out=acc, accumulate=True)
+    _check(acc, a, w, want + res.double(), False)
+    assert fast_gemm.pipeline_error() == 0
+
+
+@pytest.mark.parametrize("splits", [2, 3, 8])
+@pytest.mark.parametrize("M,N,K", [(1, 256, 2048), (8, 200, 1096), (64, 384, 8192)])
+def test_gemm_tc_split_k(M, N, K, splits):
+    from fastgguf_b200.ops import fast_gemm
+    a, w = _operands(M, N, K, torch.bfloat16, 3)
+    want = a.double() @ w.double().T
+    for _ in range(2):                      # twice: the arrival counters must be back at zero
+        got = fast_gemm.gemm_tc(a, w, out_dtype=torch.float32, force_splits=splits)
+        _check(got, a, w, want, False)
+    res = torch.randn(M, N, device="cuda")
+    acc = res.clone()
+    fast_gemm.gemm_tc(a, w, out=acc, accumulate=True, force_splits=splits)
+    _check(acc, a, w, want + res.double(), False)
+    assert fast_gemm.pipeline_error() == 0
+
+
+@pytest.mark.parametrize("M", [1, 9, 64, 130, 513])
+@pytest.mark.parametrize("F,K", [(192, 64), (200, 72), (640, 2048)])
+def test_gemm_tc_silu(M, F, K):
+    from fastgguf_b200.ops import fast_gemm
+    a, w = _operands(M, 2 * F, K, torch.bfloat16, 4)
+    g = a.double() @ w[:F].double().T
+    u = a.double() @ w[F:].double().T
+    want = g / (1 + torch.exp(-g)) * u
+    got = fast_gemm.gemm_tc(a, w, silu_rows=F)
+    assert got is not None and got.dtype == torch.bfloat16
+    bound = (a.double().abs() @ w.double().abs().T).max().item()
+    err = (got.double() - want).abs().max().item()
+    assert err <= want.abs().max().item() * 2 ** -8 + 1e-5 * bound * bound
+    assert fast_gemm.pipeline_error() == 0
+
+
+def test_gemm_tc_refuses_unaligned():
+    from fastgguf_b200.ops import fast_gemm
+    a, w = _operands(4, 32, 36, torch.bfloat16, 5)      # K % 8 != 0: TMA cannot describe the rows
+    assert fast_gemm.gemm_tc(a, w) is None
+    assert fast_gemm.plan_for_weight(w) is None
