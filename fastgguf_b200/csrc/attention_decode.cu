@@ -1,0 +1,188 @@
+// Decode attention over the paged bf16 cache on the tensor cores: one new token per sequence.
+//
+// Reference role: attn_rows for one token (fastgguf.c:4769-4786, :3273-3326): the query heads
+// of one KV head share every K/V load (the reference's "up to 4 query rows sharing one KV head",
+// :3268-3272).  Formulas as in attention_generic.cu.
+//
+// Grid (split, kv head x head chunk, sequence).  The pages of a sequence are divided evenly
+// among `n_splits` CTAs, so one long sequence fills the GPU as well as many short ones; inside a
+// CTA four warps take pages round-robin, each with K and V buffers of its own (one K and one V
+// load always in flight), and merge their running (max, sum, O) through shared memory.  With
+// n_splits > 1 each CTA writes an unnormalised partial (O, max, sum) to scratch memory and a
+// second kernel merges the splits in order.
+#include "attention_mma.cuh"
+
+#define DEC_WARPS 4
+
+template <int HD>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ positions,
+                   const int *__restrict__ block_table, int table_width,
+                   const bf16 *__restrict__ k_pool, const bf16 *__restrict__ v_pool,
+                   int KV, int G, float scale, int window, int n_splits,
+                   float *__restrict__ part_o, float *__restrict__ part_ml,
+                   bf16 *__restrict__ out, int ldo) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int TILE_BYTES = PAGE * HD * 2;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int chunks = (G + 15) / 16;
+    const int kvh = blockIdx.y / chunks, g0 = (blockIdx.y % chunks) * 16;
+    const int rows = min(16, G - g0);
+    const int b = blockIdx.z, split = blockIdx.x;
+    const int pos = positions[b];
+    const int lo_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int first_page = lo_key / PAGE, n_pages = pos / PAGE - first_page + 1;
+    const int per = (n_pages + n_splits - 1) / n_splits;
+    const int p_begin = first_page + split * per, p_end = min(first_page + n_pages, p_begin + per);
+    const int *bt = block_table + (size_t)b * table_width;
+
+    uint8_t *kbuf = smem + (size_t)warp * 2 * TILE_BYTES, *vbuf = kbuf + TILE_BYTES;
+    const uint32_t ks = smem_addr(kbuf), vs = smem_addr(vbuf);
+
+    // Q fragments of rows g0 .. g0+15 of this KV head's group (rows past the group are zero)
+    uint32_t qf[HD / 16][4];
+    {
+        const int r0 = lane >> 2, c = (lane & 3) * 2;
+        const bf16 *qrow = q + (size_t)b * ldq + (size_t)(kvh * G + g0) * HD;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; kk++) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                int r = r0 + (e & 1) * 8, k = kk * 16 + c + (e >> 1) * 8;
+                qf[kk][e] = r < rows ? *(const uint32_t *)(qrow + (size_t)r * HD + k) : 0u;
+            }
+        }
+    }
+    float o[HD / 8][4];
+#pragma unroll
+    for (int d = 0; d < HD / 8; d++) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const int lo[2] = {lo_key, lo_key}, hi[2] = {pos, pos};
+
+    int p = p_begin + warp;
+    if (p < p_end) {
+        size_t base = ((size_t)bt[p] * KV + kvh) * PAGE * HD;
+        load_page_warp<HD>(ks, k_pool + base, lane);
+        cp_async_commit();
+        load_page_warp<HD>(vs, v_pool + base, lane);
+        cp_async_commit();
+    }
+    for (; p < p_end; p += DEC_WARPS) {
+        const int pn = p + DEC_WARPS;
+        const size_t nbase = pn < p_end ? ((size_t)bt[pn] * KV + kvh) * PAGE * HD : 0;
+        cp_async_wait<1>();                    // K of this page has landed (V may still be in flight)
+        __syncwarp();
+        float s[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; j++) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+        qk_page<HD>(s, qf, ks, lane);
+        __syncwarp();
+        if (pn < p_end) load_page_warp<HD>(ks, k_pool + nbase, lane);
+        cp_async_commit();                     // (possibly empty) group: keeps the wait counts uniform
+        softmax_update<HD / 8>(s, o, m, l, scale, p * PAGE, lo, hi, lane);
+        cp_async_wait<1>();                    // V of this page has landed
+        __syncwarp();
+        pv_page<HD>(o, s, vs, lane);
+        __syncwarp();
+        if (pn < p_end) load_page_warp<HD>(vs, v_pool + nbase, lane);
+        cp_async_commit();
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // ---- merge the four warps: each leaves (m, l) and O[16][HD] in its own buffer
+    float *wo = (float *)kbuf;                 // 16 * HD floats <= TILE_BYTES
+    float *wml = (float *)vbuf;                // 16 * 2 floats
+    {
+        const int r0 = lane >> 2, c = (lane & 3) * 2;
+#pragma unroll
+        for (int d = 0; d < HD / 8; d++) {
+            wo[r0 * HD + d * 8 + c] = o[d][0];       wo[r0 * HD + d * 8 + c + 1] = o[d][1];
+            wo[(r0 + 8) * HD + d * 8 + c] = o[d][2]; wo[(r0 + 8) * HD + d * 8 + c + 1] = o[d][3];
+        }
+        if ((lane & 3) == 0) {
+            wml[r0 * 2] = m[0]; wml[r0 * 2 + 1] = l[0];
+            wml[(r0 + 8) * 2] = m[1]; wml[(r0 + 8) * 2 + 1] = l[1];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < rows * HD; i += DEC_WARPS * 32) {
+        int r = i / HD, d = i % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; w++) M = fmaxf(M, ((float *)(smem + (size_t)w * 2 * TILE_BYTES + TILE_BYTES))[r * 2]);
+        float O = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; w++) {
+            const float *pml = (const float *)(smem + (size_t)w * 2 * TILE_BYTES + TILE_BYTES);
+            const float *po = (const float *)(smem + (size_t)w * 2 * TILE_BYTES);
+            float mw = pml[r * 2];
+            float wgt = mw == -INFINITY ? 0.f : expf(mw - M);
+            O += wgt * po[r * HD + d];
+            L += wgt * pml[r * 2 + 1];
+        }
+        int h = kvh * G + g0 + r;
+        if (n_splits == 1) {
+            out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        } else {
+            size_t prow = ((size_t)b * KV * G + h) * n_splits + split;
+            part_o[prow * HD + d] = O;
+            if (d == 0) { part_ml[prow * 2] = M; part_ml[prow * 2 + 1] = L; }
+        }
+    }
+}
+
+// merge the splits of one (sequence, head) in split order
+template <int HD>
+__global__ void attn_decode_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml,
+                                         int n_splits, int H, bf16 *__restrict__ out, int ldo) {
+    const int b = blockIdx.y, h = blockIdx.x, d = threadIdx.x;
+    const size_t prow0 = ((size_t)b * H + h) * n_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; s++) M = fmaxf(M, part_ml[(prow0 + s) * 2]);
+    float O = 0.f, L = 0.f;
+    for (int s = 0; s < n_splits; s++) {
+        float ms = part_ml[(prow0 + s) * 2];
+        float wgt = ms == -INFINITY ? 0.f : expf(ms - M);
+        O += wgt * part_o[(prow0 + s) * HD + d];
+        L += wgt * part_ml[(prow0 + s) * 2 + 1];
+    }
+    out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+}
+
+template <int HD>
+static int launch_decode(const void *q, int ldq, void *out, int ldo, const int *positions, const int *block_table,
+                         int table_width, const void *k_pool, const void *v_pool, int B, int H, int KV, float scale,
+                         int window, int n_splits, float *part_o, float *part_ml, cudaStream_t stream) {
+    constexpr int smem = DEC_WARPS * 2 * PAGE * HD * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    int G = H / KV;
+    dim3 grid(n_splits, KV * ((G + 15) / 16), B);
+    attn_decode_kernel<HD><<<grid, DEC_WARPS * 32, smem, stream>>>((const bf16 *)q, ldq, positions, block_table, table_width,
+        (const bf16 *)k_pool, (const bf16 *)v_pool, KV, G, scale, window, n_splits, part_o, part_ml, (bf16 *)out, ldo);
+    int e = FG_LAUNCH_CHECK();
+    if (e || n_splits == 1) return e;
+    attn_decode_merge_kernel<HD><<<dim3(H, B), HD, 0, stream>>>(part_o, part_ml, n_splits, H, (bf16 *)out, ldo);
+    return FG_LAUNCH_CHECK();
+}
+
+// q: [B, ldq] bf16, one row per sequence, heads first in the row; positions[b] is the position of
+// that row (its key and value are already in the cache); pools [pages, KV, 64, HD] bf16.
+// part_o: [B, H, n_splits, HD] f32 and part_ml: [B, H, n_splits, 2] f32 scratch (unused when
+// n_splits == 1).  Takes HD 64 and 128 and pages of 64; anything else returns FG_ERR_BAD_SIZE.
+extern "C" int fg_attention_decode(const void *q, int ldq, void *out, int ldo, const int *positions,
+                                   const int *block_table, int table_width, const void *k_pool, const void *v_pool,
+                                   int B, int H, int KV, int hd, int page_size, float scale, int window,
+                                   int n_splits, float *part_o, float *part_ml, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (page_size != PAGE || H % KV || n_splits < 1 || B > 65535 || ldq % 2 || ((uintptr_t)q & 3)) return FG_ERR_BAD_SIZE;
+    if (n_splits > 1 && (!part_o || !part_ml)) return FG_ERR_BAD_SIZE;
+    if (hd == 64) return launch_decode<64>(q, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, B, H, KV, scale, window, n_splits, part_o, part_ml, stream);
+    if (hd == 128) return launch_decode<128>(q, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, B, H, KV, scale, window, n_splits, part_o, part_ml, stream);
+    return FG_ERR_BAD_SIZE;
+}

@@ -150,6 +150,14 @@ def attention_generic(q: torch.Tensor, positions: torch.Tensor, row_seq: torch.T
 def attention(q: torch.Tensor, batch, block_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
               n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> torch.Tensor:
     """Attention of a step's rows over the cache; picks the kernel by dtype, sizes and step shape."""
+    from . import fast_attention
+    if fast_attention.supported(q, k_pool, head_dim):
+        if batch.single_token:
+            return fast_attention.attention_decode(q, batch.positions, block_table, k_pool, v_pool, n_heads,
+                                                   n_kv_heads, head_dim, scale, window)
+        return fast_attention.attention_prefill(q, batch.cu_rows, batch.seq_start, block_table, k_pool, v_pool,
+                                                batch.n_seq, batch.max_new, n_heads, n_kv_heads, head_dim, scale,
+                                                window)
     return attention_generic(q, batch.positions, batch.row_seq, block_table, k_pool, v_pool,
                              n_heads, n_kv_heads, head_dim, scale, window)
 

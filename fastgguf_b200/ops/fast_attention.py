@@ -1,0 +1,63 @@
+"""bfloat16 tensor-core attention over the paged cache: a decode kernel (one new token per
+sequence, pages split over CTAs) and a prefill kernel (tiles of new tokens x query heads).
+Both take head sizes 64 and 128 and pages of 64 positions; ``supported`` says so, and the
+caller uses the any-size kernel otherwise."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_void_p
+from typing import Optional
+
+import torch
+
+from .lib import KernelError, check, lib, ptr, register_signatures, stream
+
+register_signatures("attn", {
+    "fg_attention_decode": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                            c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "fg_attention_prefill": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+})
+
+N_SM = 148
+
+
+def supported(q: torch.Tensor, k_pool: torch.Tensor, head_dim: int) -> bool:
+    return (q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and head_dim in (64, 128)
+            and k_pool.shape[2] == 64 and q.stride(1) == 1 and q.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0)
+
+
+def decode_splits(n_seq: int, n_heads: int, n_kv_heads: int, table_width: int) -> int:
+    """How many CTAs share one sequence's pages: enough to give every SM two CTAs."""
+    ctas = n_seq * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
+    return max(1, min((2 * N_SM + ctas - 1) // ctas, table_width))
+
+
+def attention_decode(q, positions, block_table, k_pool, v_pool, n_heads, n_kv_heads, head_dim, scale, window=0,
+                     n_splits: Optional[int] = None, out=None):
+    """q: [B, >= H*hd] bf16, one new token per sequence at ``positions[b]`` (already in the cache)."""
+    B = q.shape[0]
+    if n_splits is None:
+        n_splits = decode_splits(B, n_heads, n_kv_heads, block_table.shape[1])
+    if out is None:
+        out = torch.empty((B, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.empty((B, n_heads, n_splits, head_dim), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((B, n_heads, n_splits, 2), dtype=torch.float32, device=q.device)
+    check(lib("attn").fg_attention_decode(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(positions), ptr(block_table),
+                                          block_table.shape[1], ptr(k_pool), ptr(v_pool), B, n_heads, n_kv_heads,
+                                          head_dim, k_pool.shape[2], float(scale), int(window), n_splits,
+                                          ptr(part_o), ptr(part_ml), stream()), "attention_decode")
+    return out
+
+
+def attention_prefill(q, cu_rows, seq_start, block_table, k_pool, v_pool, n_seq, max_new, n_heads, n_kv_heads,
+                      head_dim, scale, window=0, out=None):
+    """q: [rows, >= H*hd] bf16, sequences one after another; every new key/value is in the cache."""
+    if out is None:
+        out = torch.empty((q.shape[0], n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    check(lib("attn").fg_attention_prefill(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cu_rows), ptr(seq_start),
+                                           ptr(block_table), block_table.shape[1], ptr(k_pool), ptr(v_pool), n_seq,
+                                           max_new, n_heads, n_kv_heads, head_dim, k_pool.shape[2], float(scale),
+                                           int(window), stream()), "attention_prefill")
+    return out
