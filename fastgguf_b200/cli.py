@@ -1,0 +1,223 @@
+"""Command line, in the manner of the reference's ``fastgguf <command> <model> [ctx] [options]``
+(fastgguf.c:10-17, :7067-7101), for model folders and token ids instead of GGUF files and text:
+
+    python -m fastgguf_b200 generate MODEL_DIR [ctx] --prompt 1,2,3 [--prompt ...] [options]
+    python -m fastgguf_b200 inspect  MODEL_DIR           config, sizes, tensor table
+    python -m fastgguf_b200 dump     MODEL_DIR           every key of config.json
+    python -m fastgguf_b200 random   CONFIG.json OUT_DIR [--seed N] [--dtype bfloat16|float32]
+    python -m fastgguf_b200 selftest                     every kernel against a plain computation
+
+Options of ``generate`` are the reference's chat options with the same names, meanings and
+defaults (fastgguf.c:6957-6982): positional ``ctx`` (2048, at least 64); ``--temp 1.0`` (0 =
+greedy); ``--top-k 64`` (0 = off); ``--top-p 0.95``; ``--repeat-penalty 1.0`` (1 = off);
+``--repeat-last-n 64``; ``--max-tokens 512`` (0 = until stop); ``--seed N``.  An unknown option
+or a missing value prints a message and exits 1; a model that cannot be loaded exits 2
+(fastgguf.c:5224-5228).
+"""
+from __future__ import annotations
+
+import json
+import sys
+import time
+from typing import List
+
+USAGE = __doc__
+
+CHAT_OPTIONS_HELP = (
+    "generate options: --temp 1.0 (0 = greedy)  --top-k 64 (0 = off)  --top-p 0.95\n"
+    "                  --repeat-penalty 1.0 (1 = off)  --repeat-last-n 64\n"
+    "                  --max-tokens 512 (0 = until stop)  --seed N\n"
+    "                  --prompt ID,ID,...  (repeat for a batch)  --prompts-file FILE (one prompt a line)\n"
+    "                  --dtype bfloat16|float32  --batch N  --ignore-eos  --json\n")
+
+
+class UsageError(Exception):
+    pass
+
+
+def parse_generate_args(argv: List[str]) -> dict:
+    """Positional [ctx], then --option value pairs (fastgguf.c:6957-6974)."""
+    o = dict(ctx=2048, temp=1.0, top_k=64, top_p=0.95, repeat_penalty=1.0, repeat_last_n=64, max_tokens=512,
+             seed=0, prompts=[], dtype="bfloat16", batch=None, ignore_eos=False, json=False)
+    flags = {"--ignore-eos": "ignore_eos", "--json": "json"}
+    valued = {"--temp": ("temp", float), "--top-k": ("top_k", int), "--top-p": ("top_p", float),
+              "--repeat-penalty": ("repeat_penalty", float), "--repeat-last-n": ("repeat_last_n", int),
+              "--max-tokens": ("max_tokens", int), "--seed": ("seed", int), "--dtype": ("dtype", str),
+              "--batch": ("batch", int)}
+    i = 0
+    while i < len(argv):
+        a = argv[i]
+        if not a.startswith("-"):
+            try:
+                o["ctx"] = int(a)
+            except ValueError:
+                raise UsageError(f"unknown argument {a}") from None
+            i += 1
+            continue
+        if a in flags:
+            o[flags[a]] = True
+            i += 1
+            continue
+        if i + 1 >= len(argv):
+            raise UsageError(f"missing value for {a}")
+        v = argv[i + 1]
+        i += 2
+        try:
+            if a in valued:
+                key, typ = valued[a]
+                o[key] = typ(v)
+            elif a == "--prompt":
+                o["prompts"].append([int(t) for t in v.replace(",", " ").split()])
+            elif a == "--prompts-file":
+                with open(v) as f:
+                    o["prompts"].extend([int(t) for t in line.replace(",", " ").split()] for line in f if line.strip())
+            else:
+                raise UsageError(f"unknown option {a}")
+        except ValueError:
+            raise UsageError(f"bad value for {a}: {v}") from None
+    o["ctx"] = max(64, o["ctx"])
+    return o
+
+
+def cmd_generate(model_dir: str, argv: List[str]) -> int:
+    o = parse_generate_args(argv)
+    if not o["prompts"]:
+        raise UsageError("generate needs at least one --prompt ID,ID,... (token ids) or --prompts-file FILE")
+    from .engine.api import Engine
+    n = len(o["prompts"])
+    batch = o["batch"] or min(n, 64)
+    try:
+        engine = Engine.from_dir(model_dir, dtype=o["dtype"], max_tokens=batch * ((o["ctx"] + 63) // 64 * 64),
+                                 max_batch=batch, max_seq_len=o["ctx"])
+    except (ValueError, OSError) as e:
+        print(e)
+        return 2
+    cfg = engine.config
+    print(f"[Config] {type(cfg).architecture_names[0]}: layers={len(engine.spec.layers)} embd={engine.spec.hidden_size} "
+          f"ctx={engine.cache.max_seq_len} dtype={o['dtype']}")
+    print(f"[Model] {len(engine.model.expected_tensors())} tensors, vocab={engine.spec.vocab_size}")
+    if o["temp"] <= 0:
+        print("[Sampler] greedy", end="")
+    else:
+        print(f"[Sampler] temp={o['temp']:.2f} top_k={o['top_k']} top_p={o['top_p']:.2f}", end="")
+    print(f" repeat_penalty={o['repeat_penalty']:.2f} (last {o['repeat_last_n']}) max_tokens={o['max_tokens']} "
+          f"seed={o['seed']}")
+    import torch
+    t0 = time.time()
+    out = engine.generate(o["prompts"], temp=o["temp"], top_k=o["top_k"], top_p=o["top_p"],
+                          repeat_penalty=o["repeat_penalty"], repeat_last_n=o["repeat_last_n"],
+                          max_tokens=o["max_tokens"], seed=o["seed"], ignore_eos=o["ignore_eos"], batch_size=batch)
+    torch.cuda.synchronize()
+    dt = time.time() - t0
+    n_gen = sum(len(c.tokens) for c in out)
+    if o["json"]:
+        print(json.dumps([{"tokens": c.tokens, "finish_reason": c.finish_reason} for c in out]))
+    else:
+        for i, c in enumerate(out):
+            print(f"[{i}] {' '.join(str(t) for t in c.tokens)}  ({c.finish_reason})")
+    print(f"[gen: {n_gen} tok in {dt:.2f}s @ {n_gen / max(dt, 1e-9):.2f} tok/s, prompts included]")
+    return 0
+
+
+def cmd_inspect(model_dir: str, as_json: bool = False) -> int:
+    """What ``fastgguf inspect`` prints for a GGUF file (fastgguf.c:5319-5360), for a model folder:
+    the architecture, every configuration field and derived size, a dtype histogram and the tensors."""
+    from .config.base import ConfigError
+    from .registry import config_from_dir
+    from .weights.loader import FolderSource
+    from .weights.safetensors_io import SafetensorsError
+    try:
+        cfg = config_from_dir(model_dir)
+        src = FolderSource(model_dir)
+    except (ConfigError, SafetensorsError, OSError) as e:
+        print(e)
+        return 2
+    desc = cfg.describe()
+    tensors = [(n, *src.shape_dtype(n)) for n in sorted(src.names())]
+    if as_json:
+        print(json.dumps({"architecture": type(cfg).architecture_names[0], "config": desc,
+                          "tensors": [{"name": n, "shape": list(s), "dtype": str(d)} for n, s, d in tensors]},
+                         default=str))
+        return 0
+    print(f"architecture: {type(cfg).architecture_names[0]}")
+    for k, v in desc.items():
+        print(f"  {k} = {v}")
+    hist = {}
+    for _, s, d in tensors:
+        hist[str(d)] = hist.get(str(d), 0) + 1
+    print(f"tensors: {len(tensors)}  (" + ", ".join(f"{k}: {v}" for k, v in sorted(hist.items())) + ")")
+    for n, s, d in tensors[:15]:
+        print(f"  {n:<48} {str(d).replace('torch.', ''):<9} {list(s)}")
+    if len(tensors) > 15:
+        print(f"  ... {len(tensors) - 15} more")
+    return 0
+
+
+def cmd_dump(model_dir: str) -> int:
+    """Every key of config.json (the reference's ``dump`` prints every metadata key, fastgguf.c:5362-5375)."""
+    from .config.base import ConfigError, read_config_json
+    try:
+        d = read_config_json(model_dir)
+    except ConfigError as e:
+        print(e)
+        return 2
+    for k, v in d.items():
+        print(f"{k} = {json.dumps(v)}")
+    return 0
+
+
+def cmd_random(argv: List[str]) -> int:
+    if len(argv) < 2:
+        raise UsageError("random needs CONFIG.json and OUT_DIR")
+    seed, dtype = 0, "bfloat16"
+    i = 2
+    while i < len(argv):
+        if i + 1 >= len(argv):
+            raise UsageError(f"missing value for {argv[i]}")
+        if argv[i] == "--seed":
+            seed = int(argv[i + 1])
+        elif argv[i] == "--dtype":
+            dtype = argv[i + 1]
+        else:
+            raise UsageError(f"unknown option {argv[i]}")
+        i += 2
+    from .engine.api import parse_dtype
+    from .registry import config_from_dict
+    from .weights.random_init import write_random_model
+    with open(argv[0]) as f:
+        cfg = config_from_dict(json.load(f))
+    out = write_random_model(cfg, seed, argv[1], parse_dtype(dtype))
+    print(f"wrote {out}/config.json and {out}/model.safetensors (seed {seed}, {dtype})")
+    return 0
+
+
+def main(argv: List[str] = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if not argv or argv[0] in ("-h", "--help", "help"):
+        print(USAGE)
+        print(CHAT_OPTIONS_HELP)
+        return 0 if argv else 1
+    cmd, rest = argv[0], argv[1:]
+    try:
+        if cmd == "selftest":
+            from .selftest import run_selftest
+            return run_selftest(quick="--quick" in rest)
+        if cmd == "random":
+            return cmd_random(rest)
+        if cmd in ("generate", "chat", "inspect", "dump"):
+            if not rest:
+                raise UsageError(f"{cmd} needs a model folder")
+            if cmd == "inspect":
+                return cmd_inspect(rest[0], "--json" in rest[1:])
+            if cmd == "dump":
+                return cmd_dump(rest[0])
+            return cmd_generate(rest[0], rest[1:])
+        raise UsageError(f"unknown command {cmd}")
+    except UsageError as e:
+        print(e)
+        print(CHAT_OPTIONS_HELP)
+        return 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -149,3 +149,21 @@ extern "C" int fg_silu_mul(const void *gu, void *out, int dtype, int M, int F, c
     else return FG_ERR_BAD_DTYPE;
     return FG_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------ decode feedback
+// After a decode step of a fixed-shape (graph-replayed) batch: the sampled token of every row
+// becomes its next input, and live rows move on by one position.
+__global__ void decode_advance_kernel(int *__restrict__ tokens, int *__restrict__ positions,
+                                      const int *__restrict__ next_tokens, const int *__restrict__ active, int B) {
+    int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    tokens[b] = next_tokens[b];
+    if (active[b]) positions[b] += 1;
+}
+
+extern "C" int fg_decode_advance(int *tokens, int *positions, const int *next_tokens, const int *active, int B,
+                                 cudaStream_t stream) {
+    if (B <= 0) return 0;
+    decode_advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(tokens, positions, next_tokens, active, B);
+    return FG_LAUNCH_CHECK();
+}

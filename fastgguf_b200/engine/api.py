@@ -43,7 +43,8 @@ class Engine:
     sequences hold at any time, each sequence rounded up to a page of 64."""
 
     def __init__(self, config: ModelConfig, source: TensorSource, *, dtype="bfloat16", max_tokens: int = 8192,
-                 max_batch: int = 64, max_seq_len: Optional[int] = None, device: str = "cuda:0"):
+                 max_batch: int = 64, max_seq_len: Optional[int] = None, device: str = "cuda:0",
+                 use_graphs: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("fastgguf_b200 runs on a CUDA device (sm_100a); no GPU is visible and there is "
                                "no CPU path")
@@ -55,6 +56,8 @@ class Engine:
         self.model = DecoderModel(self.spec, Runtime(self.device, self.dtype))
         self.model.load_weights(source)
         self.max_batch = max_batch
+        self.use_graphs = use_graphs
+        self._backends: dict = {}
         self.cache = self.model.make_cache(max_tokens=max_tokens, n_slots=max_batch, max_seq_len=max_seq_len)
 
     @classmethod
@@ -79,6 +82,18 @@ class Engine:
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         return self.model.step(entries)
+
+    def backend(self, params, stop_ids):
+        """The sampler state and captured decode graphs for one set of sampling options (kept, so
+        that a second call with the same options replays the graphs of the first)."""
+        from .runner import EngineBackend
+        key = (params, tuple(stop_ids))
+        b = self._backends.get(key)
+        if b is None:
+            b = self._backends[key] = EngineBackend(self, params, stop_ids)
+        else:
+            b.reseed()
+        return b
 
     # ------------------------------------------------------------------ generation
     def generate(self, prompts: Sequence[Sequence[int]], *, temp: float = 1.0, top_k: int = 64, top_p: float = 0.95,

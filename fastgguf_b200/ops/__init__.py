@@ -10,7 +10,7 @@ from .lib import KernelError, check, dtype_code, lib, ptr, require_cuda, stream
 
 __all__ = [
     "KernelError", "embed_gather", "rmsnorm", "rope_append", "silu_mul", "gemm_generic",
-    "attention_generic", "attention", "sample", "argmax",
+    "attention_generic", "attention", "sample", "argmax", "decode_advance",
 ]
 
 
@@ -200,3 +200,12 @@ def sample(logits: torch.Tensor, *, temp: float, top_k: int, top_p: float, repea
                           float(repeat_penalty), int(repeat_last_n), ptr(_i32(seq_slot, "seq_slot")), ptr(rng),
                           ptr(hist), cap, ptr(hist_count), ptr(stop_ids), n_stop, ptr(out), stream()), "sample")
     return out
+
+
+def decode_advance(tokens: torch.Tensor, positions: torch.Tensor, next_tokens: torch.Tensor,
+                   active: torch.Tensor) -> None:
+    """tokens <- next_tokens; positions += 1 where active (all int32, same length)."""
+    require_cuda(tokens, positions, next_tokens, active)
+    check(lib().fg_decode_advance(ptr(_i32(tokens, "tokens")), ptr(_i32(positions, "positions")),
+                                  ptr(_i32(next_tokens, "next_tokens")), ptr(_i32(active, "active")),
+                                  tokens.numel(), stream()), "decode_advance")
