@@ -64,13 +64,15 @@ class DecodeGraph:
                            block_tables=self.tables, n_want=B, max_new=1, max_len=cache.max_seq_len,
                            single_token=True)
         self.model = model
+        from ..ops import lib as ops_lib
+        before = ops_lib.launch_count
         self._run()                                   # warm-up outside capture: loads modules, sets attributes
+        self.launches_per_step = ops_lib.launch_count - before
         torch.cuda.synchronize()
         self.tokens.zero_(); self.positions.zero_()
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self._run()
-        self.launches_per_step = None
 
     def _run(self) -> None:
         logits = self.model.forward(self.batch)
@@ -131,38 +133,15 @@ class EngineBackend:
         return g
 
     def _run_batch_graphs(self, prompts, first_index, max_tokens, stop_ids) -> List[Completion]:
-        eng, cache, dev = self.engine, self.engine.cache, self.engine.device
+        cache = self.engine.cache
         stop = set(stop_ids)
-        for p in prompts:
-            if len(p) == 0:
-                raise ValueError("a prompt needs at least one token")
         n = len(prompts)
-        g = self._graph(bucket_for(n))                # captured before slots are taken: its warm-up uses page 0 only
-        slots = [self.acquire(first_index + i, p) for i, p in enumerate(prompts)]
+        session = DecodeSession(self, prompts, first_index)
         done = [Completion(len(p)) for p in prompts]
         try:
-            # ---- prompts: one step, logits at each prompt's last token, first sample
-            logits = self.step([StepEntry(slots[i], list(prompts[i]), [len(prompts[i]) - 1]) for i in range(n)])
-            rows = torch.tensor(slots, dtype=torch.int32, device=dev)
-            first = self.sampler.sample(logits, rows)
-            # ---- fixed buffers of the decode graph
-            W = g.width
-            g.tokens.zero_(); g.positions.zero_(); g.active.zero_()
-            g.rows.fill_(self.sampler.spare_row)
-            for t in g.tables:
-                t.zero_()
-            g.tokens[:n] = first
-            g.positions[:n] = torch.tensor([len(p) for p in prompts], dtype=torch.int32, device=dev)
-            g.rows[:n] = rows
-            g.active[:n] = 1
-            widths = [0] * n                           # page-table entries of each row already uploaded
-            host_tokens = first.cpu().tolist()
-            self.stats["d2h_bytes"] += 4 * n
-            # sample k is produced by step k (k = 0: the prompt step); emitted[k] are its tokens
-            pending = deque([(list(range(n)), host_tokens, None)])
+            # sample k is produced by step k (k = 0: the prompt step); the host sees it one step late
+            pending = deque([(list(range(n)), session.first_tokens, None)])
             known_done = [False] * n                   # decided from tokens the host has seen
-            fed = [0] * n                              # decode steps each sequence has been fed
-            step_no = 0
 
             def settle(block: bool) -> None:
                 while pending and (block or len(pending) > 1 or pending[0][2] is None):
@@ -174,59 +153,98 @@ class EngineBackend:
                         if known_done[i]:
                             continue
                         tok, c = toks[i], done[i]
-                        if tok in stop:
+                        if tok in stop:                # not emitted, not fed on purpose, not recorded
                             c.finish_reason, known_done[i] = "stop", True
                             continue
                         c.tokens.append(int(tok))
                         if 0 < max_tokens <= len(c.tokens) or len(prompts[i]) + len(c.tokens) - 1 >= cache.max_seq_len:
                             c.finish_reason, known_done[i] = "length", True
 
+            step_no = 0
             while True:
                 settle(block=False)
                 step_no += 1
                 # a sequence takes decode step s when it is not known to have ended, when sample s - 1
-                # could not have been its last by length, and when the cache has room for the token
+                # cannot have been its last by length, and when the cache has room for the token
                 live = [i for i in range(n) if not known_done[i]
                         and (max_tokens <= 0 or step_no < max_tokens)
                         and len(prompts[i]) + step_no <= cache.max_seq_len]
                 if not live:
-                    settle(block=True)
-                    # a late stop may have ended the last sequences; nothing is live either way
-                    live = []
                     break
-                cache.reserve([(slots[i], 1) for i in live])
-                gone = [i for i in range(n) if i not in live and widths[i] >= 0]
-                for i in gone:                         # finished rows: page 0, spare sampler row, position 0
-                    for t in g.tables:
-                        t[i].zero_()
-                    g.active[i] = 0
-                    g.positions[i] = 0
-                    g.rows[i] = self.sampler.spare_row
-                    widths[i] = -1
-                for i in live:                         # upload page-table entries the step will touch
-                    need = (cache.length(slots[i]) + 1 + cache.page_size - 1) // cache.page_size
-                    if need > widths[i]:
-                        for gi, t in enumerate(g.tables):
-                            row = cache.tables[gi][slots[i], widths[i]:need]
-                            t[i, widths[i]:need] = torch.from_numpy(row.copy()).to(dev)
-                            self.stats["h2d_bytes"] += 4 * (need - widths[i])
-                        widths[i] = need
-                g.replay()
-                cache.commit([(slots[i], 1) for i in live])
-                self.stats["steps"] += 1
-                host = torch.empty(W, dtype=torch.int32, pin_memory=True)
-                host.copy_(g.next_tokens, non_blocking=True)
-                ev = torch.cuda.Event()
-                ev.record()
-                self.stats["d2h_bytes"] += 4 * W
+                host, ev = session.advance(live)
                 pending.append((live, host, ev))
-                for i in live:
-                    fed[i] += 1
             settle(block=True)
-            for c in done:
-                if not c.finish_reason:
-                    c.finish_reason = "length"
         finally:
-            for s in slots:
-                self.release(s)
+            session.close()
         return done
+
+
+class DecodeSession:
+    """One batch on the graph path: the prompt step, then ``advance(live)`` once per decode step."""
+
+    def __init__(self, backend: EngineBackend, prompts, first_index: int = 0):
+        self.backend, self.prompts = backend, prompts
+        eng, dev = backend.engine, backend.engine.device
+        for p in prompts:
+            if len(p) == 0:
+                raise ValueError("a prompt needs at least one token")
+        n = self.n = len(prompts)
+        g = self.graph = backend._graph(bucket_for(n))   # captured before slots are taken: its warm-up uses page 0
+        self.slots = [backend.acquire(first_index + i, p) for i, p in enumerate(prompts)]
+        try:
+            logits = backend.step([StepEntry(self.slots[i], list(prompts[i]), [len(prompts[i]) - 1]) for i in range(n)])
+            rows = torch.tensor(self.slots, dtype=torch.int32, device=dev)
+            first = backend.sampler.sample(logits, rows)
+            g.tokens.zero_(); g.positions.zero_(); g.active.zero_()
+            g.rows.fill_(backend.sampler.spare_row)
+            for t in g.tables:
+                t.zero_()
+            g.tokens[:n] = first
+            g.positions[:n] = torch.tensor([len(p) for p in prompts], dtype=torch.int32, device=dev)
+            g.rows[:n] = rows
+            g.active[:n] = 1
+            self.widths = [0] * n                      # page-table entries of each row already uploaded
+            self.first_tokens = first.cpu().tolist()
+            backend.stats["d2h_bytes"] += 4 * n
+        except BaseException:
+            self.close()
+            raise
+
+    def advance(self, live: Sequence[int]):
+        """One decode step for the sequences ``live`` (indices into the batch).  Returns the pinned
+        host tensor that receives the sampled tokens of all rows and the event that says when."""
+        backend, g = self.backend, self.graph
+        cache, dev = backend.engine.cache, backend.engine.device
+        steps = [(self.slots[i], 1) for i in live]
+        cache.reserve(steps)
+        live_set = set(live)
+        for i in range(self.n):
+            if i not in live_set and self.widths[i] >= 0:     # finished: page 0, spare sampler row, position 0
+                for t in g.tables:
+                    t[i].zero_()
+                g.active[i] = 0
+                g.positions[i] = 0
+                g.rows[i] = backend.sampler.spare_row
+                self.widths[i] = -1
+        for i in live:                                 # upload page-table entries the step will touch
+            need = (cache.length(self.slots[i]) + 1 + cache.page_size - 1) // cache.page_size
+            if need > self.widths[i]:
+                for gi, t in enumerate(g.tables):
+                    row = cache.tables[gi][self.slots[i], self.widths[i]:need]
+                    t[i, self.widths[i]:need] = torch.from_numpy(row.copy()).to(dev)
+                    backend.stats["h2d_bytes"] += 4 * (need - self.widths[i])
+                self.widths[i] = need
+        g.replay()
+        cache.commit(steps)
+        backend.stats["steps"] += 1
+        host = torch.empty(g.width, dtype=torch.int32, pin_memory=True)
+        host.copy_(g.next_tokens, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        backend.stats["d2h_bytes"] += 4 * g.width
+        return host, ev
+
+    def close(self) -> None:
+        for s in self.slots:
+            self.backend.release(s)
+        self.slots = []

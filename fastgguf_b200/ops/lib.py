@@ -44,7 +44,13 @@ def stream() -> c_void_p:
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+#: launcher calls made so far (each launches at least one kernel of this library)
+launch_count = 0
+
+
 def check(code: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
     if code != 0:
         msg = _ERRORS.get(code)
         if msg is None:

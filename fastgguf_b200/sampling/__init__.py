@@ -78,7 +78,7 @@ class Sampler:
         self.params, self.device = params, device
         self.n_rows = n_rows + 1
         self.spare_row = n_rows
-        self.rng = torch.full((self.n_rows,), 0x9E3779B97F4A7C15, dtype=torch.int64, device=device)
+        self.rng = torch.full((self.n_rows,), _as_i64(0x9E3779B97F4A7C15), dtype=torch.int64, device=device)
         self.hist_cap = max(1, params.repeat_last_n)
         self.use_hist = params.penalizes
         self.hist = torch.zeros((self.n_rows, self.hist_cap), dtype=torch.int32, device=device) if self.use_hist else None

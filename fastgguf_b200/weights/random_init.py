@@ -25,13 +25,15 @@ def _tensor_seed(seed: int, name: str) -> int:
     return int.from_bytes(h[:8], "little") & 0x7FFFFFFFFFFFFFFF
 
 
-def random_tensor(name: str, spec: TensorSpec, seed: int, dtype: torch.dtype) -> torch.Tensor:
-    g = torch.Generator(device="cpu")
+def random_tensor(name: str, spec: TensorSpec, seed: int, dtype: torch.dtype, device="cpu") -> torch.Tensor:
+    """One tensor's values.  The values depend on (seed, name) and on the kind of ``device`` (the CPU
+    and CUDA generators differ); model folders are always written from the CPU generator."""
+    g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, name))
     if spec.kind == "int":
-        return torch.zeros(spec.shape, dtype=torch.int32)
+        return torch.zeros(spec.shape, dtype=torch.int32, device=device)
     kind, std = spec.init
-    t = torch.randn(spec.shape, generator=g, dtype=torch.float32) * std
+    t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device) * std
     if kind == "one_plus_normal":
         t = t + 1.0
     elif kind != "normal":
@@ -39,12 +41,13 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, dtype: torch.dtype) ->
     return t.to(dtype)
 
 
-def random_tensors(config: ModelConfig, seed: int, dtype: torch.dtype = torch.bfloat16) -> Dict[str, torch.Tensor]:
-    """CPU tensors by checkpoint name for ``config``, stored as ``dtype``."""
+def random_tensors(config: ModelConfig, seed: int, dtype: torch.dtype = torch.bfloat16,
+                   device="cpu") -> Dict[str, torch.Tensor]:
+    """Tensors by checkpoint name for ``config``, stored as ``dtype`` (on the CPU unless told otherwise)."""
     from ..engine.model import DecoderModel
     from ..registry import spec_from_config
     model = DecoderModel(spec_from_config(config), Runtime(torch.device("cpu"), dtype))
-    return {name: random_tensor(name, spec, seed, dtype) for name, spec in model.expected_tensors().items()}
+    return {name: random_tensor(name, spec, seed, dtype, device) for name, spec in model.expected_tensors().items()}
 
 
 def write_random_model(config: ModelConfig, seed: int, out_dir: str, dtype: torch.dtype = torch.bfloat16) -> str:
