@@ -136,7 +136,6 @@ def main():
     import torch
     from fastgguf_b200.engine.api import Engine
     from fastgguf_b200.engine.runner import DecodeSession
-    from fastgguf_b200.ops import lib as ops_lib
     from fastgguf_b200.registry import config_from_dict
     from fastgguf_b200.sampling import SamplingParams
     from fastgguf_b200.weights.random_init import random_tensors

@@ -64,10 +64,10 @@ class DecodeGraph:
                            block_tables=self.tables, n_want=B, max_new=1, max_len=cache.max_seq_len,
                            single_token=True)
         self.model = model
-        from ..ops import lib as ops_lib
-        before = ops_lib.launch_count
+        from ..ops.lib import launches
+        before = launches()
         self._run()                                   # warm-up outside capture: loads modules, sets attributes
-        self.launches_per_step = ops_lib.launch_count - before
+        self.launches_per_step = launches() - before
         torch.cuda.synchronize()
         self.tokens.zero_(); self.positions.zero_()
         self.graph = torch.cuda.CUDAGraph()

@@ -48,6 +48,10 @@ def stream() -> c_void_p:
 launch_count = 0
 
 
+def launches() -> int:
+    return launch_count
+
+
 def check(code: int, what: str) -> None:
     global launch_count
     launch_count += 1
