@@ -29,6 +29,8 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
     const int kvh = blockIdx.y / chunks, g0 = (blockIdx.y % chunks) * 16;
     const int rows = min(16, G - g0);
     const int b = blockIdx.z, split = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const int pos = positions[b];
     const int lo_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int first_page = lo_key / PAGE, n_pages = pos / PAGE - first_page + 1;
@@ -137,6 +139,8 @@ template <int HD>
 __global__ void attn_decode_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml,
                                          int n_splits, int H, bf16 *__restrict__ out, int ldo) {
     const int b = blockIdx.y, h = blockIdx.x, d = threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t prow0 = ((size_t)b * H + h) * n_splits;
     float M = -INFINITY;
     for (int s = 0; s < n_splits; s++) M = fmaxf(M, part_ml[(prow0 + s) * 2]);
@@ -163,12 +167,10 @@ static int launch_decode(const void *q, int ldq, void *out, int ldo, const int *
     }
     int G = H / KV;
     dim3 grid(n_splits, KV * ((G + 15) / 16), B);
-    attn_decode_kernel<HD><<<grid, DEC_WARPS * 32, smem, stream>>>((const bf16 *)q, ldq, positions, block_table, table_width,
+    int e = fg_launch(attn_decode_kernel<HD>, grid, dim3(DEC_WARPS * 32), (size_t)smem, stream, (const bf16 *)q, ldq, positions, block_table, table_width,
         (const bf16 *)k_pool, (const bf16 *)v_pool, KV, G, scale, window, n_splits, part_o, part_ml, (bf16 *)out, ldo);
-    int e = FG_LAUNCH_CHECK();
     if (e || n_splits == 1) return e;
-    attn_decode_merge_kernel<HD><<<dim3(H, B), HD, 0, stream>>>(part_o, part_ml, n_splits, H, (bf16 *)out, ldo);
-    return FG_LAUNCH_CHECK();
+    return fg_launch(attn_decode_merge_kernel<HD>, dim3(H, B), dim3(HD), 0, stream, (const float *)part_o, (const float *)part_ml, n_splits, H, (bf16 *)out, ldo);
 }
 
 // q: [B, ldq] bf16, one row per sequence, heads first in the row; positions[b] is the position of

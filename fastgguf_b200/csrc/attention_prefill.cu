@@ -42,6 +42,8 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
     const int chunks = (G + Gc - 1) / Gc;
     const int kvh = blockIdx.y / chunks, g0 = (blockIdx.y % chunks) * Gc;
     const int b = blockIdx.z;
+    pdl_launch_dependents();
+    pdl_wait();
     const int row0 = cu_rows[b], n_tok = cu_rows[b + 1] - row0, start = seq_start[b];
     const int q0 = blockIdx.x * TQ;
     if (q0 >= n_tok) return;
@@ -139,9 +141,8 @@ static int launch_prefill(const void *q, int ldq, void *out, int ldo, const int 
     }
     int G = H / KV, Gc = G < 16 ? G : 16, TQ = PF_ROWS / Gc;
     dim3 grid((max_new + TQ - 1) / TQ, KV * ((G + Gc - 1) / Gc), n_seq);
-    attn_prefill_kernel<HD><<<grid, PF_WARPS * 32, smem, stream>>>((const bf16 *)q, ldq, (bf16 *)out, ldo, cu_rows,
+    return fg_launch(attn_prefill_kernel<HD>, grid, dim3(PF_WARPS * 32), (size_t)smem, stream, (const bf16 *)q, ldq, (bf16 *)out, ldo, cu_rows,
         seq_start, block_table, table_width, (const bf16 *)k_pool, (const bf16 *)v_pool, KV, G, scale, window);
-    return FG_LAUNCH_CHECK();
 }
 
 // q: [rows, ldq] bf16 rows of all sequences one after another (cu_rows[b] = first row of sequence b,

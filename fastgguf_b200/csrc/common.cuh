@@ -69,3 +69,33 @@ __device__ __forceinline__ float block_max(float v, float *scratch) {
 }
 
 #define FG_LAUNCH_CHECK() ((int)cudaGetLastError())
+
+// ------------------------------------------------------------------ dependent launches
+// Every kernel of this library is launched with programmatic stream serialization: it may
+// start while the kernel before it on the stream is still running.  Each kernel calls
+// pdl_launch_dependents() at its start (its successor may be scheduled) and pdl_wait() before
+// it first touches memory that an earlier kernel writes or reads; what it does before that
+// wait (barrier set-up, fetching weights, which no kernel writes) overlaps the predecessor.
+// FASTGGUF_PDL=0 turns the attribute off; the two instructions are then no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+#include <cstdlib>
+static inline bool fg_pdl_enabled() {
+    static int v = -1;
+    if (v < 0) { const char *e = getenv("FASTGGUF_PDL"); v = !(e && e[0] == '0'); }
+    return v != 0;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int fg_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                            Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = fg_pdl_enabled() ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

@@ -13,6 +13,8 @@
 template <typename TW>
 __global__ void embed_gather_kernel(const TW *__restrict__ table, const int *__restrict__ tokens,
                                     float *__restrict__ x, int E) {
+    pdl_launch_dependents();
+    pdl_wait();
     int m = blockIdx.x;
     const TW *row = table + (size_t)tokens[m] * E;
     float *out = x + (size_t)m * E;
@@ -24,9 +26,9 @@ extern "C" int fg_embed_gather(const void *table, int table_dtype, const int *to
     if (M <= 0) return 0;
     int threads = E >= 1024 ? 256 : 128;
     if (table_dtype == FG_F32)
-        embed_gather_kernel<float><<<M, threads, 0, stream>>>((const float *)table, tokens, x, E);
+        return fg_launch(embed_gather_kernel<float>, dim3(M), dim3(threads), 0, stream, (const float *)table, tokens, x, E);
     else if (table_dtype == FG_BF16)
-        embed_gather_kernel<bf16><<<M, threads, 0, stream>>>((const bf16 *)table, tokens, x, E);
+        return fg_launch(embed_gather_kernel<bf16>, dim3(M), dim3(threads), 0, stream, (const bf16 *)table, tokens, x, E);
     else return FG_ERR_BAD_DTYPE;
     return FG_LAUNCH_CHECK();
 }
@@ -39,6 +41,8 @@ template <typename TO>
 __global__ void rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ w,
                                const int *__restrict__ rows, TO *__restrict__ out, int E, float eps) {
     __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
     int r = blockIdx.x;
     const float *xi = x + (size_t)(rows ? rows[r] : r) * E;
     float ss = 0.f;
@@ -54,9 +58,9 @@ extern "C" int fg_rmsnorm(const float *x, const float *w, const int *rows, void 
     if (R <= 0) return 0;
     int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : 128);
     if (out_dtype == FG_F32)
-        rmsnorm_kernel<float><<<R, threads, 0, stream>>>(x, w, rows, (float *)out, E, eps);
+        return fg_launch(rmsnorm_kernel<float>, dim3(R), dim3(threads), 0, stream, x, w, rows, (float *)out, E, eps);
     else if (out_dtype == FG_BF16)
-        rmsnorm_kernel<bf16><<<R, threads, 0, stream>>>(x, w, rows, (bf16 *)out, E, eps);
+        return fg_launch(rmsnorm_kernel<bf16>, dim3(R), dim3(threads), 0, stream, x, w, rows, (bf16 *)out, E, eps);
     else return FG_ERR_BAD_DTYPE;
     return FG_LAUNCH_CHECK();
 }
@@ -71,6 +75,8 @@ __global__ void rope_append_kernel(T *__restrict__ qkv, int ld, const int *__res
                                    int table_width, T *__restrict__ k_pool, T *__restrict__ v_pool,
                                    const float *__restrict__ cos_t, const float *__restrict__ sin_t,
                                    int H, int KV, int hd, int page_size, int write_kv) {
+    pdl_launch_dependents();
+    pdl_wait();
     int m = blockIdx.x;
     int pos = positions[m];
     int half = hd >> 1;
@@ -113,10 +119,10 @@ extern "C" int fg_rope_append(void *qkv, int dtype, int ld, const int *positions
     int work = H * hd / 2;
     int threads = work >= 1024 ? 256 : (work >= 128 ? 128 : 64);
     if (dtype == FG_F32)
-        rope_append_kernel<float><<<M, threads, 0, stream>>>((float *)qkv, ld, positions, row_seq, block_table,
+        return fg_launch(rope_append_kernel<float>, dim3(M), dim3(threads), 0, stream, (float *)qkv, ld, positions, row_seq, block_table,
             table_width, (float *)k_pool, (float *)v_pool, cos_t, sin_t, H, KV, hd, page_size, write_kv);
     else if (dtype == FG_BF16)
-        rope_append_kernel<bf16><<<M, threads, 0, stream>>>((bf16 *)qkv, ld, positions, row_seq, block_table,
+        return fg_launch(rope_append_kernel<bf16>, dim3(M), dim3(threads), 0, stream, (bf16 *)qkv, ld, positions, row_seq, block_table,
             table_width, (bf16 *)k_pool, (bf16 *)v_pool, cos_t, sin_t, H, KV, hd, page_size, write_kv);
     else return FG_ERR_BAD_DTYPE;
     return FG_LAUNCH_CHECK();
@@ -126,6 +132,8 @@ extern "C" int fg_rope_append(void *qkv, int dtype, int ld, const int *positions
 // gu: [M, 2F] rows of (gate | up); out: [M, F].
 template <typename T>
 __global__ void silu_mul_kernel(const T *__restrict__ gu, T *__restrict__ out, size_t total, int F) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < total; i += stride) {
@@ -143,9 +151,9 @@ extern "C" int fg_silu_mul(const void *gu, void *out, int dtype, int M, int F, c
     size_t want = (total + threads - 1) / threads;
     int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
     if (dtype == FG_F32)
-        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float *)gu, (float *)out, total, F);
+        return fg_launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float *)gu, (float *)out, total, F);
     else if (dtype == FG_BF16)
-        silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16 *)gu, (bf16 *)out, total, F);
+        return fg_launch(silu_mul_kernel<bf16>, dim3(blocks), dim3(threads), 0, stream, (const bf16 *)gu, (bf16 *)out, total, F);
     else return FG_ERR_BAD_DTYPE;
     return FG_LAUNCH_CHECK();
 }
@@ -155,6 +163,8 @@ extern "C" int fg_silu_mul(const void *gu, void *out, int dtype, int M, int F, c
 // becomes its next input, and live rows move on by one position.
 __global__ void decode_advance_kernel(int *__restrict__ tokens, int *__restrict__ positions,
                                       const int *__restrict__ next_tokens, const int *__restrict__ active, int B) {
+    pdl_launch_dependents();
+    pdl_wait();
     int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B) return;
     tokens[b] = next_tokens[b];
@@ -164,6 +174,5 @@ __global__ void decode_advance_kernel(int *__restrict__ tokens, int *__restrict_
 extern "C" int fg_decode_advance(int *tokens, int *positions, const int *next_tokens, const int *active, int B,
                                  cudaStream_t stream) {
     if (B <= 0) return 0;
-    decode_advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(tokens, positions, next_tokens, active, B);
-    return FG_LAUNCH_CHECK();
+    return fg_launch(decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, stream, tokens, positions, next_tokens, active, B);
 }

@@ -4,19 +4,23 @@
 // Role in the reference: matvec / matvec_multi / matmul (fastgguf.c:2575-2622, :2552-2573,
 // :3004-3093) - every projection of the decoder, for one token or a batch of prompt tokens.
 //
-// Shape of the kernel ("swap-AB"): the WEIGHT rows are the 128-row M operand of the MMA and the
-// token rows are its N operand (16..256), so the same kernel streams weights for a decode step of
-// 1..64 tokens and tiles a prefill of thousands.  One CTA computes a 128 (features) x BN (tokens)
-// tile; blockIdx.z splits K when there are too few tiles to fill the GPU (decode), the last CTA
-// of a tile then sums the partial tiles in split order (deterministic) and runs the epilogue.
+// One CTA computes a 128 x BN tile of the MMA: "P" rows are its M side (128), "Q" rows its N side.
+//   SWAP (decode, up to 64 tokens): P = weight rows, Q = token rows (BN = 16/32/64).  The kernel
+//     streams the weights once; blockIdx.z splits K when there are too few tiles to fill the GPU,
+//     and the CTA that finishes a tile last sums the partial tiles in split order (deterministic).
+//   not SWAP (prefill): P = 128 token rows, Q = BN = 128/256 weight rows; a thread of the epilogue
+//     owns one token row and writes runs of consecutive features with 16-byte stores.
 //
-//   warp 0      TMA producer   (one lane): K-blocks of 64 into a ring of smem stages, 128B swizzle
-//   warp 1      MMA issuer     (one lane): tcgen05.mma 128 x BN x 16, commit frees the stage
+//   warp 0      TMA producer (one lane): K-blocks of 64 into a ring of smem stages, 128B swizzle.
+//               The weight tiles of the first stages are fetched BEFORE the wait on the preceding
+//               kernel (weights are never written), so weight traffic overlaps that kernel's tail.
+//   warp 1      MMA issuer (one lane): tcgen05.mma 128 x BN x 16; its commit frees the stage.
 //   warps 2-5   epilogue: tcgen05.ld of the f32 tile, then one of
 //               store bf16 | store f32 | add into f32 (residual) | silu(gate) * up -> bf16
 //
-// The silu epilogue runs two accumulators: the gate rows and the up rows of the same features
-// are two A tiles against one B tile, so gate and up of a feature meet in one thread.
+// The silu epilogue expects the gate and up matrices interleaved in blocks of 64 rows
+// (g0..g63, u0..u63, g64..g127, ...): a 128-row weight tile then holds gate and up of the same
+// 64 features.
 //
 // Every wait on an mbarrier is bounded; when it runs out the kernel raises an error flag, waits
 // (bounded) for its own copies in flight, frees its tensor memory and returns.
@@ -26,7 +30,7 @@
 #define FG_ERR_PIPELINE 10003
 #define FG_ERR_TENSORMAP 10004
 
-#define BM 128          // weight rows per tile (MMA M)
+#define BM 128          // P rows per tile (MMA M)
 #define BK 64           // K elements per stage: 64 bf16 = one 128-byte swizzle row
 #define UMMA_K 16
 #define GEMM_THREADS 192
@@ -72,14 +76,17 @@ __device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t adesc, uin
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
 }
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
                  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
                    "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                  : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
 }
-__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows at 128 B, 8-row groups at 1024 B
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
@@ -98,24 +105,26 @@ __device__ __forceinline__ uint32_t make_idesc(int M, int N) {
 
 __device__ __forceinline__ void raise_error(int role) { atomicCAS(&g_gemm_error, 0, (FG_ERR_PIPELINE << 8) | role); }
 
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
 struct GemmArgs {
     void *out;            // [M, ldc] bf16 or f32 by epilogue
     float *ws;            // split-K partial tiles [splits, M, N] f32
     int *counters;        // split-K arrival counters, one per tile, zero between launches
-    int M, N, K;          // tokens, output features, reduction
+    int M, N, K;          // tokens, weight rows (2F for the silu epilogue), reduction
     int ldc;
-    int up_row_offset;    // EPI_SILU_MUL: first row of the up projection inside W (= F)
     int kb_per_split;     // K-blocks of 64 per split
+    int vec_ok;           // rows of `out` allow 16-byte accesses
 };
 
-template <int BN, int STAGES, int EPI>
+template <int BN, int STAGES, int EPI, bool SWAP>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmArgs a) {
-    constexpr bool DUAL = EPI == EPI_SILU_MUL;
-    constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-    constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + B_BYTES;
-    constexpr int TMEM_NEED = (DUAL ? 2 : 1) * BN;
-    constexpr int TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, GemmArgs a) {
+    constexpr int P_BYTES = BM * BK * 2, Q_BYTES = BN * BK * 2;
+    constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
+    constexpr int TMEM_COLS = BN <= 32 ? 32 : BN;
+    // which part of a stage holds weights: they are fetched before the wait on the previous kernel
+    constexpr int W_OFF = SWAP ? 0 : P_BYTES, X_OFF = SWAP ? P_BYTES : 0;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms need 1 KB alignment
@@ -124,12 +133,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     __shared__ int s_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN;
+    const int p0 = blockIdx.x * BM, q0 = blockIdx.y * BN;
     const int total_kb = (a.K + BK - 1) / BK;
     const int kb0 = blockIdx.z * a.kb_per_split;
     const int nkb = min(a.kb_per_split, total_kb - kb0);
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), tfull = smem_u32(&bars[2 * STAGES]);
     const uint32_t smem0 = smem_u32(smem);
+    const CUtensorMap *tmW = SWAP ? &tmP : &tmQ, *tmX = SWAP ? &tmQ : &tmP;
+    const int w_row = SWAP ? p0 : q0, x_row = SWAP ? q0 : p0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -145,23 +156,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
+    pdl_launch_dependents();
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            bool ok = true;
-            int issued = 0;
-            for (int kb = 0; kb < nkb && ok; kb++) {
+            const int pre = min(STAGES, nkb);
+            for (int kb = 0; kb < pre; kb++) {             // weights of the first stages: no dependency
+                mbar_expect_tx(full0 + 8 * kb, STAGE_BYTES);
+                tma_load_2d(smem0 + kb * STAGE_BYTES + W_OFF, tmW, (kb0 + kb) * BK, w_row, full0 + 8 * kb);
+            }
+            pdl_wait();                                    // activations come from the kernel before
+            for (int kb = 0; kb < pre; kb++)
+                tma_load_2d(smem0 + kb * STAGE_BYTES + X_OFF, tmX, (kb0 + kb) * BK, x_row, full0 + 8 * kb);
+            int issued = pre;
+            for (int kb = pre; kb < nkb; kb++) {
                 int s = kb % STAGES;
-                uint32_t ph = (kb / STAGES) & 1;
-                ok = mbar_wait(empty0 + 8 * s, ph ^ 1);
-                if (!ok) { raise_error(1); break; }
+                if (!mbar_wait(empty0 + 8 * s, ((kb / STAGES) & 1) ^ 1)) { raise_error(1); break; }
                 uint32_t dst = smem0 + s * STAGE_BYTES, bar = full0 + 8 * s;
                 mbar_expect_tx(bar, STAGE_BYTES);
-                int kx = (kb0 + kb) * BK;
-                tma_load_2d(dst, &tmW, kx, n0, bar);
-                if (DUAL) tma_load_2d(dst + A_BYTES, &tmW, kx, a.up_row_offset + n0, bar);
-                tma_load_2d(dst + (DUAL ? 2 : 1) * A_BYTES, &tmX, kx, m0, bar);
+                tma_load_2d(dst + W_OFF, tmW, (kb0 + kb) * BK, w_row, bar);
+                tma_load_2d(dst + X_OFF, tmX, (kb0 + kb) * BK, x_row, bar);
                 issued = kb + 1;
             }
             // copies still in flight must land before the CTA may exit
@@ -177,13 +192,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 if (!mbar_wait(full0 + 8 * s, (kb / STAGES) & 1)) { raise_error(2); break; }
                 tc_fence_after();
                 uint32_t sa = smem0 + s * STAGE_BYTES;
-                uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sa + (DUAL ? 2 : 1) * A_BYTES);
+                uint64_t pdesc = make_smem_desc(sa), qdesc = make_smem_desc(sa + P_BYTES);
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; k++) {
-                    uint32_t acc = (kb | k) != 0;
                     uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);     // advance inside the swizzle row
-                    tc_mma_bf16(tmem_base, adesc + koff, bdesc + koff, idesc, acc);
-                    if (DUAL) tc_mma_bf16(tmem_base + BN, make_smem_desc(sa + A_BYTES) + koff, bdesc + koff, idesc, acc);
+                    tc_mma_bf16(tmem_base, pdesc + koff, qdesc + koff, idesc, (kb | k) != 0);
                 }
                 tc_commit(empty0 + 8 * s);        // arrives when these MMAs have read the stage
             }
@@ -191,78 +204,168 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
+        pdl_wait();
         const int lg = warp & 3;                  // the TMEM lane group this warp may read
-        const int n = n0 + lg * 32 + lane;        // output feature of this thread
-        const bool n_ok = n < a.N;
+        const int prow = lg * 32 + lane;          // row of the tile this thread owns
         bool ok = nkb > 0 ? mbar_wait(tfull, 0) : true;
         if (!ok) raise_error(3);
         tc_fence_after();
         const uint32_t trow = tmem_base + ((uint32_t)(lg * 32) << 16);
-        const int splits = gridDim.z;
-        bool last = true;
-        if (splits > 1) {
-            // partial tile -> workspace; the CTA that arrives last sums all splits in order
-            if (ok) {
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    uint32_t r[16];
-                    tc_ld16(trow + c0, r);
-                    tc_ld_wait();
+        if (SWAP) {
+            // thread = weight row (feature), columns = tokens
+            const int n = p0 + prow;
+            const bool n_ok = n < a.N;
+            const int splits = gridDim.z;
+            if (EPI == EPI_SILU_MUL) {
+                // rows 0..63 of the tile are gate, 64..127 up of the same 64 features: meet through smem
+                float *ex = (float *)smem;        // [64][BN]; the stages are idle once tfull has fired
+                if (ok && prow >= 64) {
+                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                        float v[16];
+                        tc_ld16(trow + c0, v);
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        int m = m0 + c0 + j;
-                        if (n_ok && m < a.M)
-                            a.ws[((size_t)blockIdx.z * a.M + m) * a.N + n] = nkb > 0 ? __uint_as_float(r[j]) : 0.f;
+                        for (int j = 0; j < 16; j++) ex[(prow - 64) * BN + c0 + j] = v[j];
                     }
                 }
-            }
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (threadIdx.x == 64) {
-                int tile = blockIdx.y * gridDim.x + blockIdx.x;
-                int old = atomicAdd(&a.counters[tile], 1);
-                s_flag = old == splits - 1;
-                if (old == splits - 1) a.counters[tile] = 0;      // ready for the next launch
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            last = s_flag != 0;
-            if (last) __threadfence();
-        }
-        if (last && ok) {
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                float v[16], u[16];
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int f = (p0 >> 1) + prow;
+                if (ok && prow < 64) {
+                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                        float v[16];
+                        tc_ld16(trow + c0, v);
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            int m = q0 + c0 + j;
+                            if (m < a.M && f < (a.N >> 1))
+                                ((bf16 *)a.out)[(size_t)m * a.ldc + f] = __float2bfloat16_rn(silu_mul(v[j], ex[prow * BN + c0 + j]));
+                        }
+                    }
+                }
+            } else {
+                bool last = true;
                 if (splits > 1) {
+                    // partial tile -> workspace; the CTA that arrives last sums all splits in order
+                    if (ok) {
+                        for (int c0 = 0; c0 < BN; c0 += 16) {
+                            float v[16];
+                            tc_ld16(trow + c0, v);
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        int m = m0 + c0 + j;
-                        float s = 0.f;
-                        if (n_ok && m < a.M)
-                            for (int z = 0; z < splits; z++) s += __ldcg(&a.ws[((size_t)z * a.M + m) * a.N + n]);
-                        v[j] = s;
+                            for (int j = 0; j < 16; j++) {
+                                int m = q0 + c0 + j;
+                                if (n_ok && m < a.M) a.ws[((size_t)blockIdx.z * a.M + m) * a.N + n] = v[j];
+                            }
+                        }
                     }
-                } else {
-                    uint32_t r[16];
-                    tc_ld16(trow + c0, r);
-                    if (DUAL) {
-                        uint32_t r2[16];
-                        tc_ld16(trow + BN + c0, r2);
-                        tc_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 16; j++) u[j] = __uint_as_float(r2[j]);
-                    } else tc_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 16; j++) v[j] = nkb > 0 ? __uint_as_float(r[j]) : 0.f;
+                    __threadfence();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (threadIdx.x == 64) {
+                        int tile = blockIdx.y * gridDim.x + blockIdx.x;
+                        int old = atomicAdd(&a.counters[tile], 1);
+                        s_flag = old == splits - 1;
+                        if (old == splits - 1) a.counters[tile] = 0;      // ready for the next launch
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    last = s_flag != 0;
+                    if (last) __threadfence();
                 }
+                if (last && ok) {
+                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                        float v[16];
+                        if (splits > 1) {
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    int m = m0 + c0 + j;
-                    if (!n_ok || m >= a.M) continue;
-                    size_t idx = (size_t)m * a.ldc + n;
-                    if (EPI == EPI_BF16) ((bf16 *)a.out)[idx] = __float2bfloat16_rn(v[j]);
-                    else if (EPI == EPI_F32) ((float *)a.out)[idx] = v[j];
-                    else if (EPI == EPI_ADD_F32) ((float *)a.out)[idx] += v[j];
-                    else {
-                        float g = v[j];
-                        ((bf16 *)a.out)[idx] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u[j]);
+                            for (int j = 0; j < 16; j++) v[j] = 0.f;
+                            for (int z = 0; z < splits; z++) {
+#pragma unroll
+                                for (int j = 0; j < 16; j++) {
+                                    int m = q0 + c0 + j;
+                                    if (n_ok && m < a.M) v[j] += __ldcg(&a.ws[((size_t)z * a.M + m) * a.N + n]);
+                                }
+                            }
+                        } else {
+                            tc_ld16(trow + c0, v);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            int m = q0 + c0 + j;
+                            if (!n_ok || m >= a.M) continue;
+                            size_t idx = (size_t)m * a.ldc + n;
+                            if (EPI == EPI_BF16) ((bf16 *)a.out)[idx] = __float2bfloat16_rn(v[j]);
+                            else if (EPI == EPI_F32) ((float *)a.out)[idx] = v[j];
+                            else ((float *)a.out)[idx] += v[j];
+                        }
+                    }
+                }
+            }
+        } else if (ok) {
+            // thread = token row, columns = weight rows (features): runs of 16 consecutive outputs
+            const int m = p0 + prow;
+            const bool m_ok = m < a.M;
+            if (EPI == EPI_SILU_MUL) {
+                const int F = a.N >> 1;
+                for (int blk = 0; blk < BN / 128; blk++) {
+                    for (int c0 = 0; c0 < 64; c0 += 16) {
+                        float g[16], u[16];
+                        tc_ld16(trow + blk * 128 + c0, g);
+                        tc_ld16(trow + blk * 128 + 64 + c0, u);
+                        const int f0 = ((q0 + blk * 128) >> 1) + c0;
+                        if (!m_ok || f0 >= F) continue;
+                        bf16 *dst = (bf16 *)a.out + (size_t)m * a.ldc + f0;
+                        if (a.vec_ok && f0 + 16 <= F) {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int j = 0; j < 8; j++) {
+                                __nv_bfloat162 t = __floats2bfloat162_rn(silu_mul(g[2 * j], u[2 * j]), silu_mul(g[2 * j + 1], u[2 * j + 1]));
+                                w[j] = *(uint32_t *)&t;
+                            }
+                            ((uint4 *)dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                            ((uint4 *)dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; j++)
+                                if (f0 + j < F) dst[j] = __float2bfloat16_rn(silu_mul(g[j], u[j]));
+                        }
+                    }
+                }
+            } else {
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
+                    tc_ld16(trow + c0, v);
+                    const int n0 = q0 + c0;
+                    if (!m_ok || n0 >= a.N) continue;
+                    const size_t idx = (size_t)m * a.ldc + n0;
+                    const bool full = a.vec_ok && n0 + 16 <= a.N;
+                    if (EPI == EPI_BF16) {
+                        bf16 *dst = (bf16 *)a.out + idx;
+                        if (full) {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int j = 0; j < 8; j++) {
+                                __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                                w[j] = *(uint32_t *)&t;
+                            }
+                            ((uint4 *)dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                            ((uint4 *)dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; j++) if (n0 + j < a.N) dst[j] = __float2bfloat16_rn(v[j]);
+                        }
+                    } else {
+                        float *dst = (float *)a.out + idx;
+                        if (full) {
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                float4 t = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                                if (EPI == EPI_ADD_F32) {
+                                    float4 o = ((float4 *)dst)[j];
+                                    t.x += o.x; t.y += o.y; t.z += o.z; t.w += o.w;
+                                }
+                                ((float4 *)dst)[j] = t;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; j++)
+                                if (n0 + j < a.N) dst[j] = EPI == EPI_ADD_F32 ? dst[j] + v[j] : v[j];
+                        }
                     }
                 }
             }
@@ -307,30 +410,31 @@ static int make_map(CUtensorMap *map, const void *base, int rows, int K, int ld,
     return r == CUDA_SUCCESS ? 0 : FG_ERR_TENSORMAP;
 }
 
-template <int BN, int STAGES, int EPI>
-static int launch(const CUtensorMap &tmW, const CUtensorMap &tmX, const GemmArgs &a, int splits, cudaStream_t stream) {
-    constexpr int stage = ((EPI == EPI_SILU_MUL ? 2 : 1) * BM + BN) * BK * 2;
-    constexpr int smem = STAGES * stage + 1024;
+template <int BN, int STAGES, int EPI, bool SWAP>
+static int launch(const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs &a, dim3 grid, cudaStream_t stream) {
+    constexpr int smem = STAGES * (BM + BN) * BK * 2 + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid((a.N + BM - 1) / BM, (a.M + BN - 1) / BN, splits);
-    gemm_tc_kernel<BN, STAGES, EPI><<<grid, GEMM_THREADS, smem, stream>>>(tmW, tmX, a);
-    return FG_LAUNCH_CHECK();
+    return fg_launch(gemm_tc_kernel<BN, STAGES, EPI, SWAP>, grid, dim3(GEMM_THREADS), (size_t)smem, stream, tmP, tmQ, a);
 }
 
 template <int EPI>
-static int dispatch_bn(int bn, const CUtensorMap &tmW, const CUtensorMap &tmX, const GemmArgs &a, int splits, cudaStream_t st) {
-    constexpr bool D = EPI == EPI_SILU_MUL;
-    switch (bn) {
-    case 16: return launch<16, D ? 5 : 8, EPI>(tmW, tmX, a, splits, st);
-    case 32: return launch<32, D ? 5 : 8, EPI>(tmW, tmX, a, splits, st);
-    case 64: return launch<64, D ? 5 : 8, EPI>(tmW, tmX, a, splits, st);
-    case 128: return launch<128, D ? 4 : 6, EPI>(tmW, tmX, a, splits, st);
-    case 256: return launch<256, D ? 3 : 4, EPI>(tmW, tmX, a, splits, st);
+static int dispatch(bool swap, int bn, const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs &a, dim3 grid, cudaStream_t st) {
+    if (swap) {
+        switch (bn) {
+        case 16: return launch<16, 8, EPI, true>(tmP, tmQ, a, grid, st);
+        case 32: return launch<32, 8, EPI, true>(tmP, tmQ, a, grid, st);
+        case 64: return launch<64, 7, EPI, true>(tmP, tmQ, a, grid, st);
+        }
+    } else {
+        switch (bn) {
+        case 128: return launch<128, 6, EPI, false>(tmP, tmQ, a, grid, st);
+        case 256: return launch<256, 4, EPI, false>(tmP, tmQ, a, grid, st);
+        }
     }
     return FG_ERR_BAD_SIZE;
 }
@@ -340,40 +444,53 @@ extern "C" long long fg_gemm_tc_workspace_floats(void) { return 8ll * 64 * 8192;
 extern "C" int fg_gemm_tc_counter_count(void) { return 4096; }
 
 // X: [M, K] bf16 (row stride ldx), W: [N, K] bf16 (row stride ldw); epi as the enum above.
-// EPI_SILU_MUL: W holds gate rows [0, N) and up rows [up_row_offset, up_row_offset + N); out is [M, N] bf16.
+// EPI_SILU_MUL: W is [N = 2F, K] with gate and up interleaved in blocks of 64 rows; out is [M, F] bf16.
 // Returns FG_ERR_BAD_SIZE for shapes TMA cannot describe (K % 8, unaligned bases): the caller
 // then uses the plain kernel.
 extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *out, int ldc, int epi,
-                          int M, int N, int K, int w_rows_total, int up_row_offset, float *ws, int *counters,
-                          int force_splits, cudaStream_t stream) {
+                          int M, int N, int K, float *ws, int *counters, int force_splits, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return FG_ERR_BAD_SIZE;
-    int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-    int total_kb = (K + BK - 1) / BK;
-    int tiles = ((N + BM - 1) / BM) * ((M + bn - 1) / bn);
-    int splits = 1;
-    if (epi != EPI_SILU_MUL && ws && counters && tiles <= 74 && tiles <= fg_gemm_tc_counter_count()) {
-        splits = (148 + tiles - 1) / tiles;
-        if (splits > 8) splits = 8;
-        if (splits > total_kb / 2) splits = total_kb / 2 > 0 ? total_kb / 2 : 1;
+    if (epi == EPI_SILU_MUL && N % 128) return FG_ERR_BAD_SIZE;
+    const bool swap = M <= 64;
+    const int total_kb = (K + BK - 1) / BK;
+    int bn, splits = 1;
+    dim3 grid;
+    if (swap) {
+        bn = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+        int tiles = (N + BM - 1) / BM;
+        bool can_split = epi != EPI_SILU_MUL && ws && counters && tiles <= fg_gemm_tc_counter_count();
+        if (can_split && tiles <= 74) {
+            splits = (148 + tiles - 1) / tiles;
+            if (splits > 8) splits = 8;
+            if (splits > total_kb / 2) splits = total_kb / 2 > 0 ? total_kb / 2 : 1;
+        }
+        if (can_split && force_splits > 0 && force_splits <= total_kb) splits = force_splits;
         if ((long long)splits * M * N > fg_gemm_tc_workspace_floats()) splits = 1;
+        grid = dim3(tiles, 1, 1);
+    } else {
+        int pt = (M + BM - 1) / BM;
+        long long t256 = (long long)pt * ((N + 255) / 256), t128 = (long long)pt * ((N + 127) / 128);
+        double c256 = (double)((t256 + 147) / 148), c128 = 0.55 * (double)((t128 + 147) / 148);
+        bn = (N <= 128 || c128 < c256) ? 128 : 256;
+        grid = dim3(pt, (N + bn - 1) / bn, 1);
     }
-    if (force_splits > 0 && epi != EPI_SILU_MUL && ws && counters && force_splits <= total_kb &&
-        (long long)force_splits * M * N <= fg_gemm_tc_workspace_floats() && tiles <= fg_gemm_tc_counter_count())
-        splits = force_splits;
     int kb_per_split = (total_kb + splits - 1) / splits;
     splits = (total_kb + kb_per_split - 1) / kb_per_split;      // no empty split
-    CUtensorMap tmW, tmX;
-    int e = make_map(&tmW, W, w_rows_total, K, ldw, BM);
+    grid.z = splits;
+    CUtensorMap tmP, tmQ;
+    int e = swap ? make_map(&tmP, W, N, K, ldw, BM) : make_map(&tmP, X, M, K, ldx, BM);
     if (e) return e;
-    e = make_map(&tmX, X, M, K, ldx, bn);
+    e = swap ? make_map(&tmQ, X, M, K, ldx, bn) : make_map(&tmQ, W, N, K, ldw, bn);
     if (e) return e;
-    GemmArgs a{out, ws, counters, M, N, K, ldc, up_row_offset, kb_per_split};
+    int esz = (epi == EPI_F32 || epi == EPI_ADD_F32) ? 4 : 2;
+    int vec_ok = ((uintptr_t)out % 16 == 0) && ((size_t)ldc * esz % 16 == 0);
+    GemmArgs a{out, ws, counters, M, N, K, ldc, kb_per_split, vec_ok};
     switch (epi) {
-    case EPI_BF16: return dispatch_bn<EPI_BF16>(bn, tmW, tmX, a, splits, stream);
-    case EPI_F32: return dispatch_bn<EPI_F32>(bn, tmW, tmX, a, splits, stream);
-    case EPI_ADD_F32: return dispatch_bn<EPI_ADD_F32>(bn, tmW, tmX, a, splits, stream);
-    case EPI_SILU_MUL: return dispatch_bn<EPI_SILU_MUL>(bn, tmW, tmX, a, splits, stream);
+    case EPI_BF16: return dispatch<EPI_BF16>(swap, bn, tmP, tmQ, a, grid, stream);
+    case EPI_F32: return dispatch<EPI_F32>(swap, bn, tmP, tmQ, a, grid, stream);
+    case EPI_ADD_F32: return dispatch<EPI_ADD_F32>(swap, bn, tmP, tmQ, a, grid, stream);
+    case EPI_SILU_MUL: return dispatch<EPI_SILU_MUL>(swap, bn, tmP, tmQ, a, grid, stream);
     }
     return FG_ERR_BAD_DTYPE;
 }

@@ -22,7 +22,7 @@ EPI_BF16, EPI_F32, EPI_ADD_F32, EPI_SILU_MUL = 0, 1, 2, 3
 _BAD_SIZE = 10002
 
 register_signatures("tc", {
-    "fg_gemm_tc": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+    "fg_gemm_tc": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                    c_void_p, c_void_p, c_int, c_void_p],
     "fg_gemm_tc_error": [],
     "fg_gemm_tc_counter_count": [],
@@ -51,12 +51,12 @@ def pipeline_error() -> int:
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
-            out_dtype: Optional[torch.dtype] = None, accumulate: bool = False, silu_rows: Optional[int] = None,
+            out_dtype: Optional[torch.dtype] = None, accumulate: bool = False, silu: bool = False,
             force_splits: int = 0) -> Optional[torch.Tensor]:
     """out[m, n] (+)= sum_k a[m, k] w[n, k] on the tensor cores; None if the sizes are refused.
 
-    ``silu_rows=F``: ``w`` is [2F, K] (gate rows then up rows) and the result is
-    ``silu(a gate^T) * (a up^T)`` as bfloat16 [M, F].
+    ``silu=True``: ``w`` is [2F, K] with gate and up interleaved in blocks of 64 rows (see
+    ``interleave_gate_up``) and the result is ``silu(a gate^T) * (a up^T)`` as bfloat16 [M, F].
     """
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_tc takes bfloat16 operands")
@@ -66,12 +66,12 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = N
         raise KernelError(f"gemm_tc: a is [{M}, {K}] but w is [{rows}, {K2}]")
     if a.stride(1) != 1 or w.stride(1) != 1:
         raise KernelError("gemm_tc: the reduction dimension must be contiguous in both operands")
-    if silu_rows is not None:
-        N, epi, dt, up = silu_rows, EPI_SILU_MUL, torch.bfloat16, silu_rows
-        if rows != 2 * silu_rows or accumulate:
-            raise KernelError("gemm_tc: the silu epilogue needs w = [2F, K] and no accumulation")
+    if silu:
+        N, epi, dt = rows // 2, EPI_SILU_MUL, torch.bfloat16
+        if rows % 128 or accumulate:
+            raise KernelError("gemm_tc: the silu epilogue needs w = [2F, K] with F a multiple of 64, and no accumulation")
     else:
-        N, up = rows, 0
+        N = rows
         if accumulate:
             epi, dt = EPI_ADD_F32, torch.float32
         else:
@@ -90,7 +90,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = N
         raise KernelError(f"gemm_tc: out must be [{M}, {N}] {dt} with contiguous rows")
     ws, counters = _workspace(a.device)
     code = lib("tc").fg_gemm_tc(ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out.stride(0), epi,
-                                M, N, K, rows, up, ptr(ws), ptr(counters), int(force_splits), stream())
+                                M, rows, K, ptr(ws), ptr(counters), int(force_splits), stream())
     if code == _BAD_SIZE:
         return None
     check(code, "gemm_tc")
@@ -105,8 +105,16 @@ class _Plan:
     def run(self, a, out=None, out_dtype=None, accumulate=False):
         return gemm_tc(a, self.weight, out=out, out_dtype=out_dtype, accumulate=accumulate)
 
-    def run_silu(self, a, d_ff: int):
-        return gemm_tc(a, self.weight, silu_rows=d_ff)
+    def run_silu(self, a):
+        return gemm_tc(a, self.weight, silu=True)
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[2F, K]: blocks of 64 gate rows followed by the 64 up rows of the same features."""
+    F, K = gate.shape
+    if F % 64:
+        raise KernelError("interleave_gate_up: the feed-forward width must be a multiple of 64")
+    return torch.stack([gate.view(F // 64, 64, K), up.view(F // 64, 64, K)], dim=1).reshape(2 * F, K).contiguous()
 
 
 def plan_for_weight(weight: torch.Tensor) -> Optional[_Plan]:

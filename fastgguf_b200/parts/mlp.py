@@ -32,14 +32,21 @@ class SwiGLU(FeedForward):
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
         dt = g.dtype if g.dtype == u.dtype else torch.float32
-        self.gate_up = Linear(torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous())
+        self.fused = None
+        if dt == torch.bfloat16 and g.is_cuda and self.d_ff % 64 == 0 and self.hidden_size % 8 == 0:
+            from ..ops import fast_gemm
+            # gate, up and SiLU-mul in one tensor-core kernel: rows interleaved in blocks of 64
+            self.fused = fast_gemm.plan_for_weight(fast_gemm.interleave_gate_up(g, u))
+        if self.fused is None:
+            self.gate_up = Linear(torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous())
         self.down = Linear(tensors["down_proj.weight"].contiguous())
 
     def forward(self, xn: torch.Tensor, batch, residual: torch.Tensor) -> None:
-        t = None
-        if self.gate_up._fast is not None and xn.dtype == torch.bfloat16:
-            t = self.gate_up._fast.run_silu(xn, self.d_ff)      # gate, up and SiLU-mul in one kernel
-        if t is None:
+        if self.fused is not None:
+            t = self.fused.run_silu(xn)
+            if t is None:
+                raise ops.KernelError("the fused gate/up kernel refused a shape it was planned for")
+        else:
             t = ops.silu_mul(self.gate_up.forward(xn, out_dtype=self.runtime.dtype))
         self.down.forward(t, out=residual, accumulate=True)
 

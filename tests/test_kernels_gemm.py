@@ -73,14 +73,14 @@ def test_gemm_tc_split_k(M, N, K, splits):
 
 
 @pytest.mark.parametrize("M", [1, 9, 64, 130, 513])
-@pytest.mark.parametrize("F,K", [(192, 64), (200, 72), (640, 2048)])
+@pytest.mark.parametrize("F,K", [(192, 64), (320, 72), (640, 2048)])
 def test_gemm_tc_silu(M, F, K):
     from fastgguf_b200.ops import fast_gemm
     a, w = _operands(M, 2 * F, K, torch.bfloat16, 4)
     g = a.double() @ w[:F].double().T
     u = a.double() @ w[F:].double().T
     want = g / (1 + torch.exp(-g)) * u
-    got = fast_gemm.gemm_tc(a, w, silu_rows=F)
+    got = fast_gemm.gemm_tc(a, fast_gemm.interleave_gate_up(w[:F], w[F:]), silu=True)
     assert got is not None and got.dtype == torch.bfloat16
     bound = (a.double().abs() @ w.double().abs().T).max().item()
     err = (got.double() - want).abs().max().item()
