@@ -99,3 +99,26 @@ static inline int fg_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     cfg.numAttrs = fg_pdl_enabled() ? 1 : 0;
     return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
+
+// the same, for a thread-block cluster of (1, 1, cluster_z) CTAs
+template <typename... KArgs, typename... Args>
+static inline int fg_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    int cluster_z, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (fg_pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
+    if (cluster_z > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1; attr[n].val.clusterDim.y = 1; attr[n].val.clusterDim.z = cluster_z;
+        n++;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

@@ -6,8 +6,9 @@
 //
 // One CTA computes a 128 x BN tile of the MMA: "P" rows are its M side (128), "Q" rows its N side.
 //   SWAP (decode, up to 64 tokens): P = weight rows, Q = token rows (BN = 16/32/64).  The kernel
-//     streams the weights once; blockIdx.z splits K when there are too few tiles to fill the GPU,
-//     and the CTA that finishes a tile last sums the partial tiles in split order (deterministic).
+//     streams the weights once; when there are too few tiles to fill the GPU, a thread-block
+//     cluster of 2/4/8 CTAs splits K, and the CTAs sum their partial tiles in rank order
+//     (deterministic) through distributed shared memory - no scratch in global memory.
 //   not SWAP (prefill): P = 128 token rows, Q = BN = 128/256 weight rows; a thread of the epilogue
 //     owns one token row and writes runs of consecutive features with 16-byte stores.
 //
@@ -105,12 +106,24 @@ __device__ __forceinline__ uint32_t make_idesc(int M, int N) {
 
 __device__ __forceinline__ void raise_error(int role) { atomicCAS(&g_gemm_error, 0, (FG_ERR_PIPELINE << 8) | role); }
 
+// all threads of all CTAs of the cluster; release/acquire so that shared-memory writes are seen remotely
+__device__ __forceinline__ void cluster_sync() {
+    __syncwarp();                                 // lanes that skipped a single-lane role rejoin first
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// read a float at the same shared-memory offset in the CTA of rank `rank` of this cluster
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, int rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
 struct GemmArgs {
     void *out;            // [M, ldc] bf16 or f32 by epilogue
-    float *ws;            // split-K partial tiles [splits, M, N] f32
-    int *counters;        // split-K arrival counters, one per tile, zero between launches
     int M, N, K;          // tokens, weight rows (2F for the silu epilogue), reduction
     int ldc;
     int kb_per_split;     // K-blocks of 64 per split
@@ -130,7 +143,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms need 1 KB alignment
     __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
     __shared__ uint32_t tmem_base_s;
-    __shared__ int s_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int p0 = blockIdx.x * BM, q0 = blockIdx.y * BN;
@@ -241,58 +253,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                         }
                     }
                 }
-            } else {
-                bool last = true;
-                if (splits > 1) {
-                    // partial tile -> workspace; the CTA that arrives last sums all splits in order
-                    if (ok) {
-                        for (int c0 = 0; c0 < BN; c0 += 16) {
-                            float v[16];
-                            tc_ld16(trow + c0, v);
-#pragma unroll
-                            for (int j = 0; j < 16; j++) {
-                                int m = q0 + c0 + j;
-                                if (n_ok && m < a.M) a.ws[((size_t)blockIdx.z * a.M + m) * a.N + n] = v[j];
-                            }
-                        }
-                    }
-                    __threadfence();
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    if (threadIdx.x == 64) {
-                        int tile = blockIdx.y * gridDim.x + blockIdx.x;
-                        int old = atomicAdd(&a.counters[tile], 1);
-                        s_flag = old == splits - 1;
-                        if (old == splits - 1) a.counters[tile] = 0;      // ready for the next launch
-                    }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    last = s_flag != 0;
-                    if (last) __threadfence();
-                }
-                if (last && ok) {
+            } else if (splits > 1) {
+                // partial tile -> own shared memory, column-major so that a warp touches consecutive words;
+                // the cluster then sums the partials of its CTAs (below)
+                float *part = (float *)smem;      // [BN][128]; the stages are idle once tfull has fired
+                if (ok) {
                     for (int c0 = 0; c0 < BN; c0 += 16) {
                         float v[16];
-                        if (splits > 1) {
+                        tc_ld16(trow + c0, v);
 #pragma unroll
-                            for (int j = 0; j < 16; j++) v[j] = 0.f;
-                            for (int z = 0; z < splits; z++) {
+                        for (int j = 0; j < 16; j++) part[(c0 + j) * BM + prow] = nkb > 0 ? v[j] : 0.f;
+                    }
+                }
+            } else if (ok) {
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
+                    tc_ld16(trow + c0, v);
 #pragma unroll
-                                for (int j = 0; j < 16; j++) {
-                                    int m = q0 + c0 + j;
-                                    if (n_ok && m < a.M) v[j] += __ldcg(&a.ws[((size_t)z * a.M + m) * a.N + n]);
-                                }
-                            }
-                        } else {
-                            tc_ld16(trow + c0, v);
-                        }
-#pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            int m = q0 + c0 + j;
-                            if (!n_ok || m >= a.M) continue;
-                            size_t idx = (size_t)m * a.ldc + n;
-                            if (EPI == EPI_BF16) ((bf16 *)a.out)[idx] = __float2bfloat16_rn(v[j]);
-                            else if (EPI == EPI_F32) ((float *)a.out)[idx] = v[j];
-                            else ((float *)a.out)[idx] += v[j];
-                        }
+                    for (int j = 0; j < 16; j++) {
+                        int m = q0 + c0 + j;
+                        if (!n_ok || m >= a.M) continue;
+                        size_t idx = (size_t)m * a.ldc + n;
+                        if (EPI == EPI_BF16) ((bf16 *)a.out)[idx] = __float2bfloat16_rn(v[j]);
+                        else if (EPI == EPI_F32) ((float *)a.out)[idx] = v[j];
+                        else ((float *)a.out)[idx] += v[j];
                     }
                 }
             }
@@ -372,6 +356,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         }
         tc_fence_before();
     }
+    if (SWAP && EPI != EPI_SILU_MUL && gridDim.z > 1) {
+        // ---- split-K: the CTAs of a cluster hold partial tiles of the same outputs in their shared
+        // memory; CTA r sums columns [r * BN / S, (r + 1) * BN / S) over all CTAs in rank order
+        // (deterministic) through distributed shared memory and runs the epilogue on them
+        const int S = gridDim.z;
+        cluster_sync();
+        if (warp >= 2) {
+            const int prow = (warp & 3) * 32 + lane, n = p0 + prow;
+            const float *part = (const float *)smem;
+            const int per = BN / S, c_begin = blockIdx.z * per;
+            for (int c = c_begin; c < c_begin + per; c++) {
+                float v = 0.f;
+                uint32_t local = smem_u32(&part[c * BM + prow]);
+                for (int z = 0; z < S; z++) v += ld_dsmem_f32(local, z);
+                int m = q0 + c;
+                if (n < a.N && m < a.M) {
+                    size_t idx = (size_t)m * a.ldc + n;
+                    if (EPI == EPI_BF16) ((bf16 *)a.out)[idx] = __float2bfloat16_rn(v);
+                    else if (EPI == EPI_F32) ((float *)a.out)[idx] = v;
+                    else ((float *)a.out)[idx] += v;
+                }
+            }
+        }
+        cluster_sync();                           // no CTA leaves while its partial is still being read
+    }
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
@@ -419,7 +428,8 @@ static int launch(const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return fg_launch(gemm_tc_kernel<BN, STAGES, EPI, SWAP>, grid, dim3(GEMM_THREADS), (size_t)smem, stream, tmP, tmQ, a);
+    return fg_launch_cluster(gemm_tc_kernel<BN, STAGES, EPI, SWAP>, grid, dim3(GEMM_THREADS), (size_t)smem, stream,
+                             (int)grid.z, tmP, tmQ, a);
 }
 
 template <int EPI>
@@ -439,16 +449,12 @@ static int dispatch(bool swap, int bn, const CUtensorMap &tmP, const CUtensorMap
     return FG_ERR_BAD_SIZE;
 }
 
-// Largest workspace (floats) and counter count any call may need: callers allocate once.
-extern "C" long long fg_gemm_tc_workspace_floats(void) { return 8ll * 64 * 8192; }
-extern "C" int fg_gemm_tc_counter_count(void) { return 4096; }
-
 // X: [M, K] bf16 (row stride ldx), W: [N, K] bf16 (row stride ldw); epi as the enum above.
 // EPI_SILU_MUL: W is [N = 2F, K] with gate and up interleaved in blocks of 64 rows; out is [M, F] bf16.
 // Returns FG_ERR_BAD_SIZE for shapes TMA cannot describe (K % 8, unaligned bases): the caller
 // then uses the plain kernel.
 extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *out, int ldc, int epi,
-                          int M, int N, int K, float *ws, int *counters, int force_splits, cudaStream_t stream) {
+                          int M, int N, int K, int force_splits, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return FG_ERR_BAD_SIZE;
     if (epi == EPI_SILU_MUL && N % 128) return FG_ERR_BAD_SIZE;
@@ -459,14 +465,12 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
     if (swap) {
         bn = M <= 16 ? 16 : M <= 32 ? 32 : 64;
         int tiles = (N + BM - 1) / BM;
-        bool can_split = epi != EPI_SILU_MUL && ws && counters && tiles <= fg_gemm_tc_counter_count();
-        if (can_split && tiles <= 74) {
-            splits = (148 + tiles - 1) / tiles;
-            if (splits > 8) splits = 8;
-            if (splits > total_kb / 2) splits = total_kb / 2 > 0 ? total_kb / 2 : 1;
+        // too few tiles to fill 148 SMs: a cluster of 2, 4 or 8 CTAs shares each tile along K
+        if (epi != EPI_SILU_MUL) {
+            while (splits < 8 && tiles * splits < 120 && total_kb >= 4 * splits) splits *= 2;
+            if (force_splits == 1 || force_splits == 2 || force_splits == 4 || force_splits == 8)
+                if (force_splits <= total_kb) splits = force_splits;
         }
-        if (can_split && force_splits > 0 && force_splits <= total_kb) splits = force_splits;
-        if ((long long)splits * M * N > fg_gemm_tc_workspace_floats()) splits = 1;
         grid = dim3(tiles, 1, 1);
     } else {
         int pt = (M + BM - 1) / BM;
@@ -475,8 +479,7 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
         bn = (N <= 128 || c128 < c256) ? 128 : 256;
         grid = dim3(pt, (N + bn - 1) / bn, 1);
     }
-    int kb_per_split = (total_kb + splits - 1) / splits;
-    splits = (total_kb + kb_per_split - 1) / kb_per_split;      // no empty split
+    int kb_per_split = (total_kb + splits - 1) / splits;       // a split may be empty: it adds zeros
     grid.z = splits;
     CUtensorMap tmP, tmQ;
     int e = swap ? make_map(&tmP, W, N, K, ldw, BM) : make_map(&tmP, X, M, K, ldx, BM);
@@ -485,7 +488,7 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
     if (e) return e;
     int esz = (epi == EPI_F32 || epi == EPI_ADD_F32) ? 4 : 2;
     int vec_ok = ((uintptr_t)out % 16 == 0) && ((size_t)ldc * esz % 16 == 0);
-    GemmArgs a{out, ws, counters, M, N, K, ldc, kb_per_split, vec_ok};
+    GemmArgs a{out, M, N, K, ldc, kb_per_split, vec_ok};
     switch (epi) {
     case EPI_BF16: return dispatch<EPI_BF16>(swap, bn, tmP, tmQ, a, grid, stream);
     case EPI_F32: return dispatch<EPI_F32>(swap, bn, tmP, tmQ, a, grid, stream);

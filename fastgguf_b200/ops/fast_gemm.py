@@ -4,14 +4,12 @@
 None when the sizes are outside what the fast kernel takes (a reduction length that is no
 multiple of 8, unaligned rows), in which case the caller uses the plain kernel.
 
-The split-K path of the kernel sums partial tiles through a float32 workspace and per-tile
-arrival counters; one workspace per device is allocated when the first plan is made (before any
-stream capture) and shared by every contraction on that device, which run one after another on
-the stream.
+With few rows (decode) and few weight tiles the kernel splits the reduction over a thread-block
+cluster and sums the partial tiles through distributed shared memory; it needs no scratch memory.
 """
 from __future__ import annotations
 
-from ctypes import c_int, c_longlong, c_void_p
+from ctypes import c_int, c_void_p
 from typing import Optional
 
 import torch
@@ -22,27 +20,9 @@ EPI_BF16, EPI_F32, EPI_ADD_F32, EPI_SILU_MUL = 0, 1, 2, 3
 _BAD_SIZE = 10002
 
 register_signatures("tc", {
-    "fg_gemm_tc": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                   c_void_p, c_void_p, c_int, c_void_p],
+    "fg_gemm_tc": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "fg_gemm_tc_error": [],
-    "fg_gemm_tc_counter_count": [],
 })
-
-_workspaces: dict = {}
-
-
-def _workspace(device: torch.device):
-    key = device.index if device.index is not None else torch.cuda.current_device()
-    ws = _workspaces.get(key)
-    if ws is None:
-        l = lib("tc")
-        l.fg_gemm_tc_workspace_floats.restype = c_longlong
-        l.fg_gemm_tc_workspace_floats.argtypes = []
-        n = int(l.fg_gemm_tc_workspace_floats())
-        ws = (torch.empty(n, dtype=torch.float32, device=device),
-              torch.zeros(int(l.fg_gemm_tc_counter_count()), dtype=torch.int32, device=device))
-        _workspaces[key] = ws
-    return ws
 
 
 def pipeline_error() -> int:
@@ -88,9 +68,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = N
         out = torch.empty((M, N), dtype=dt, device=a.device)
     if out.shape != (M, N) or out.stride(1) != 1 or out.dtype != dt:
         raise KernelError(f"gemm_tc: out must be [{M}, {N}] {dt} with contiguous rows")
-    ws, counters = _workspace(a.device)
     code = lib("tc").fg_gemm_tc(ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out.stride(0), epi,
-                                M, rows, K, ptr(ws), ptr(counters), int(force_splits), stream())
+                                M, rows, K, int(force_splits), stream())
     if code == _BAD_SIZE:
         return None
     check(code, "gemm_tc")
@@ -100,7 +79,6 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = N
 class _Plan:
     def __init__(self, weight: torch.Tensor):
         self.weight = weight
-        _workspace(weight.device)
 
     def run(self, a, out=None, out_dtype=None, accumulate=False):
         return gemm_tc(a, self.weight, out=out, out_dtype=out_dtype, accumulate=accumulate)

@@ -56,13 +56,13 @@ def test_gemm_tc_epilogues(M, N, K):
     assert fast_gemm.pipeline_error() == 0
 
 
-@pytest.mark.parametrize("splits", [2, 3, 8])
+@pytest.mark.parametrize("splits", [2, 4, 8])
 @pytest.mark.parametrize("M,N,K", [(1, 256, 2048), (8, 200, 1096), (64, 384, 8192)])
 def test_gemm_tc_split_k(M, N, K, splits):
     from fastgguf_b200.ops import fast_gemm
     a, w = _operands(M, N, K, torch.bfloat16, 3)
     want = a.double() @ w.double().T
-    for _ in range(2):                      # twice: the arrival counters must be back at zero
+    for _ in range(2):
         got = fast_gemm.gemm_tc(a, w, out_dtype=torch.float32, force_splits=splits)
         _check(got, a, w, want, False)
     res = torch.randn(M, N, device="cuda")
