@@ -8,13 +8,25 @@
 // among `n_splits` CTAs, so one long sequence fills the GPU as well as many short ones; inside a
 // CTA four warps take pages round-robin, each with K and V buffers of its own (one K and one V
 // load always in flight), and merge their running (max, sum, O) through shared memory.  With
-// n_splits > 1 each CTA writes an unnormalised partial (O, max, sum) to scratch memory and a
-// second kernel merges the splits in order.
+// n_splits > 1 the CTAs of a sequence and KV head either form a thread-block cluster (2, 4 or 8
+// splits) and merge their partial (O, max, sum) through distributed shared memory, or (more
+// splits, very long contexts) write them to scratch memory for a second kernel to merge.
 #include "attention_mma.cuh"
 
 #define DEC_WARPS 4
 
-template <int HD>
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_dsmem(const float *p, int rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(p)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+template <int HD, bool CLUSTER>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ positions,
                    const int *__restrict__ block_table, int table_width,
@@ -108,6 +120,8 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
         }
     }
     __syncthreads();
+    float *cta_o = (float *)(smem + (size_t)DEC_WARPS * 2 * TILE_BYTES);     // [16][HD] result of this CTA
+    float *cta_ml = cta_o + 16 * HD;                                          // [16][2]
     for (int i = threadIdx.x; i < rows * HD; i += DEC_WARPS * 32) {
         int r = i / HD, d = i % HD;
         float M = -INFINITY;
@@ -126,11 +140,43 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
         int h = kvh * G + g0 + r;
         if (n_splits == 1) {
             out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        } else if (CLUSTER) {
+            cta_o[i] = O;
+            if (d == 0) { cta_ml[r * 2] = M; cta_ml[r * 2 + 1] = L; }
         } else {
             size_t prow = ((size_t)b * KV * G + h) * n_splits + split;
             part_o[prow * HD + d] = O;
             if (d == 0) { part_ml[prow * 2] = M; part_ml[prow * 2 + 1] = L; }
         }
+    }
+    if (CLUSTER && n_splits > 1) {
+        // the splits of this (sequence, KV head) are the CTAs of one cluster: CTA `split` merges its
+        // share of the (row, dim) elements over all of them, in rank order
+        cluster_sync_all();
+        const int total = rows * HD, per = (total + n_splits - 1) / n_splits;
+        for (int i = split * per + threadIdx.x; i < min(total, (split + 1) * per); i += DEC_WARPS * 32) {
+            int r = i / HD, d = i % HD;
+            float ms[8], ls[8], os[8];
+#pragma unroll
+            for (int z = 0; z < 8; z++) {
+                bool in = z < n_splits;
+                ms[z] = in ? ld_dsmem(&cta_ml[r * 2], z) : -INFINITY;
+                ls[z] = in ? ld_dsmem(&cta_ml[r * 2 + 1], z) : 0.f;
+                os[z] = in ? ld_dsmem(&cta_o[i], z) : 0.f;
+            }
+            float M = -INFINITY;
+#pragma unroll
+            for (int z = 0; z < 8; z++) M = fmaxf(M, ms[z]);
+            float O = 0.f, L = 0.f;
+#pragma unroll
+            for (int z = 0; z < 8; z++) {
+                float wgt = ms[z] == -INFINITY ? 0.f : expf(ms[z] - M);
+                O += wgt * os[z];
+                L += wgt * ls[z];
+            }
+            out[(size_t)b * ldo + (size_t)(kvh * G + g0 + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        }
+        cluster_sync_all();                    // no CTA leaves while its partial is still being read
     }
 }
 
@@ -154,36 +200,69 @@ __global__ void attn_decode_merge_kernel(const float *__restrict__ part_o, const
     out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
 }
 
+template <int HD, bool CLUSTER>
+static int launch_decode_kernel(dim3 grid, int cluster_x, cudaStream_t stream, const void *q, int ldq, void *out, int ldo,
+                                const int *positions, const int *block_table, int table_width, const void *k_pool,
+                                const void *v_pool, int KV, int G, float scale, int window, int n_splits,
+                                float *part_o, float *part_ml) {
+    constexpr int smem = DEC_WARPS * 2 * PAGE * HD * 2 + 16 * HD * 4 + 16 * 2 * 4;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(DEC_WARPS * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (fg_pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster_x; attr[n].val.clusterDim.y = 1; attr[n].val.clusterDim.z = 1;
+        n++;
+    }
+    cfg.attrs = attr; cfg.numAttrs = n;
+    return (int)cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, CLUSTER>, (const bf16 *)q, ldq, positions, block_table,
+                                   table_width, (const bf16 *)k_pool, (const bf16 *)v_pool, KV, G, scale, window, n_splits,
+                                   part_o, part_ml, (bf16 *)out, ldo);
+}
+
 template <int HD>
 static int launch_decode(const void *q, int ldq, void *out, int ldo, const int *positions, const int *block_table,
                          int table_width, const void *k_pool, const void *v_pool, int B, int H, int KV, float scale,
                          int window, int n_splits, float *part_o, float *part_ml, cudaStream_t stream) {
-    constexpr int smem = DEC_WARPS * 2 * PAGE * HD * 2;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
     int G = H / KV;
     dim3 grid(n_splits, KV * ((G + 15) / 16), B);
-    int e = fg_launch(attn_decode_kernel<HD>, grid, dim3(DEC_WARPS * 32), (size_t)smem, stream, (const bf16 *)q, ldq, positions, block_table, table_width,
-        (const bf16 *)k_pool, (const bf16 *)v_pool, KV, G, scale, window, n_splits, part_o, part_ml, (bf16 *)out, ldo);
-    if (e || n_splits == 1) return e;
-    return fg_launch(attn_decode_merge_kernel<HD>, dim3(H, B), dim3(HD), 0, stream, (const float *)part_o, (const float *)part_ml, n_splits, H, (bf16 *)out, ldo);
+    // 2, 4 or 8 splits without scratch memory: merged inside a cluster
+    bool cluster = !part_o && (n_splits == 2 || n_splits == 4 || n_splits == 8);
+    if (n_splits == 1 || cluster)
+        return launch_decode_kernel<HD, true>(grid, cluster ? n_splits : 1, stream, q, ldq, out, ldo, positions, block_table,
+                                              table_width, k_pool, v_pool, KV, G, scale, window, n_splits, nullptr, nullptr);
+    int e = launch_decode_kernel<HD, false>(grid, 1, stream, q, ldq, out, ldo, positions, block_table, table_width, k_pool,
+                                            v_pool, KV, G, scale, window, n_splits, part_o, part_ml);
+    if (e) return e;
+    return fg_launch(attn_decode_merge_kernel<HD>, dim3(H, B), dim3(HD), 0, stream, (const float *)part_o,
+                     (const float *)part_ml, n_splits, H, (bf16 *)out, ldo);
 }
 
 // q: [B, ldq] bf16, one row per sequence, heads first in the row; positions[b] is the position of
 // that row (its key and value are already in the cache); pools [pages, KV, 64, HD] bf16.
-// part_o: [B, H, n_splits, HD] f32 and part_ml: [B, H, n_splits, 2] f32 scratch (unused when
-// n_splits == 1).  Takes HD 64 and 128 and pages of 64; anything else returns FG_ERR_BAD_SIZE.
+// part_o: [B, H, n_splits, HD] f32 and part_ml: [B, H, n_splits, 2] f32 scratch for the two-kernel
+// path; pass null pointers with n_splits 1, 2, 4 or 8 for the path that needs no scratch.
+// Takes HD 64 and 128 and pages of 64; anything else returns FG_ERR_BAD_SIZE.
 extern "C" int fg_attention_decode(const void *q, int ldq, void *out, int ldo, const int *positions,
                                    const int *block_table, int table_width, const void *k_pool, const void *v_pool,
                                    int B, int H, int KV, int hd, int page_size, float scale, int window,
                                    int n_splits, float *part_o, float *part_ml, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (page_size != PAGE || H % KV || n_splits < 1 || B > 65535 || ldq % 2 || ((uintptr_t)q & 3)) return FG_ERR_BAD_SIZE;
-    if (n_splits > 1 && (!part_o || !part_ml)) return FG_ERR_BAD_SIZE;
+    if ((part_o == nullptr) != (part_ml == nullptr)) return FG_ERR_BAD_SIZE;
+    if (!part_o && n_splits != 1 && n_splits != 2 && n_splits != 4 && n_splits != 8) return FG_ERR_BAD_SIZE;
     if (hd == 64) return launch_decode<64>(q, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, B, H, KV, scale, window, n_splits, part_o, part_ml, stream);
     if (hd == 128) return launch_decode<128>(q, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, B, H, KV, scale, window, n_splits, part_o, part_ml, stream);
     return FG_ERR_BAD_SIZE;

@@ -169,6 +169,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
     pdl_launch_dependents();
+    if (threadIdx.x == 32) {                      // descriptors into the cache before their first use
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmP) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmQ) : "memory");
+    }
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -367,15 +371,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
             const float *part = (const float *)smem;
             const int per = BN / S, c_begin = blockIdx.z * per;
             for (int c = c_begin; c < c_begin + per; c++) {
+                const int m = q0 + c;
+                const bool in = n < a.N && m < a.M;
+                const size_t idx = (size_t)m * a.ldc + n;
+                float res = 0.f;
+                if (EPI == EPI_ADD_F32 && in) res = ((const float *)a.out)[idx];   // in flight during the remote reads
+                const uint32_t local = smem_u32(&part[c * BM + prow]);
+                float pz[8];
+#pragma unroll
+                for (int z = 0; z < 8; z++) pz[z] = z < S ? ld_dsmem_f32(local, z) : 0.f;
                 float v = 0.f;
-                uint32_t local = smem_u32(&part[c * BM + prow]);
-                for (int z = 0; z < S; z++) v += ld_dsmem_f32(local, z);
-                int m = q0 + c;
-                if (n < a.N && m < a.M) {
-                    size_t idx = (size_t)m * a.ldc + n;
+#pragma unroll
+                for (int z = 0; z < 8; z++) v += pz[z];                            // rank order; absent ranks add 0
+                if (in) {
                     if (EPI == EPI_BF16) ((bf16 *)a.out)[idx] = __float2bfloat16_rn(v);
                     else if (EPI == EPI_F32) ((float *)a.out)[idx] = v;
-                    else ((float *)a.out)[idx] += v;
+                    else ((float *)a.out)[idx] = res + v;
                 }
             }
         }
@@ -436,9 +447,9 @@ template <int EPI>
 static int dispatch(bool swap, int bn, const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs &a, dim3 grid, cudaStream_t st) {
     if (swap) {
         switch (bn) {
-        case 16: return launch<16, 8, EPI, true>(tmP, tmQ, a, grid, st);
-        case 32: return launch<32, 8, EPI, true>(tmP, tmQ, a, grid, st);
-        case 64: return launch<64, 7, EPI, true>(tmP, tmQ, a, grid, st);
+        case 16: return launch<16, 6, EPI, true>(tmP, tmQ, a, grid, st);
+        case 32: return launch<32, 5, EPI, true>(tmP, tmQ, a, grid, st);
+        case 64: return launch<64, 4, EPI, true>(tmP, tmQ, a, grid, st);
         }
     } else {
         switch (bn) {

@@ -275,12 +275,70 @@ sample_kernel(float *__restrict__ logits, int V, int ldl, SampleParams sp,
     }
 }
 
+// ---- greedy without a repeat penalty: the vocabulary of each row is split over GREEDY_BLOCKS blocks;
+// each folds its best (value, lowest index) into one 64-bit word per row with atomicMax, and the
+// block that arrives last writes the token and clears the word for the next call.  The words
+// live in device memory of this library; calls on one stream follow one another.
+#define GREEDY_BLOCKS 32
+#define GREEDY_MAX_ROWS 1024
+__device__ unsigned long long g_greedy_best[GREEDY_MAX_ROWS];
+__device__ int g_greedy_count[GREEDY_MAX_ROWS];
+
+__global__ void __launch_bounds__(256)
+greedy_kernel(const float *__restrict__ logits, int V, int ldl, const int *__restrict__ seq_slot,
+              int *__restrict__ hist, int hist_cap, int *__restrict__ hist_count, int *__restrict__ out_tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ unsigned long long s_best[8];
+    const int b = blockIdx.y;
+    const float *row = logits + (size_t)b * ldl;
+    const int per = (V + GREEDY_BLOCKS - 1) / GREEDY_BLOCKS;
+    const int i0 = blockIdx.x * per, i1 = min(V, i0 + per);
+    unsigned long long best = 0ull;
+    for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+        unsigned long long w = ((unsigned long long)float_key(row[i]) << 32) | (uint32_t)(~(uint32_t)i);
+        best = w > best ? w : best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    if ((threadIdx.x & 31) == 0) s_best[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++) best = s_best[w] > best ? s_best[w] : best;
+        atomicMax(&g_greedy_best[b], best);
+        __threadfence();
+        if (atomicAdd(&g_greedy_count[b], 1) == GREEDY_BLOCKS - 1) {
+            __threadfence();
+            unsigned long long win = atomicMax(&g_greedy_best[b], 0ull);
+            int tok = (int)(~(uint32_t)(win & 0xffffffffull));
+            out_tokens[b] = tok;
+            g_greedy_best[b] = 0ull;
+            g_greedy_count[b] = 0;
+            if (hist) {
+                int slot = seq_slot[b];
+                int *h = hist + (size_t)slot * hist_cap;
+                int c = hist_count[slot];
+                if (c < hist_cap) h[c] = tok;
+                else { for (int i = 1; i < hist_cap; i++) h[i - 1] = h[i]; h[hist_cap - 1] = tok; }
+                hist_count[slot] = c + 1;
+            }
+        }
+    }
+}
+
 extern "C" int fg_sample(float *logits, int B, int V, int ldl, float temp, int top_k, float top_p,
                          float repeat_penalty, int repeat_last_n, const int *seq_slot,
                          unsigned long long *rng, int *hist, int hist_cap, int *hist_count,
                          const int *stop_ids, int n_stop, int *out_tokens, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (top_k > MAX_TOP_K) return FG_ERR_BAD_SIZE;
+    bool penalizes = hist && repeat_penalty > 0.f && repeat_penalty != 1.0f && repeat_last_n > 0;
+    if (temp <= 0.f && !penalizes && B <= GREEDY_MAX_ROWS)
+        return fg_launch(greedy_kernel, dim3(GREEDY_BLOCKS, B), dim3(256), 0, stream, (const float *)logits, V, ldl,
+                         seq_slot, hist, hist_cap, hist_count, out_tokens);
     SampleParams sp{temp, top_p, repeat_penalty, top_k, repeat_last_n};
     sample_kernel<<<B, SAMPLE_THREADS, 0, stream>>>(logits, V, ldl, sp, seq_slot, rng, hist, hist_cap,
                                                     hist_count, stop_ids, n_stop, out_tokens);

@@ -27,13 +27,21 @@ def supported(q: torch.Tensor, k_pool: torch.Tensor, head_dim: int) -> bool:
 
 
 def decode_splits(n_seq: int, n_heads: int, n_kv_heads: int, table_width: int) -> int:
-    """How many CTAs share one sequence's pages: enough to give every SM two CTAs."""
+    """How many CTAs share one sequence's pages: enough to give every SM two CTAs.  Up to 8 splits
+    (a power of two) are merged inside a thread-block cluster; only contexts beyond 16K positions
+    take more splits and the scratch-memory path."""
     ctas = n_seq * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
-    return max(1, min((2 * N_SM + ctas - 1) // ctas, table_width))
+    want = max(1, min((2 * N_SM + ctas - 1) // ctas, table_width))
+    if want > 8 and table_width > 256:
+        return want
+    s = 1
+    while s < want and s < 8:
+        s *= 2
+    return s
 
 
 def attention_decode(q, positions, block_table, k_pool, v_pool, n_heads, n_kv_heads, head_dim, scale, window=0,
-                     n_splits: Optional[int] = None, out=None):
+                     n_splits: Optional[int] = None, out=None, use_scratch: bool = False):
     """q: [B, >= H*hd] bf16, one new token per sequence at ``positions[b]`` (already in the cache)."""
     B = q.shape[0]
     if n_splits is None:
@@ -41,7 +49,7 @@ def attention_decode(q, positions, block_table, k_pool, v_pool, n_heads, n_kv_he
     if out is None:
         out = torch.empty((B, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
     part_o = part_ml = None
-    if n_splits > 1:
+    if n_splits not in (1, 2, 4, 8) or use_scratch:
         part_o = torch.empty((B, n_heads, n_splits, head_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((B, n_heads, n_splits, 2), dtype=torch.float32, device=q.device)
     check(lib("attn").fg_attention_decode(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(positions), ptr(block_table),

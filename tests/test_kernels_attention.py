@@ -80,7 +80,7 @@ def test_attention_generic(H, KV, hd, window, dtype, tol):
     assert _err(got, plain(case, H, KV, hd, scale, window)) < tol
 
 
-@pytest.mark.parametrize("n_splits", [None, 1, 3, 16])
+@pytest.mark.parametrize("n_splits", [None, 1, 2, 3, 8, 16])
 @pytest.mark.parametrize("H,KV,hd,window", [(8, 2, 64, 0), (3, 1, 128, 0), (24, 8, 128, 0), (20, 1, 64, 0),
                                             (4, 4, 64, 100)])
 def test_attention_decode(H, KV, hd, window, n_splits):
@@ -89,7 +89,13 @@ def test_attention_decode(H, KV, hd, window, n_splits):
     scale = 1.0 / math.sqrt(hd)
     got = fast_attention.attention_decode(case["q"], case["positions"], case["table"], case["k_pool"], case["v_pool"],
                                           H, KV, hd, scale, window, n_splits=n_splits)
-    assert _err(got, plain(case, H, KV, hd, scale, window)) < 1.5e-2
+    want = plain(case, H, KV, hd, scale, window)
+    assert _err(got, want) < 1.5e-2
+    if n_splits in (2, 8):        # the same splits through scratch memory and the merge kernel
+        got = fast_attention.attention_decode(case["q"], case["positions"], case["table"], case["k_pool"],
+                                              case["v_pool"], H, KV, hd, scale, window, n_splits=n_splits,
+                                              use_scratch=True)
+        assert _err(got, want) < 1.5e-2
 
 
 @pytest.mark.parametrize("H,KV,hd,window", [(8, 2, 64, 0), (3, 1, 128, 0), (24, 8, 128, 0), (20, 1, 64, 0),
