@@ -267,3 +267,56 @@ extern "C" int fg_attention_decode(const void *q, int ldq, void *out, int ldo, c
     if (hd == 128) return launch_decode<128>(q, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, B, H, KV, scale, window, n_splits, part_o, part_ml, stream);
     return FG_ERR_BAD_SIZE;
 }
+
+// ---------------------------------------------------------------------------- no allocation
+// See fastgguf_noalloc.h.  The scratch of the two-kernel path lives in this array, which is part
+// of the library image: every GPU that loads the library holds it until the process exits.
+#include "fastgguf_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[FG_NOALLOC_SCRATCH_FLOATS];
+
+// In host code the name of a __device__ array is only a handle; the address the kernels need comes
+// from cudaGetSymbolAddress, asked once per device with that device current.
+static int noalloc_scratch_address(float **ptr) {
+    static float *per_device[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return FG_ERR_BAD_SIZE;
+    if (!per_device[dev]) {
+        float *p = nullptr;
+        e = cudaGetSymbolAddress((void **)&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        per_device[dev] = p;
+    }
+    *ptr = per_device[dev];
+    return 0;
+}
+
+extern "C" int fg_attention_decode_noalloc(const void *q, int ldq, void *out, int ldo, const int *positions,
+                                           const int *block_table, int table_width, const void *k_pool,
+                                           const void *v_pool, int B, int H, int KV, int hd, int page_size, float scale,
+                                           int window, int n_splits, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (n_splits < 1 || H <= 0 || hd <= 0) return FG_ERR_BAD_SIZE;
+    long long rows = (long long)B * H * n_splits;
+    if (rows * (hd + 2) > FG_NOALLOC_SCRATCH_FLOATS) return FG_ERR_NOALLOC_TOO_LARGE;
+    float *scratch = nullptr;
+    int e = noalloc_scratch_address(&scratch);
+    if (e) return e;
+    // partial outputs first, then the (max, sum) pairs; each call writes every element it later reads
+    float *part_o = scratch, *part_ml = scratch + rows * hd;
+    if (page_size != PAGE || H % KV || B > 65535 || ldq % 2 || ((uintptr_t)q & 3)) return FG_ERR_BAD_SIZE;
+    int G = H / KV;
+    dim3 grid(n_splits, KV * ((G + 15) / 16), B);
+#define NOALLOC_RUN(HD) do { \
+        e = launch_decode_kernel<HD, false>(grid, 1, stream, q, ldq, out, ldo, positions, block_table, table_width, \
+                                            k_pool, v_pool, KV, G, scale, window, n_splits, part_o, part_ml); \
+        if (e || n_splits == 1) return e;      /* one split writes the output itself */ \
+        return fg_launch(attn_decode_merge_kernel<HD>, dim3(H, B), dim3(HD), 0, stream, (const float *)part_o, \
+                         (const float *)part_ml, n_splits, H, (bf16 *)out, ldo); } while (0)
+    if (hd == 64) NOALLOC_RUN(64);
+    if (hd == 128) NOALLOC_RUN(128);
+#undef NOALLOC_RUN
+    return FG_ERR_BAD_SIZE;
+}

@@ -21,6 +21,7 @@ _ERRORS = {
     10002: "a size outside what this kernel takes",
     10003: "device-side wait ran out (pipeline error flag set)",
     10004: "could not encode a TMA tensor map",
+    10005: "the request exceeds the fixed scratch array of the no-allocation entry point",
 }
 
 
