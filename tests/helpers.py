@@ -27,7 +27,12 @@ TINY_B = {
     "max_position_embeddings": 1024, "tie_word_embeddings": False, "hidden_act": "silu",
     "eos_token_id": [3, 5],
 }
-TINY = {"a": (TINY_A, 0), "b": (TINY_B, 1)}
+# head sizes the tensor-core attention kernels take: 64 with 4 query heads a KV head, 128 with 3
+TINY_C = dict(TINY_A, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=1,
+              head_dim=64, intermediate_size=448, vocab_size=300, max_position_embeddings=2048)
+TINY_D = dict(TINY_B, hidden_size=200, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2,
+              head_dim=128, intermediate_size=320, vocab_size=333, max_position_embeddings=2048)
+TINY = {"a": (TINY_A, 0), "b": (TINY_B, 1), "c": (TINY_C, 2), "d": (TINY_D, 3)}
 
 
 def make_model_dir(tmp_path, cfg_dict, seed, dtype=torch.bfloat16):

@@ -10,7 +10,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["a", "b"])
+@pytest.mark.parametrize("which", ["a", "b", "c", "d"])
 def test_whole_requests(tmp_path, which, dtype):
     from fastgguf_b200.engine.api import Engine
     from fastgguf_b200.engine.batch import StepEntry

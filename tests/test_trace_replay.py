@@ -36,7 +36,7 @@ def _compare(rows, want, requests, tol, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["a", "b"])
+@pytest.mark.parametrize("which", ["a", "b", "c", "d"])
 def test_replay_three_cuts(tmp_path, models, which, dtype):
     model_dir, cfg, requests, want = models[which]
     V = cfg["vocab_size"]
