@@ -68,7 +68,8 @@ def test_rope_append(H, KV, hd, dtype, tol):
         written[page, off] = True
         assert (k_pool[page, :, off].cpu().double() - want_k[m]).abs().max() <= tol * want_k.abs().max()
         assert torch.equal(v_pool[page, :, off].cpu(), qkv[m, Q + D:].reshape(KV, hd))
-    assert k_pool.cpu()[~written].abs().sum() == 0 and v_pool.cpu()[~written].abs().sum() == 0   # nothing else touched
+    untouched = ~written[:, None, :, None]                         # nothing else is written
+    assert (k_pool.cpu() * untouched).abs().sum() == 0 and (v_pool.cpu() * untouched).abs().sum() == 0
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 2 ** -7)])
