@@ -107,7 +107,7 @@ def test_toy_mixer_with_state_and_a_schedule_with_repeats(dtype, tol):
     _register_toy()
     model = DecoderModel(_spec(), Runtime(torch.device("cuda"), dtype))
     expected = model.expected_tensors()
-    assert "l1.mix" in expected and len(expected) == 15            # the repeated layer's tensors appear once
+    assert "l1.mix" in expected and len(expected) == 17            # the repeated layer's tensors appear once
     W = {n: random_tensor(n, s, 9, torch.bfloat16) * (5 if s.init[0] == "normal" else 1) for n, s in expected.items()}
     model.load_weights(MemorySource(W))
     cache = model.make_cache(max_tokens=512, n_slots=3)
