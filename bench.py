@@ -1,7 +1,8 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the engine on one GPU, as one JSON line.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--no-points] [--no-prefill]
+                    [--impl reference]
 
 Default run: the layer sizes of Llama 3.2 1B with random weights, bfloat16, a batch of 8
 sequences with random prompts of unequal lengths 128..1024, context 4096.  A "step" is one
@@ -120,7 +121,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill measurement")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -233,7 +235,7 @@ def main():
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
     }
 
-    if not args.no_points:
+    if not args.no_prefill:
         # ---- prefill of 2,048 tokens in one step
         toks = rng.integers(0, c["vocab_size"], size=PREFILL_TOKENS).tolist()
         from fastgguf_b200.engine.batch import StepEntry
@@ -253,6 +255,7 @@ def main():
         fl = prefill_flops(c, layers, PREFILL_TOKENS)
         rec["prefill"] = {"value": round(PREFILL_TOKENS / (pms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
                           "frac": round(fl / (pms * 1e-3) / 1e12 / pk["bf16_tflops"], 4)}
+    if not args.no_points:
         points = {}
         for b in (1, 64):
             timed_decode(b, 3, 3)
