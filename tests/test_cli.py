@@ -1,0 +1,55 @@
+"""The command line: inspect / dump / random on the CPU, generate and selftest on the GPU."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from helpers import TINY_A, TINY_C, make_model_dir
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def run(*args):
+    return subprocess.run([sys.executable, "-m", "fastgguf_b200", *args], cwd=ROOT, capture_output=True, text=True)
+
+
+def test_inspect_dump_random_and_usage(tmp_path):
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(TINY_A))
+    p = run("random", str(cfg_path), str(tmp_path / "m"), "--seed", "4", "--dtype", "float32")
+    assert p.returncode == 0 and os.path.exists(tmp_path / "m" / "model.safetensors")
+    p = run("inspect", str(tmp_path / "m"))
+    assert p.returncode == 0 and "LlamaForCausalLM" in p.stdout and "hidden_size = 64" in p.stdout
+    assert "tensors: 21" in p.stdout and "model.embed_tokens.weight" in p.stdout
+    p = run("inspect", str(tmp_path / "m"), "--json")
+    assert json.loads(p.stdout)["config"]["q_dim"] == 64
+    p = run("dump", str(tmp_path / "m"))
+    assert p.returncode == 0 and "rope_theta = 10000.0" in p.stdout
+    assert run("inspect", str(tmp_path / "nothing")).returncode == 2          # load errors exit 2
+    p = run("generate", str(tmp_path / "m"), "--bogus", "1")
+    assert p.returncode == 1 and "unknown option --bogus" in p.stdout        # usage errors exit 1
+    assert run("frobnicate").returncode == 1
+
+
+@pytest.mark.gpu
+def test_generate_command(tmp_path):
+    d = make_model_dir(tmp_path, TINY_C, 2, torch.bfloat16)
+    p = run("generate", d, "256", "--temp", "0", "--max-tokens", "6", "--prompt", "5,17,3", "--prompt", "9", "--json",
+            "--ignore-eos")
+    assert p.returncode == 0, p.stdout + p.stderr
+    assert "[Sampler] greedy" in p.stdout and "[Config] LlamaForCausalLM: layers=2 embd=256 ctx=256" in p.stdout
+    out = json.loads([l for l in p.stdout.splitlines() if l.startswith("[{")][0])
+    assert [len(o["tokens"]) for o in out] == [6, 6] and all(o["finish_reason"] == "length" for o in out)
+    q = run("generate", d, "256", "--temp", "0", "--max-tokens", "6", "--prompt", "5,17,3", "--prompt", "9", "--json",
+            "--ignore-eos", "--dtype", "float32")
+    assert q.returncode == 0
+
+
+@pytest.mark.gpu
+def test_selftest_command():
+    p = run("selftest", "--quick")
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-2000:]
+    assert "ALL TESTS PASSED" in p.stdout and "FAIL " not in p.stdout
