@@ -23,7 +23,7 @@ def test_inspect_dump_random_and_usage(tmp_path):
     assert p.returncode == 0 and os.path.exists(tmp_path / "m" / "model.safetensors")
     p = run("inspect", str(tmp_path / "m"))
     assert p.returncode == 0 and "LlamaForCausalLM" in p.stdout and "hidden_size = 64" in p.stdout
-    assert "tensors: 21" in p.stdout and "model.embed_tokens.weight" in p.stdout
+    assert "tensors: 20" in p.stdout and "model.embed_tokens.weight" in p.stdout
     p = run("inspect", str(tmp_path / "m"), "--json")
     assert json.loads(p.stdout)["config"]["q_dim"] == 64
     p = run("dump", str(tmp_path / "m"))
