@@ -93,7 +93,10 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
         __syncwarp();
         if (pn < p_end) load_page_warp<HD>(ks, k_pool + nbase, lane);
         cp_async_commit();                     // (possibly empty) group: keeps the wait counts uniform
-        softmax_update<HD / 8>(s, o, m, l, scale, p * PAGE, lo, hi, lane);
+        if (p * PAGE + PAGE - 1 <= pos && p * PAGE >= lo_key)
+            softmax_update<HD / 8, false>(s, o, m, l, scale * LOG2E, p * PAGE, lo, hi, lane);
+        else
+            softmax_update<HD / 8, true>(s, o, m, l, scale * LOG2E, p * PAGE, lo, hi, lane);
         cp_async_wait<1>();                    // V of this page has landed
         __syncwarp();
         pv_page<HD>(o, s, vs, lane);
@@ -133,7 +136,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
             const float *pml = (const float *)(smem + (size_t)w * 2 * TILE_BYTES + TILE_BYTES);
             const float *po = (const float *)(smem + (size_t)w * 2 * TILE_BYTES);
             float mw = pml[r * 2];
-            float wgt = mw == -INFINITY ? 0.f : expf(mw - M);
+            float wgt = mw == -INFINITY ? 0.f : ex2(mw - M);
             O += wgt * po[r * HD + d];
             L += wgt * pml[r * 2 + 1];
         }
@@ -170,7 +173,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
             float O = 0.f, L = 0.f;
 #pragma unroll
             for (int z = 0; z < 8; z++) {
-                float wgt = ms[z] == -INFINITY ? 0.f : expf(ms[z] - M);
+                float wgt = ms[z] == -INFINITY ? 0.f : ex2(ms[z] - M);
                 O += wgt * os[z];
                 L += wgt * ls[z];
             }
@@ -193,7 +196,7 @@ __global__ void attn_decode_merge_kernel(const float *__restrict__ part_o, const
     float O = 0.f, L = 0.f;
     for (int s = 0; s < n_splits; s++) {
         float ms = part_ml[(prow0 + s) * 2];
-        float wgt = ms == -INFINITY ? 0.f : expf(ms - M);
+        float wgt = ms == -INFINITY ? 0.f : ex2(ms - M);
         O += wgt * part_o[(prow0 + s) * HD + d];
         L += wgt * part_ml[(prow0 + s) * 2 + 1];
     }

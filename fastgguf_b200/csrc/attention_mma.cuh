@@ -84,13 +84,24 @@ __device__ __forceinline__ void pv_page(float (&o)[HD / 8][4], const float (&s)[
     }
 }
 
+// 2^x on the special-function unit (2 ulp); exponents are kept in the base-2 domain so that one
+// multiply-add and one ex2 make a probability.  ex2(-inf) = 0.
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+#define LOG2E 1.4426950408889634f
+
 // Online-softmax update of one 16 x 64 score tile held by a warp.  Thread t owns rows t/4 and
 // t/4 + 8 (index 0 / 1 below) and key columns 8j + 2(t%4) + {0, 1} of every n-tile j.
-// `key0` is the position of the tile's first key; keys outside [lo[i], hi[i]] are masked.
-// On return s holds the probabilities exp(score - m_new) and o, l are rescaled.
-template <int NO>
+// `scale_log2` = scale * log2(e): running maxima `m` live in the base-2 domain.
+// MASK: `key0` is the position of the tile's first key and keys outside [lo[i], hi[i]] are
+// masked; without MASK every key of the tile is visible to every row (no compares).
+// On return s holds the probabilities 2^(score - m_new) and o, l are rescaled.
+template <int NO, bool MASK>
 __device__ __forceinline__ void softmax_update(float (&s)[8][4], float (&o)[NO][4], float (&m)[2], float (&l)[2],
-                                               float scale, int key0, const int (&lo)[2], const int (&hi)[2], int lane) {
+                                               float scale_log2, int key0, const int (&lo)[2], const int (&hi)[2], int lane) {
     const int c0 = key0 + 2 * (lane & 3);
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -98,7 +109,8 @@ __device__ __forceinline__ void softmax_update(float (&s)[8][4], float (&o)[NO][
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             int i = e >> 1, key = c0 + 8 * j + (e & 1);
-            float v = (key >= lo[i] && key <= hi[i]) ? s[j][e] * scale : -INFINITY;
+            float v = s[j][e] * scale_log2;
+            if (MASK) v = (key >= lo[i] && key <= hi[i]) ? v : -INFINITY;
             s[j][e] = v;
             mx[i] = fmaxf(mx[i], v);
         }
@@ -111,14 +123,15 @@ __device__ __forceinline__ void softmax_update(float (&s)[8][4], float (&o)[NO][
 #pragma unroll
     for (int i = 0; i < 2; i++) {
         mn[i] = fmaxf(m[i], mx[i]);
-        corr[i] = mn[i] == -INFINITY ? 1.f : expf(m[i] - mn[i]);     // nothing seen yet: keep zeros
+        corr[i] = mn[i] == -INFINITY ? 1.f : ex2(m[i] - mn[i]);     // nothing seen yet: keep zeros
+        if (mn[i] == -INFINITY) mn[i] = 0.f;                        // every key masked: 2^(-inf - 0) = 0 below
     }
 #pragma unroll
     for (int j = 0; j < 8; j++)
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             int i = e >> 1;
-            float p = mn[i] == -INFINITY ? 0.f : expf(s[j][e] - mn[i]);
+            float p = ex2(s[j][e] - mn[i]);
             s[j][e] = p;
             sum[i] += p;
         }
@@ -127,7 +140,7 @@ __device__ __forceinline__ void softmax_update(float (&s)[8][4], float (&o)[NO][
         sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
         sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
         l[i] = l[i] * corr[i] + sum[i];
-        m[i] = mn[i];
+        m[i] = fmaxf(m[i], mx[i]);
     }
 #pragma unroll
     for (int d = 0; d < NO; d++) {

@@ -65,9 +65,13 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
     const int tile_hi = start + q0 + tq - 1;
     const int tile_lo = (window > 0 && start + q0 - window + 1 > 0) ? start + q0 - window + 1 : 0;
     const int p_begin = tile_lo / PAGE, p_end = tile_hi / PAGE + 1;
-    int warp_hi = max(hi[0], hi[1]);
+    int warp_hi = max(hi[0], hi[1]), warp_min_hi = min(hi[0], hi[1]), warp_max_lo = max(lo[0], lo[1]);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) warp_hi = max(warp_hi, __shfl_xor_sync(0xffffffffu, warp_hi, o));
+    for (int o = 16; o > 0; o >>= 1) {
+        warp_hi = max(warp_hi, __shfl_xor_sync(0xffffffffu, warp_hi, o));
+        warp_min_hi = min(warp_min_hi, __shfl_xor_sync(0xffffffffu, warp_min_hi, o));   // -1 with an invalid row: always mask
+        warp_max_lo = max(warp_max_lo, __shfl_xor_sync(0xffffffffu, warp_max_lo, o));
+    }
 
     uint32_t qf[HD / 16][4];
     {
@@ -110,7 +114,11 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
 #pragma unroll
             for (int j = 0; j < 8; j++) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
             qk_page<HD>(s, qf, kaddr(st), lane);
-            softmax_update<HD / 8>(s, o, m, l, scale, p * PAGE, lo, hi, lane);
+            // only pages that hold a row's own position (or a window's edge) need the mask
+            if (p * PAGE + PAGE - 1 <= warp_min_hi && p * PAGE >= warp_max_lo)
+                softmax_update<HD / 8, false>(s, o, m, l, scale * LOG2E, p * PAGE, lo, hi, lane);
+            else
+                softmax_update<HD / 8, true>(s, o, m, l, scale * LOG2E, p * PAGE, lo, hi, lane);
             pv_page<HD>(o, s, vaddr(st), lane);
         }
         __syncthreads();                       // the stage is overwritten by the load after next

@@ -37,7 +37,17 @@ extern "C" int fg_embed_gather(const void *table, int table_dtype, const int *to
 // One block per output row.  `rows` (optional) names the input row of each output row, so the
 // final norm runs only on the rows whose logits are wanted.  Statistics in f32 with a fixed
 // reduction order: a row's result does not depend on what else is in the batch.
-template <typename TO>
+template <typename TO> __device__ __forceinline__ void store4(TO *dst, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float *dst, float a, float b, float c, float d) {
+    *(float4 *)dst = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<bf16>(bf16 *dst, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    *(uint2 *)dst = make_uint2(*(uint32_t *)&lo, *(uint32_t *)&hi);
+}
+
+// VEC: rows are read and written four elements at a time (E % 4 == 0, 16-byte aligned rows)
+template <typename TO, bool VEC>
 __global__ void rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ w,
                                const int *__restrict__ rows, TO *__restrict__ out, int E, float eps) {
     __shared__ float scratch[32];
@@ -45,24 +55,44 @@ __global__ void rmsnorm_kernel(const float *__restrict__ x, const float *__restr
     pdl_wait();
     int r = blockIdx.x;
     const float *xi = x + (size_t)(rows ? rows[r] : r) * E;
+    TO *o = out + (size_t)r * E;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < E; i += blockDim.x) { float v = xi[i]; ss += v * v; }
+    if (VEC) {
+        const float4 *x4 = (const float4 *)xi;
+        for (int i = threadIdx.x; i < E / 4; i += blockDim.x) {
+            float4 v = x4[i];
+            ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
+        }
+    } else {
+        for (int i = threadIdx.x; i < E; i += blockDim.x) { float v = xi[i]; ss += v * v; }
+    }
     ss = block_sum(ss, scratch);
     float inv = 1.0f / sqrtf(ss / (float)E + eps);
-    TO *o = out + (size_t)r * E;
-    for (int i = threadIdx.x; i < E; i += blockDim.x) o[i] = from_f32<TO>(xi[i] * inv * w[i]);
+    if (VEC) {
+        const float4 *x4 = (const float4 *)xi, *w4 = (const float4 *)w;
+        for (int i = threadIdx.x; i < E / 4; i += blockDim.x) {
+            float4 v = x4[i], g = w4[i];
+            store4<TO>(o + 4 * i, v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < E; i += blockDim.x) o[i] = from_f32<TO>(xi[i] * inv * w[i]);
+    }
 }
 
 extern "C" int fg_rmsnorm(const float *x, const float *w, const int *rows, void *out, int out_dtype,
                           int R, int E, float eps, cudaStream_t stream) {
     if (R <= 0) return 0;
-    int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : 128);
-    if (out_dtype == FG_F32)
-        return fg_launch(rmsnorm_kernel<float>, dim3(R), dim3(threads), 0, stream, x, w, rows, (float *)out, E, eps);
-    else if (out_dtype == FG_BF16)
-        return fg_launch(rmsnorm_kernel<bf16>, dim3(R), dim3(threads), 0, stream, x, w, rows, (bf16 *)out, E, eps);
-    else return FG_ERR_BAD_DTYPE;
-    return FG_LAUNCH_CHECK();
+    bool vec = E % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 15) == 0;
+    int per = vec ? E / 4 : E;
+    int threads = per >= 1024 ? 256 : (per >= 256 ? 128 : 64);
+    if (out_dtype == FG_F32) {
+        if (vec) return fg_launch(rmsnorm_kernel<float, true>, dim3(R), dim3(threads), 0, stream, x, w, rows, (float *)out, E, eps);
+        return fg_launch(rmsnorm_kernel<float, false>, dim3(R), dim3(threads), 0, stream, x, w, rows, (float *)out, E, eps);
+    } else if (out_dtype == FG_BF16) {
+        if (vec) return fg_launch(rmsnorm_kernel<bf16, true>, dim3(R), dim3(threads), 0, stream, x, w, rows, (bf16 *)out, E, eps);
+        return fg_launch(rmsnorm_kernel<bf16, false>, dim3(R), dim3(threads), 0, stream, x, w, rows, (bf16 *)out, E, eps);
+    }
+    return FG_ERR_BAD_DTYPE;
 }
 
 // ------------------------------------------------------------------ RoPE + cache append
@@ -110,6 +140,52 @@ __global__ void rope_append_kernel(T *__restrict__ qkv, int ld, const int *__res
     }
 }
 
+// bf16 rows with head sizes that are multiples of 16: eight pairs (two 16-byte loads) a thread
+__global__ void rope_append_vec_kernel(bf16 *__restrict__ qkv, int ld, const int *__restrict__ positions,
+                                       const int *__restrict__ row_seq, const int *__restrict__ block_table,
+                                       int table_width, bf16 *__restrict__ k_pool, bf16 *__restrict__ v_pool,
+                                       const float *__restrict__ cos_t, const float *__restrict__ sin_t,
+                                       int H, int KV, int hd, int page_size, int write_kv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int m = blockIdx.x, pos = positions[m], half = hd >> 1, cph = half >> 3;   // chunks of 8 pairs per head
+    bf16 *row = qkv + (size_t)m * ld;
+    const float *cs = cos_t + (size_t)pos * half, *sn = sin_t + (size_t)pos * half;
+    size_t kv_base = 0;
+    if (write_kv) {
+        int page = block_table[(size_t)row_seq[m] * table_width + pos / page_size];
+        kv_base = ((size_t)page * KV * page_size + pos % page_size) * hd;              // + h * page_size * hd
+    }
+    const int n_rot = (H + (write_kv ? KV : 0)) * cph;
+    for (int i = threadIdx.x; i < n_rot; i += blockDim.x) {
+        int h = i / cph, j0 = (i - h * cph) * 8;
+        const bf16 *src = row + (size_t)h * hd;                                         // k heads follow the q heads
+        uint4 lo = *(const uint4 *)(src + j0), hi = *(const uint4 *)(src + j0 + half);
+        float4 c0 = *(const float4 *)(cs + j0), c1 = *(const float4 *)(cs + j0 + 4);
+        float4 s0 = *(const float4 *)(sn + j0), s1 = *(const float4 *)(sn + j0 + 4);
+        const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        const __nv_bfloat162 *lp = (const __nv_bfloat162 *)&lo, *hp = (const __nv_bfloat162 *)&hi;
+        uint4 olo, ohi;
+        __nv_bfloat162 *ol = (__nv_bfloat162 *)&olo, *oh = (__nv_bfloat162 *)&ohi;
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            float2 a = __bfloat1622float2(lp[e]), b = __bfloat1622float2(hp[e]);
+            ol[e] = __floats2bfloat162_rn(a.x * c[2 * e] - b.x * sv[2 * e], a.y * c[2 * e + 1] - b.y * sv[2 * e + 1]);
+            oh[e] = __floats2bfloat162_rn(a.x * sv[2 * e] + b.x * c[2 * e], a.y * sv[2 * e + 1] + b.y * c[2 * e + 1]);
+        }
+        bf16 *dst = h < H ? row + (size_t)h * hd : k_pool + kv_base + (size_t)(h - H) * page_size * hd;
+        *(uint4 *)(dst + j0) = olo;
+        *(uint4 *)(dst + j0 + half) = ohi;
+    }
+    if (!write_kv) return;
+    const bf16 *vrow = row + (size_t)(H + KV) * hd;
+    for (int i = threadIdx.x; i < KV * (hd >> 3); i += blockDim.x) {
+        int h = i / (hd >> 3), d0 = (i - h * (hd >> 3)) * 8;
+        *(uint4 *)(v_pool + kv_base + (size_t)h * page_size * hd + d0) = *(const uint4 *)(vrow + (size_t)h * hd + d0);
+    }
+}
+
 extern "C" int fg_rope_append(void *qkv, int dtype, int ld, const int *positions, const int *row_seq,
                               const int *block_table, int table_width, void *k_pool, void *v_pool,
                               const float *cos_t, const float *sin_t, int M, int H, int KV, int hd,
@@ -118,6 +194,13 @@ extern "C" int fg_rope_append(void *qkv, int dtype, int ld, const int *positions
     if (hd % 2) return FG_ERR_BAD_SIZE;
     int work = H * hd / 2;
     int threads = work >= 1024 ? 256 : (work >= 128 ? 128 : 64);
+    if (dtype == FG_BF16 && hd % 16 == 0 && ld % 8 == 0 && ((uintptr_t)qkv & 15) == 0 &&
+        (!write_kv || ((((uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0))) {
+        int items = (H + KV) * (hd / 16);
+        return fg_launch(rope_append_vec_kernel, dim3(M), dim3(items >= 256 ? 256 : (items >= 128 ? 128 : 64)), 0, stream,
+                         (bf16 *)qkv, ld, positions, row_seq, block_table, table_width, (bf16 *)k_pool, (bf16 *)v_pool,
+                         cos_t, sin_t, H, KV, hd, page_size, write_kv);
+    }
     if (dtype == FG_F32)
         return fg_launch(rope_append_kernel<float>, dim3(M), dim3(threads), 0, stream, (float *)qkv, ld, positions, row_seq, block_table,
             table_width, (float *)k_pool, (float *)v_pool, cos_t, sin_t, H, KV, hd, page_size, write_kv);
