@@ -33,6 +33,41 @@ extern "C" int fg_embed_gather(const void *table, int table_dtype, const int *to
     return FG_LAUNCH_CHECK();
 }
 
+// The same gather that also starts a deferred RMSNorm: xw = bf16(x * norm_w) and the row's sum of squares
+// (one "tile"), for a contraction that applies 1/rms in its epilogue.
+template <typename TW>
+__global__ void embed_gather_norm_kernel(const TW *__restrict__ table, const int *__restrict__ tokens,
+                                         float *__restrict__ x, const float *__restrict__ norm_w,
+                                         bf16 *__restrict__ xw, float *__restrict__ ss, int E) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    int m = blockIdx.x;
+    const TW *row = table + (size_t)tokens[m] * E;
+    float acc = 0.f;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+        float v = to_f32<TW>(row[i]);
+        x[(size_t)m * E + i] = v;
+        xw[(size_t)m * E + i] = __float2bfloat16_rn(v * norm_w[i]);
+        acc += v * v;
+    }
+    acc = block_sum(acc, scratch);
+    if (threadIdx.x == 0) ss[m] = acc;
+}
+
+extern "C" int fg_embed_gather_norm(const void *table, int table_dtype, const int *tokens, float *x,
+                                    const float *norm_w, void *xw, float *ss, int M, int E, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    int threads = E >= 1024 ? 256 : 128;
+    if (table_dtype == FG_F32)
+        return fg_launch(embed_gather_norm_kernel<float>, dim3(M), dim3(threads), 0, stream, (const float *)table, tokens, x,
+                         norm_w, (bf16 *)xw, ss, E);
+    if (table_dtype == FG_BF16)
+        return fg_launch(embed_gather_norm_kernel<bf16>, dim3(M), dim3(threads), 0, stream, (const bf16 *)table, tokens, x,
+                         norm_w, (bf16 *)xw, ss, E);
+    return FG_ERR_BAD_DTYPE;
+}
+
 // ------------------------------------------------------------------ RMSNorm
 // One block per output row.  `rows` (optional) names the input row of each output row, so the
 // final norm runs only on the rows whose logits are wanted.  Statistics in f32 with a fixed

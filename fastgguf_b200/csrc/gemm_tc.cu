@@ -128,7 +128,23 @@ struct GemmArgs {
     int ldc;
     int kb_per_split;     // K-blocks of 64 per split
     int vec_ok;           // rows of `out` allow 16-byte accesses
+    // input side of a deferred RMSNorm: X holds x * w, and 1/rms(x) of each token row is applied to
+    // the accumulators here; ss_in[t * M + m] are partial sums of squares of row m (null: none)
+    const float *ss_in;
+    int ss_tiles, ss_size;
+    float ss_eps;
+    // output side (residual-add epilogue only): besides out = out + acc, write the next norm's
+    // input xw = bf16(out * norm_w) and the partial sums of squares of out, one per tile of features
+    const float *norm_w;  // [N], or null
+    bf16 *xw_out;         // [M, N]
+    float *ss_out;        // [tiles, M]
 };
+
+__device__ __forceinline__ float inv_rms(const GemmArgs &a, int m) {
+    float s = 0.f;
+    for (int t = 0; t < a.ss_tiles; t++) s += a.ss_in[(size_t)t * a.M + m];     // tile order: deterministic
+    return 1.0f / sqrtf(s / (float)a.ss_size + a.ss_eps);
+}
 
 template <int BN, int STAGES, int EPI, bool SWAP>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -143,6 +159,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms need 1 KB alignment
     __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
     __shared__ uint32_t tmem_base_s;
+    __shared__ float inv_s[SWAP ? BN : 1];        // 1/rms of the token columns (deferred norm), else 1
+    __shared__ float red_s[SWAP ? BN : 1][4];     // per-column partial sums of squares of the four epilogue warps
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int p0 = blockIdx.x * BM, q0 = blockIdx.y * BN;
@@ -223,6 +241,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         pdl_wait();
         const int lg = warp & 3;                  // the TMEM lane group this warp may read
         const int prow = lg * 32 + lane;          // row of the tile this thread owns
+        if (SWAP) {
+            // 1/rms of the token columns of this tile, while the main loop runs
+            for (int c = prow; c < BN; c += 128)
+                inv_s[c] = (a.ss_in && q0 + c < a.M) ? inv_rms(a, q0 + c) : 1.0f;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         bool ok = nkb > 0 ? mbar_wait(tfull, 0) : true;
         if (!ok) raise_error(3);
         tc_fence_after();
@@ -252,8 +276,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
 #pragma unroll
                         for (int j = 0; j < 16; j++) {
                             int m = q0 + c0 + j;
+                            float iv = inv_s[c0 + j];
                             if (m < a.M && f < (a.N >> 1))
-                                ((bf16 *)a.out)[(size_t)m * a.ldc + f] = __float2bfloat16_rn(silu_mul(v[j], ex[prow * BN + c0 + j]));
+                                ((bf16 *)a.out)[(size_t)m * a.ldc + f] =
+                                    __float2bfloat16_rn(silu_mul(v[j] * iv, ex[prow * BN + c0 + j] * iv));
                         }
                     }
                 }
@@ -269,25 +295,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                         for (int j = 0; j < 16; j++) part[(c0 + j) * BM + prow] = nkb > 0 ? v[j] : 0.f;
                     }
                 }
-            } else if (ok) {
+            } else {
                 for (int c0 = 0; c0 < BN; c0 += 16) {
                     float v[16];
-                    tc_ld16(trow + c0, v);
+                    if (ok) tc_ld16(trow + c0, v);
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         int m = q0 + c0 + j;
-                        if (!n_ok || m >= a.M) continue;
-                        size_t idx = (size_t)m * a.ldc + n;
-                        if (EPI == EPI_BF16) ((bf16 *)a.out)[idx] = __float2bfloat16_rn(v[j]);
-                        else if (EPI == EPI_F32) ((float *)a.out)[idx] = v[j];
-                        else ((float *)a.out)[idx] += v[j];
+                        float sq = 0.f;
+                        if (ok && n_ok && m < a.M) {
+                            size_t idx = (size_t)m * a.ldc + n;
+                            float val = v[j] * inv_s[c0 + j];
+                            if (EPI == EPI_BF16) ((bf16 *)a.out)[idx] = __float2bfloat16_rn(val);
+                            else if (EPI == EPI_F32) ((float *)a.out)[idx] = val;
+                            else {
+                                val += ((float *)a.out)[idx];
+                                ((float *)a.out)[idx] = val;
+                                if (a.norm_w) {
+                                    a.xw_out[(size_t)m * a.N + n] = __float2bfloat16_rn(val * a.norm_w[n]);
+                                    sq = val * val;
+                                }
+                            }
+                        }
+                        if (EPI == EPI_ADD_F32 && a.norm_w) {
+                            sq = warp_sum(sq);
+                            if (lane == 0) red_s[c0 + j][lg] = sq;
+                        }
                     }
+                }
+                if (EPI == EPI_ADD_F32 && a.norm_w) {
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    for (int c = prow; c < BN; c += 128)
+                        if (q0 + c < a.M)
+                            a.ss_out[(size_t)blockIdx.x * a.M + q0 + c] = red_s[c][0] + red_s[c][1] + red_s[c][2] + red_s[c][3];
                 }
             }
         } else if (ok) {
             // thread = token row, columns = weight rows (features): runs of 16 consecutive outputs
             const int m = p0 + prow;
             const bool m_ok = m < a.M;
+            const float iv = (a.ss_in && m_ok) ? inv_rms(a, m) : 1.0f;
             if (EPI == EPI_SILU_MUL) {
                 const int F = a.N >> 1;
                 for (int blk = 0; blk < BN / 128; blk++) {
@@ -302,7 +349,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                             uint32_t w[8];
 #pragma unroll
                             for (int j = 0; j < 8; j++) {
-                                __nv_bfloat162 t = __floats2bfloat162_rn(silu_mul(g[2 * j], u[2 * j]), silu_mul(g[2 * j + 1], u[2 * j + 1]));
+                                __nv_bfloat162 t = __floats2bfloat162_rn(silu_mul(g[2 * j] * iv, u[2 * j] * iv),
+                                                                         silu_mul(g[2 * j + 1] * iv, u[2 * j + 1] * iv));
                                 w[j] = *(uint32_t *)&t;
                             }
                             ((uint4 *)dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -310,16 +358,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                         } else {
 #pragma unroll
                             for (int j = 0; j < 16; j++)
-                                if (f0 + j < F) dst[j] = __float2bfloat16_rn(silu_mul(g[j], u[j]));
+                                if (f0 + j < F) dst[j] = __float2bfloat16_rn(silu_mul(g[j] * iv, u[j] * iv));
                         }
                     }
                 }
             } else {
+                float sq = 0.f;
                 for (int c0 = 0; c0 < BN; c0 += 16) {
                     float v[16];
                     tc_ld16(trow + c0, v);
                     const int n0 = q0 + c0;
                     if (!m_ok || n0 >= a.N) continue;
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] *= iv;
                     const size_t idx = (size_t)m * a.ldc + n0;
                     const bool full = a.vec_ok && n0 + 16 <= a.N;
                     if (EPI == EPI_BF16) {
@@ -342,20 +393,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                         if (full) {
 #pragma unroll
                             for (int j = 0; j < 4; j++) {
-                                float4 t = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                                 if (EPI == EPI_ADD_F32) {
                                     float4 o = ((float4 *)dst)[j];
-                                    t.x += o.x; t.y += o.y; t.z += o.z; t.w += o.w;
+                                    v[4 * j] += o.x; v[4 * j + 1] += o.y; v[4 * j + 2] += o.z; v[4 * j + 3] += o.w;
                                 }
-                                ((float4 *)dst)[j] = t;
+                                ((float4 *)dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                             }
                         } else {
 #pragma unroll
                             for (int j = 0; j < 16; j++)
-                                if (n0 + j < a.N) dst[j] = EPI == EPI_ADD_F32 ? dst[j] + v[j] : v[j];
+                                if (n0 + j < a.N) { if (EPI == EPI_ADD_F32) v[j] += dst[j]; dst[j] = v[j]; }
+                        }
+                        if (EPI == EPI_ADD_F32 && a.norm_w) {
+                            // the next norm's input, and this thread's share of its row's sum of squares
+                            bf16 *xw = a.xw_out + (size_t)m * a.N + n0;
+#pragma unroll
+                            for (int j = 0; j < 16; j++)
+                                if (n0 + j < a.N) { xw[j] = __float2bfloat16_rn(v[j] * a.norm_w[n0 + j]); sq += v[j] * v[j]; }
                         }
                     }
                 }
+                if (EPI == EPI_ADD_F32 && a.norm_w && m_ok) a.ss_out[(size_t)blockIdx.y * a.M + m] = sq;
             }
         }
         tc_fence_before();
@@ -367,9 +425,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         const int S = gridDim.z;
         cluster_sync();
         if (warp >= 2) {
-            const int prow = (warp & 3) * 32 + lane, n = p0 + prow;
+            const int lg = warp & 3, prow = lg * 32 + lane, n = p0 + prow;
             const float *part = (const float *)smem;
             const int per = BN / S, c_begin = blockIdx.z * per;
+            const bool emit = EPI == EPI_ADD_F32 && a.norm_w != nullptr;
             for (int c = c_begin; c < c_begin + per; c++) {
                 const int m = q0 + c;
                 const bool in = n < a.N && m < a.M;
@@ -383,11 +442,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                 float v = 0.f;
 #pragma unroll
                 for (int z = 0; z < 8; z++) v += pz[z];                            // rank order; absent ranks add 0
+                v *= inv_s[c];
+                float sq = 0.f;
                 if (in) {
                     if (EPI == EPI_BF16) ((bf16 *)a.out)[idx] = __float2bfloat16_rn(v);
                     else if (EPI == EPI_F32) ((float *)a.out)[idx] = v;
-                    else ((float *)a.out)[idx] = res + v;
+                    else {
+                        v += res;
+                        ((float *)a.out)[idx] = v;
+                        if (emit) { a.xw_out[(size_t)m * a.N + n] = __float2bfloat16_rn(v * a.norm_w[n]); sq = v * v; }
+                    }
                 }
+                if (emit) {
+                    sq = warp_sum(sq);
+                    if (lane == 0) red_s[c - c_begin][lg] = sq;
+                }
+            }
+            if (emit) {
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (prow < per && q0 + c_begin + prow < a.M)
+                    a.ss_out[(size_t)blockIdx.x * a.M + q0 + c_begin + prow] =
+                        red_s[prow][0] + red_s[prow][1] + red_s[prow][2] + red_s[prow][3];
             }
         }
         cluster_sync();                           // no CTA leaves while its partial is still being read
@@ -460,12 +535,21 @@ static int dispatch(bool swap, int bn, const CUtensorMap &tmP, const CUtensorMap
     return FG_ERR_BAD_SIZE;
 }
 
+// Upper bound of the tiles along N that the residual-add epilogue writes sums of squares for.
+extern "C" int fg_gemm_tc_max_ss_tiles(int N) { return (N + BM - 1) / BM; }
+
 // X: [M, K] bf16 (row stride ldx), W: [N, K] bf16 (row stride ldw); epi as the enum above.
+// ss_in (optional): X holds rows x * w of a deferred RMSNorm; ss_in[t * M + m], t < ss_tiles, are partial
+// sums of squares of row m over ss_size elements, and 1/sqrt(sum / ss_size + ss_eps) scales row m's results.
+// norm_w (optional, residual-add epilogue): also write xw_out[M, N] = bf16(out * norm_w) and the partial
+// sums of squares ss_out[tile, M]; *ss_tiles_out receives the number of tiles.
 // EPI_SILU_MUL: W is [N = 2F, K] with gate and up interleaved in blocks of 64 rows; out is [M, F] bf16.
 // Returns FG_ERR_BAD_SIZE for shapes TMA cannot describe (K % 8, unaligned bases): the caller
 // then uses the plain kernel.
 extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *out, int ldc, int epi,
-                          int M, int N, int K, int force_splits, cudaStream_t stream) {
+                          int M, int N, int K, int force_splits, const float *ss_in, int ss_tiles, int ss_size,
+                          float ss_eps, const float *norm_w, void *xw_out, float *ss_out, int *ss_tiles_out,
+                          cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return FG_ERR_BAD_SIZE;
     if (epi == EPI_SILU_MUL && N % 128) return FG_ERR_BAD_SIZE;
@@ -499,7 +583,9 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
     if (e) return e;
     int esz = (epi == EPI_F32 || epi == EPI_ADD_F32) ? 4 : 2;
     int vec_ok = ((uintptr_t)out % 16 == 0) && ((size_t)ldc * esz % 16 == 0);
-    GemmArgs a{out, M, N, K, ldc, kb_per_split, vec_ok};
+    if (norm_w && (epi != EPI_ADD_F32 || !xw_out || !ss_out)) return FG_ERR_BAD_DTYPE;
+    if (ss_tiles_out) *ss_tiles_out = swap ? (int)grid.x : (int)grid.y;
+    GemmArgs a{out, M, N, K, ldc, kb_per_split, vec_ok, ss_in, ss_tiles, ss_size, ss_eps, norm_w, (bf16 *)xw_out, ss_out};
     switch (epi) {
     case EPI_BF16: return dispatch<EPI_BF16>(swap, bn, tmP, tmQ, a, grid, stream);
     case EPI_F32: return dispatch<EPI_F32>(swap, bn, tmP, tmQ, a, grid, stream);

@@ -141,9 +141,21 @@ class DecoderModel:
 
     def forward(self, batch: Batch) -> Optional[torch.Tensor]:
         """The layers over a prepared batch (pages reserved, integers on the device)."""
-        x = self.embedding.forward(batch.tokens)       # [M, E] float32 residual stream
-        for i, run in enumerate(self.spec.schedule):
-            self.blocks[run.layer].forward(x, batch, self._io[i])
+        blocks = [self.blocks[run.layer] for run in self.spec.schedule]
+
+        def entry_norm(block):
+            # the norm a block starts with, if whoever writes the residual stream may start it
+            ok = getattr(block.mixer, "supports_deferred_norm", False) and getattr(block.mixer_norm, "deferrable", False)
+            return block.mixer_norm if ok and self.runtime.dtype == torch.bfloat16 else None
+
+        first = entry_norm(blocks[0]) if blocks else None
+        if first is not None:
+            x, pending = self.embedding.forward(batch.tokens, emit_norm=first)
+        else:
+            x, pending = self.embedding.forward(batch.tokens), None      # [M, E] float32 residual stream
+        for i, block in enumerate(blocks):
+            nxt = entry_norm(blocks[i + 1]) if i + 1 < len(blocks) else None
+            pending = block.forward(x, batch, self._io[i], pending=pending, next_norm=nxt)
         if batch.want_rows is None:
             return None
         return self.head.forward(self.final_norm.forward(x, rows=batch.want_rows))

@@ -9,7 +9,7 @@ import torch
 from .lib import KernelError, check, dtype_code, lib, ptr, require_cuda, stream
 
 __all__ = [
-    "KernelError", "embed_gather", "rmsnorm", "rope_append", "silu_mul", "gemm_generic",
+    "KernelError", "embed_gather", "embed_gather_norm", "rmsnorm", "rope_append", "silu_mul", "gemm_generic",
     "attention_generic", "attention", "sample", "argmax", "decode_advance",
 ]
 
@@ -33,6 +33,23 @@ def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.
     check(lib().fg_embed_gather(ptr(table), dtype_code(table.dtype), ptr(tokens), ptr(out), M, E, stream()),
           "embed_gather")
     return out
+
+
+def embed_gather_norm(table: torch.Tensor, tokens: torch.Tensor, norm_weight: torch.Tensor, eps: float):
+    """``embed_gather`` that also starts the first RMSNorm: returns (x, DeferredNorm)."""
+    from .fast_gemm import DeferredNorm
+    require_cuda(table, tokens, norm_weight)
+    _i32(tokens, "tokens")
+    V, E = table.shape
+    M = tokens.numel()
+    if norm_weight.dtype != torch.float32 or norm_weight.numel() != E or not table.is_contiguous():
+        raise KernelError("embed_gather_norm: the norm weight must be float32 [E] and the table contiguous")
+    x = torch.empty((M, E), dtype=torch.float32, device=table.device)
+    xw = torch.empty((M, E), dtype=torch.bfloat16, device=table.device)
+    ss = torch.empty((1, M), dtype=torch.float32, device=table.device)
+    check(lib().fg_embed_gather_norm(ptr(table), dtype_code(table.dtype), ptr(tokens), ptr(x), ptr(norm_weight),
+                                     ptr(xw), ptr(ss), M, E, stream()), "embed_gather_norm")
+    return x, DeferredNorm(xw, ss, 1, E, float(eps), x, norm_weight)
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,

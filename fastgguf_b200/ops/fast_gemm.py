@@ -9,7 +9,9 @@ cluster and sums the partial tiles through distributed shared memory; it needs n
 """
 from __future__ import annotations
 
-from ctypes import c_int, c_void_p
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from dataclasses import dataclass
 from typing import Optional
 
 import torch
@@ -20,9 +22,32 @@ EPI_BF16, EPI_F32, EPI_ADD_F32, EPI_SILU_MUL = 0, 1, 2, 3
 _BAD_SIZE = 10002
 
 register_signatures("tc", {
-    "fg_gemm_tc": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "fg_gemm_tc": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                   c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "fg_gemm_tc_error": [],
+    "fg_gemm_tc_max_ss_tiles": [c_int],
 })
+
+
+@dataclass
+class DeferredNorm:
+    """An RMSNorm whose 1/rms has not been applied yet: ``xw = bf16(x * weight)`` and partial sums of
+    squares of each row of x (``ss[t, m]``, t < tiles).  A tensor-core contraction takes ``xw`` as its
+    input and applies 1/sqrt(sum / size + eps) per row in its epilogue; ``materialize`` gives the
+    normalised rows to anything else."""
+
+    xw: torch.Tensor              # [M, size] bfloat16
+    ss: torch.Tensor              # [>= tiles, M] float32
+    tiles: int
+    size: int
+    eps: float
+    x: torch.Tensor               # [M, size] float32: the rows being normalised
+    weight: torch.Tensor          # [size] float32: the norm's weight
+
+    def materialize(self) -> torch.Tensor:
+        """The normalised rows, by the RMSNorm kernel (for consumers that cannot apply 1/rms themselves)."""
+        from . import rmsnorm
+        return rmsnorm(self.x, self.weight, self.eps, torch.bfloat16)
 
 
 def pipeline_error() -> int:
@@ -32,11 +57,15 @@ def pipeline_error() -> int:
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
             out_dtype: Optional[torch.dtype] = None, accumulate: bool = False, silu: bool = False,
-            force_splits: int = 0) -> Optional[torch.Tensor]:
+            force_splits: int = 0, deferred: Optional["DeferredNorm"] = None,
+            emit_norm_weight: Optional[torch.Tensor] = None, emit_eps: float = 0.0):
     """out[m, n] (+)= sum_k a[m, k] w[n, k] on the tensor cores; None if the sizes are refused.
 
     ``silu=True``: ``w`` is [2F, K] with gate and up interleaved in blocks of 64 rows (see
     ``interleave_gate_up``) and the result is ``silu(a gate^T) * (a up^T)`` as bfloat16 [M, F].
+    ``deferred``: ``a`` is ``deferred.xw`` and the rows' 1/rms is applied in the epilogue.
+    ``emit_norm_weight`` (with ``accumulate``): also start the next RMSNorm from the updated ``out``;
+    the call then returns ``(out, DeferredNorm)``.
     """
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_tc takes bfloat16 operands")
@@ -68,11 +97,24 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = N
         out = torch.empty((M, N), dtype=dt, device=a.device)
     if out.shape != (M, N) or out.stride(1) != 1 or out.dtype != dt:
         raise KernelError(f"gemm_tc: out must be [{M}, {N}] {dt} with contiguous rows")
+    ss_in, ss_tiles, ss_size, ss_eps = None, 0, 1, 0.0
+    if deferred is not None:
+        ss_in, ss_tiles, ss_size, ss_eps = deferred.ss, deferred.tiles, deferred.size, deferred.eps
+    xw_out = ss_out = None
+    tiles_out = ctypes.c_int(0)
+    if emit_norm_weight is not None:
+        if not accumulate or emit_norm_weight.dtype != torch.float32 or emit_norm_weight.numel() != N:
+            raise KernelError("gemm_tc: emitting a norm needs the residual-add epilogue and a float32 weight [N]")
+        xw_out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+        ss_out = torch.empty((int(lib("tc").fg_gemm_tc_max_ss_tiles(N)), M), dtype=torch.float32, device=a.device)
     code = lib("tc").fg_gemm_tc(ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out.stride(0), epi,
-                                M, rows, K, int(force_splits), stream())
+                                M, rows, K, int(force_splits), ptr(ss_in), ss_tiles, ss_size, float(ss_eps),
+                                ptr(emit_norm_weight), ptr(xw_out), ptr(ss_out), ctypes.byref(tiles_out), stream())
     if code == _BAD_SIZE:
         return None
     check(code, "gemm_tc")
+    if emit_norm_weight is not None:
+        return out, DeferredNorm(xw_out, ss_out, int(tiles_out.value), N, float(emit_eps), out, emit_norm_weight)
     return out
 
 
@@ -80,11 +122,12 @@ class _Plan:
     def __init__(self, weight: torch.Tensor):
         self.weight = weight
 
-    def run(self, a, out=None, out_dtype=None, accumulate=False):
-        return gemm_tc(a, self.weight, out=out, out_dtype=out_dtype, accumulate=accumulate)
+    def run(self, a, out=None, out_dtype=None, accumulate=False, deferred=None, emit_norm_weight=None, emit_eps=0.0):
+        return gemm_tc(a, self.weight, out=out, out_dtype=out_dtype, accumulate=accumulate, deferred=deferred,
+                       emit_norm_weight=emit_norm_weight, emit_eps=emit_eps)
 
-    def run_silu(self, a):
-        return gemm_tc(a, self.weight, silu=True)
+    def run_silu(self, a, deferred=None):
+        return gemm_tc(a, self.weight, silu=True, deferred=deferred)
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:

@@ -73,6 +73,8 @@ def require_cuda(*tensors) -> None:
 _SIGNATURES = {
     "core": {
         "fg_embed_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "fg_embed_gather_norm": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                 c_void_p],
         "fg_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
         "fg_rope_append": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],

@@ -22,6 +22,9 @@ from .linear import Linear
 
 
 class GQAAttention(Mixer):
+    #: takes a ``DeferredNorm`` as input and can start the next norm from its output projection
+    supports_deferred_norm = True
+
     def __init__(self, runtime: Runtime, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  position=None, scale: Optional[float] = None, window: Optional[int] = None):
         super().__init__(runtime)
@@ -56,7 +59,7 @@ class GQAAttention(Mixer):
         self.q_only = self.qkv.rows(0, self.q_dim)
         self.o = Linear(tensors["o_proj.weight"].contiguous())
 
-    def forward(self, xn: torch.Tensor, batch, io: LayerIO, residual: torch.Tensor) -> None:
+    def forward(self, xn, batch, io: LayerIO, residual: torch.Tensor, emit_norm=None):
         proj = self.qkv if io.write_cache else self.q_only
         qkv = proj.forward(xn, out_dtype=self.runtime.dtype)
         table = batch.block_tables[io.group]
@@ -68,7 +71,10 @@ class GQAAttention(Mixer):
             raise NotImplementedError("attention without a position encoding is not built")
         attn = ops.attention(qkv, batch, table, io.k_pool, io.v_pool, self.n_heads, self.n_kv_heads,
                              self.head_dim, self.scale, self.window or 0)
-        self.o.forward(attn, out=residual, accumulate=True)
+        if emit_norm is None:
+            self.o.forward(attn, out=residual, accumulate=True)
+            return None
+        return self.o.forward(attn, out=residual, accumulate=True, emit_norm=emit_norm)[1]
 
 
 register_mixer("gqa_attention", GQAAttention)

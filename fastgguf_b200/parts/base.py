@@ -18,7 +18,12 @@ Mixer           ``cache_request()``                   -> CacheRequest or None (k
                 ``state_request()``                   -> StateRequest or None (fixed-size state)
                 ``forward(xn, batch, io, residual)``  adds its output into ``residual`` ([M, E] f32)
 FeedForward     ``forward(xn, batch, residual)``      adds its output into ``residual``
-Block           ``forward(x, batch, io)``             runs norm/mixer/norm/feed-forward on ``x`` in place
+Block           ``forward(x, batch, io, pending, next_norm)``  runs norm/mixer/norm/feed-forward on ``x`` in place
+
+Optional protocol (an optimisation, never needed for correctness): a norm with ``deferrable = True``
+(and ``weight``, ``eps``) can be *started* by the contraction that produces its input and *finished*
+by the contraction that consumes it; mixers and feed-forwards that set
+``supports_deferred_norm = True`` accept a ``DeferredNorm`` as ``xn`` and an ``emit_norm=`` keyword.
 """
 from __future__ import annotations
 
@@ -119,7 +124,10 @@ class Block:
         self.mixer, self.feed_forward = mixer, feed_forward
         self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
 
-    def forward(self, x: torch.Tensor, batch, io: LayerIO) -> None:
+    def forward(self, x: torch.Tensor, batch, io: LayerIO, pending=None, next_norm=None):
+        """Run the block on ``x`` in place.  ``pending`` / ``next_norm`` / the return value let a
+        block hand a started norm to the next one (see ``PreNormBlock``); a block may ignore them
+        and return None."""
         raise NotImplementedError
 
 

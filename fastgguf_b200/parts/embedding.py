@@ -29,8 +29,14 @@ class TokenEmbedding(Part):
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"].contiguous()
 
-    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
-        return ops.embed_gather(self.weight, tokens)
+    def forward(self, tokens: torch.Tensor, emit_norm=None):
+        """The float32 residual stream [M, E]; with ``emit_norm`` (a deferrable norm) also that
+        norm started from it: returns ``(x, DeferredNorm or None)``."""
+        if emit_norm is None:
+            return ops.embed_gather(self.weight, tokens)
+        if self.runtime.dtype == torch.bfloat16 and self.weight.is_cuda:
+            return ops.embed_gather_norm(self.weight, tokens, emit_norm.weight, emit_norm.eps)
+        return ops.embed_gather(self.weight, tokens), None
 
 
 class LMHead(Part):

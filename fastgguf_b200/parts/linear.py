@@ -33,11 +33,24 @@ class Linear:
         """The sub-matrix of output rows [start, stop) (shares storage)."""
         return Linear(self.weight[start:stop])
 
-    def forward(self, a: torch.Tensor, out: Optional[torch.Tensor] = None,
-                out_dtype: Optional[torch.dtype] = None, accumulate: bool = False) -> torch.Tensor:
-        """out[m, n] (+)= sum_k a[m, k] W[n, k].  ``accumulate`` adds into a float32 ``out``."""
-        if self._fast is not None and a.dtype == torch.bfloat16:
-            res = self._fast.run(a, out=out, out_dtype=out_dtype, accumulate=accumulate)
+    def forward(self, a, out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+                accumulate: bool = False, emit_norm=None):
+        """out[m, n] (+)= sum_k a[m, k] W[n, k].  ``accumulate`` adds into a float32 ``out``.
+
+        ``a`` may be a ``DeferredNorm`` (rows x * w whose 1/rms the tensor-core kernel applies).
+        ``emit_norm`` (a norm part with ``weight``, ``eps``; needs ``accumulate``): the call returns
+        ``(out, DeferredNorm or None)`` - the next norm started from the updated ``out`` when the
+        tensor-core kernel ran, None when the plain kernel did."""
+        from ..ops.fast_gemm import DeferredNorm
+        deferred = a if isinstance(a, DeferredNorm) else None
+        if self._fast is not None and (deferred is not None or a.dtype == torch.bfloat16):
+            res = self._fast.run(deferred.xw if deferred is not None else a, out=out, out_dtype=out_dtype,
+                                 accumulate=accumulate, deferred=deferred,
+                                 emit_norm_weight=emit_norm.weight if emit_norm is not None else None,
+                                 emit_eps=emit_norm.eps if emit_norm is not None else 0.0)
             if res is not None:
                 return res
-        return ops.gemm_generic(a, self.weight, out=out, out_dtype=out_dtype, accumulate=accumulate)
+        if deferred is not None:
+            a = deferred.materialize()
+        res = ops.gemm_generic(a, self.weight, out=out, out_dtype=out_dtype, accumulate=accumulate)
+        return (res, None) if emit_norm is not None else res

@@ -15,6 +15,8 @@ from .linear import Linear
 
 
 class SwiGLU(FeedForward):
+    supports_deferred_norm = True
+
     def __init__(self, runtime: Runtime, hidden_size: int, d_ff: int):
         super().__init__(runtime)
         self.hidden_size, self.d_ff = hidden_size, d_ff
@@ -41,14 +43,19 @@ class SwiGLU(FeedForward):
             self.gate_up = Linear(torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous())
         self.down = Linear(tensors["down_proj.weight"].contiguous())
 
-    def forward(self, xn: torch.Tensor, batch, residual: torch.Tensor) -> None:
+    def forward(self, xn, batch, residual: torch.Tensor, emit_norm=None):
+        from ..ops.fast_gemm import DeferredNorm
+        deferred = xn if isinstance(xn, DeferredNorm) else None
         if self.fused is not None:
-            t = self.fused.run_silu(xn)
+            t = self.fused.run_silu(deferred.xw if deferred is not None else xn, deferred=deferred)
             if t is None:
                 raise ops.KernelError("the fused gate/up kernel refused a shape it was planned for")
         else:
             t = ops.silu_mul(self.gate_up.forward(xn, out_dtype=self.runtime.dtype))
-        self.down.forward(t, out=residual, accumulate=True)
+        if emit_norm is None:
+            self.down.forward(t, out=residual, accumulate=True)
+            return None
+        return self.down.forward(t, out=residual, accumulate=True, emit_norm=emit_norm)[1]
 
 
 register_feed_forward("swiglu", SwiGLU)

@@ -14,6 +14,9 @@ from .base import Norm, Runtime, TensorSpec, register_norm
 
 
 class RMSNorm(Norm):
+    #: a contraction that follows this norm may apply its 1/rms itself (see ``ops.fast_gemm.DeferredNorm``)
+    deferrable = True
+
     def __init__(self, runtime: Runtime, size: int, eps: float):
         super().__init__(runtime)
         self.size, self.eps = int(size), float(eps)
