@@ -407,9 +407,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                         if (EPI == EPI_ADD_F32 && a.norm_w) {
                             // the next norm's input, and this thread's share of its row's sum of squares
                             bf16 *xw = a.xw_out + (size_t)m * a.N + n0;
+                            if (full && (a.N & 7) == 0) {
+                                uint32_t w[8];
 #pragma unroll
-                            for (int j = 0; j < 16; j++)
-                                if (n0 + j < a.N) { xw[j] = __float2bfloat16_rn(v[j] * a.norm_w[n0 + j]); sq += v[j] * v[j]; }
+                                for (int j = 0; j < 4; j++) {
+                                    float4 g = ((const float4 *)(a.norm_w + n0))[j];
+                                    __nv_bfloat162 t0 = __floats2bfloat162_rn(v[4 * j] * g.x, v[4 * j + 1] * g.y);
+                                    __nv_bfloat162 t1 = __floats2bfloat162_rn(v[4 * j + 2] * g.z, v[4 * j + 3] * g.w);
+                                    w[2 * j] = *(uint32_t *)&t0; w[2 * j + 1] = *(uint32_t *)&t1;
+                                }
+                                ((uint4 *)xw)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                                ((uint4 *)xw)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+#pragma unroll
+                                for (int j = 0; j < 16; j++) sq += v[j] * v[j];
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 16; j++)
+                                    if (n0 + j < a.N) { xw[j] = __float2bfloat16_rn(v[j] * a.norm_w[n0 + j]); sq += v[j] * v[j]; }
+                            }
                         }
                     }
                 }

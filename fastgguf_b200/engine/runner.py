@@ -71,8 +71,18 @@ class DecodeGraph:
         torch.cuda.synchronize()
         self.tokens.zero_(); self.positions.zero_()
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self._run()
+        # Objects of earlier engines (graphs, pinned buffers, events) must not be finalised in the middle
+        # of the capture: their CUDA calls are not allowed while a stream captures.
+        import gc
+        gc.collect()
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph, capture_error_mode="relaxed"):
+                self._run()
+        finally:
+            if was_enabled:
+                gc.enable()
 
     def _run(self) -> None:
         logits = self.model.forward(self.batch)
