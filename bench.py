@@ -34,6 +34,12 @@ LLAMA_3_2_1B = {
     "max_position_embeddings": 131072, "tie_word_embeddings": True, "hidden_act": "silu",
     "bos_token_id": 128000, "eos_token_id": 128001,
 }
+LLAMA_3_2_3B = dict(LLAMA_3_2_1B, hidden_size=3072, num_hidden_layers=28, num_attention_heads=24, head_dim=128)
+LLAMA_3_1_8B = dict(LLAMA_3_2_1B, hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, head_dim=128,
+                    intermediate_size=14336, tie_word_embeddings=False,
+                    rope_scaling=dict(LLAMA_3_2_1B["rope_scaling"], factor=8.0))
+MODELS = {"1b": ("Llama-3.2-1B shapes", LLAMA_3_2_1B), "3b": ("Llama-3.2-3B shapes", LLAMA_3_2_3B),
+          "8b": ("Llama-3.1-8B shapes", LLAMA_3_1_8B)}
 CONTEXT = 4096
 PROMPT_MIN, PROMPT_MAX = 128, 1024
 PREFILL_TOKENS = 2048
@@ -99,7 +105,7 @@ def layer_weight_bytes(c):
 
 def decode_step_bytes(c, layers, context_tokens):
     """Bytes one decode step must read: every weight it uses once, and the cache of the live requests."""
-    head = 2 * c["vocab_size"] * c["hidden_size"] + 2 * c["hidden_size"]
+    head = 2 * c["vocab_size"] * c["hidden_size"] + 2 * c["hidden_size"]      # the head matrix (tied or not) is read once
     kv = context_tokens * layers * 2 * c["num_key_value_heads"] * c["head_dim"] * 2
     return layers * layer_weight_bytes(c) + head + kv
 
@@ -120,6 +126,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--model", default="1b", choices=sorted(MODELS), help="layer sizes (default: the 1B configuration)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill measurement")
@@ -144,7 +151,8 @@ def main():
 
     W = max(3, args.warmup)
     K = args.steps
-    c = dict(LLAMA_3_2_1B)
+    model_name, base = MODELS[args.model]
+    c = dict(base)
     full_layers = c["num_hidden_layers"]
     if args.layers:
         c["num_hidden_layers"] = args.layers
@@ -215,14 +223,15 @@ def main():
                "d2h_bytes_per_step": round((s1["d2h_bytes"] - s0["d2h_bytes"]) / n_steps, 1)}
 
     rec = {
-        "metric": "decode tokens/s (Llama 3.2 1B shapes, bf16, batch %d, context %d)" % (args.batch, CONTEXT),
+        "metric": "decode tokens/s (%s, bf16, batch %d, context %d)" % (model_name, args.batch, CONTEXT),
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), uniform random token ids",
         "config": {
-            "model": "Llama-3.2-1B shapes", "layers": layers, "layers_full": full_layers, "hidden": c["hidden_size"],
+            "model": model_name, "layers": layers, "layers_full": full_layers, "hidden": c["hidden_size"],
             "heads": c["num_attention_heads"], "kv_heads": c["num_key_value_heads"], "head_dim": c["head_dim"],
-            "d_ff": c["intermediate_size"], "vocab": c["vocab_size"], "tied_head": True, "rope": "llama3 x32 theta 5e5",
+            "d_ff": c["intermediate_size"], "vocab": c["vocab_size"], "tied_head": c["tie_word_embeddings"],
+            "rope": "llama3 x%g theta 5e5" % c["rope_scaling"]["factor"],
             "global_batch": args.batch, "seq_len": CONTEXT, "prompt_lens": "%d-%d unequal" % (PROMPT_MIN, PROMPT_MAX),
             "mean_context": round(mean_ctx / args.batch, 1), "parallelism": "single GPU",
             "l2": "inputs larger than L2: each step reads %.2f GB" % (step_bytes / 1e9),

@@ -146,6 +146,111 @@ __device__ __forceinline__ float inv_rms(const GemmArgs &a, int m) {
     return 1.0f / sqrtf(s / (float)a.ss_size + a.ss_eps);
 }
 
+// Epilogue of a token-major tile: thread = token row p0 + prow, columns = weight rows q0 .. q0 + BN.
+// `qt` is the index of the tile along the features (row of ss_out it writes).
+template <int BN, int EPI>
+__device__ __forceinline__ void epilogue_token_major(const GemmArgs &a, uint32_t trow, int p0, int q0, int qt, int prow) {
+    // thread = token row, columns = weight rows (features): runs of 16 consecutive outputs
+    const int m = p0 + prow;
+    const bool m_ok = m < a.M;
+    const float iv = (a.ss_in && m_ok) ? inv_rms(a, m) : 1.0f;
+    if (EPI == EPI_SILU_MUL) {
+        const int F = a.N >> 1;
+        for (int blk = 0; blk < BN / 128; blk++) {
+            for (int c0 = 0; c0 < 64; c0 += 16) {
+                float g[16], u[16];
+                tc_ld16(trow + blk * 128 + c0, g);
+                tc_ld16(trow + blk * 128 + 64 + c0, u);
+                const int f0 = ((q0 + blk * 128) >> 1) + c0;
+                if (!m_ok || f0 >= F) continue;
+                bf16 *dst = (bf16 *)a.out + (size_t)m * a.ldc + f0;
+                if (a.vec_ok && f0 + 16 <= F) {
+                    uint32_t w[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        __nv_bfloat162 t = __floats2bfloat162_rn(silu_mul(g[2 * j] * iv, u[2 * j] * iv),
+                                                                 silu_mul(g[2 * j + 1] * iv, u[2 * j + 1] * iv));
+                        w[j] = *(uint32_t *)&t;
+                    }
+                    ((uint4 *)dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                    ((uint4 *)dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++)
+                        if (f0 + j < F) dst[j] = __float2bfloat16_rn(silu_mul(g[j] * iv, u[j] * iv));
+                }
+            }
+        }
+    } else {
+        float sq = 0.f;
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+            float v[16];
+            tc_ld16(trow + c0, v);
+            const int n0 = q0 + c0;
+            if (!m_ok || n0 >= a.N) continue;
+#pragma unroll
+            for (int j = 0; j < 16; j++) v[j] *= iv;
+            const size_t idx = (size_t)m * a.ldc + n0;
+            const bool full = a.vec_ok && n0 + 16 <= a.N;
+            if (EPI == EPI_BF16) {
+                bf16 *dst = (bf16 *)a.out + idx;
+                if (full) {
+                    uint32_t w[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                        w[j] = *(uint32_t *)&t;
+                    }
+                    ((uint4 *)dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                    ((uint4 *)dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) if (n0 + j < a.N) dst[j] = __float2bfloat16_rn(v[j]);
+                }
+            } else {
+                float *dst = (float *)a.out + idx;
+                if (full) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        if (EPI == EPI_ADD_F32) {
+                            float4 o = ((float4 *)dst)[j];
+                            v[4 * j] += o.x; v[4 * j + 1] += o.y; v[4 * j + 2] += o.z; v[4 * j + 3] += o.w;
+                        }
+                        ((float4 *)dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++)
+                        if (n0 + j < a.N) { if (EPI == EPI_ADD_F32) v[j] += dst[j]; dst[j] = v[j]; }
+                }
+                if (EPI == EPI_ADD_F32 && a.norm_w) {
+                    // the next norm's input, and this thread's share of its row's sum of squares
+                    bf16 *xw = a.xw_out + (size_t)m * a.N + n0;
+                    if (full && (a.N & 7) == 0) {
+                        uint32_t w[8];
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            float4 g = ((const float4 *)(a.norm_w + n0))[j];
+                            __nv_bfloat162 t0 = __floats2bfloat162_rn(v[4 * j] * g.x, v[4 * j + 1] * g.y);
+                            __nv_bfloat162 t1 = __floats2bfloat162_rn(v[4 * j + 2] * g.z, v[4 * j + 3] * g.w);
+                            w[2 * j] = *(uint32_t *)&t0; w[2 * j + 1] = *(uint32_t *)&t1;
+                        }
+                        ((uint4 *)xw)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                        ((uint4 *)xw)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+#pragma unroll
+                        for (int j = 0; j < 16; j++) sq += v[j] * v[j];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            if (n0 + j < a.N) { xw[j] = __float2bfloat16_rn(v[j] * a.norm_w[n0 + j]); sq += v[j] * v[j]; }
+                    }
+                }
+            }
+        }
+        if (EPI == EPI_ADD_F32 && a.norm_w && m_ok) a.ss_out[(size_t)qt * a.M + m] = sq;
+    }
+}
+
 template <int BN, int STAGES, int EPI, bool SWAP>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, GemmArgs a) {
@@ -331,105 +436,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                 }
             }
         } else if (ok) {
-            // thread = token row, columns = weight rows (features): runs of 16 consecutive outputs
-            const int m = p0 + prow;
-            const bool m_ok = m < a.M;
-            const float iv = (a.ss_in && m_ok) ? inv_rms(a, m) : 1.0f;
-            if (EPI == EPI_SILU_MUL) {
-                const int F = a.N >> 1;
-                for (int blk = 0; blk < BN / 128; blk++) {
-                    for (int c0 = 0; c0 < 64; c0 += 16) {
-                        float g[16], u[16];
-                        tc_ld16(trow + blk * 128 + c0, g);
-                        tc_ld16(trow + blk * 128 + 64 + c0, u);
-                        const int f0 = ((q0 + blk * 128) >> 1) + c0;
-                        if (!m_ok || f0 >= F) continue;
-                        bf16 *dst = (bf16 *)a.out + (size_t)m * a.ldc + f0;
-                        if (a.vec_ok && f0 + 16 <= F) {
-                            uint32_t w[8];
-#pragma unroll
-                            for (int j = 0; j < 8; j++) {
-                                __nv_bfloat162 t = __floats2bfloat162_rn(silu_mul(g[2 * j] * iv, u[2 * j] * iv),
-                                                                         silu_mul(g[2 * j + 1] * iv, u[2 * j + 1] * iv));
-                                w[j] = *(uint32_t *)&t;
-                            }
-                            ((uint4 *)dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                            ((uint4 *)dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; j++)
-                                if (f0 + j < F) dst[j] = __float2bfloat16_rn(silu_mul(g[j] * iv, u[j] * iv));
-                        }
-                    }
-                }
-            } else {
-                float sq = 0.f;
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    float v[16];
-                    tc_ld16(trow + c0, v);
-                    const int n0 = q0 + c0;
-                    if (!m_ok || n0 >= a.N) continue;
-#pragma unroll
-                    for (int j = 0; j < 16; j++) v[j] *= iv;
-                    const size_t idx = (size_t)m * a.ldc + n0;
-                    const bool full = a.vec_ok && n0 + 16 <= a.N;
-                    if (EPI == EPI_BF16) {
-                        bf16 *dst = (bf16 *)a.out + idx;
-                        if (full) {
-                            uint32_t w[8];
-#pragma unroll
-                            for (int j = 0; j < 8; j++) {
-                                __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                                w[j] = *(uint32_t *)&t;
-                            }
-                            ((uint4 *)dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                            ((uint4 *)dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; j++) if (n0 + j < a.N) dst[j] = __float2bfloat16_rn(v[j]);
-                        }
-                    } else {
-                        float *dst = (float *)a.out + idx;
-                        if (full) {
-#pragma unroll
-                            for (int j = 0; j < 4; j++) {
-                                if (EPI == EPI_ADD_F32) {
-                                    float4 o = ((float4 *)dst)[j];
-                                    v[4 * j] += o.x; v[4 * j + 1] += o.y; v[4 * j + 2] += o.z; v[4 * j + 3] += o.w;
-                                }
-                                ((float4 *)dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; j++)
-                                if (n0 + j < a.N) { if (EPI == EPI_ADD_F32) v[j] += dst[j]; dst[j] = v[j]; }
-                        }
-                        if (EPI == EPI_ADD_F32 && a.norm_w) {
-                            // the next norm's input, and this thread's share of its row's sum of squares
-                            bf16 *xw = a.xw_out + (size_t)m * a.N + n0;
-                            if (full && (a.N & 7) == 0) {
-                                uint32_t w[8];
-#pragma unroll
-                                for (int j = 0; j < 4; j++) {
-                                    float4 g = ((const float4 *)(a.norm_w + n0))[j];
-                                    __nv_bfloat162 t0 = __floats2bfloat162_rn(v[4 * j] * g.x, v[4 * j + 1] * g.y);
-                                    __nv_bfloat162 t1 = __floats2bfloat162_rn(v[4 * j + 2] * g.z, v[4 * j + 3] * g.w);
-                                    w[2 * j] = *(uint32_t *)&t0; w[2 * j + 1] = *(uint32_t *)&t1;
-                                }
-                                ((uint4 *)xw)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                                ((uint4 *)xw)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-#pragma unroll
-                                for (int j = 0; j < 16; j++) sq += v[j] * v[j];
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 16; j++)
-                                    if (n0 + j < a.N) { xw[j] = __float2bfloat16_rn(v[j] * a.norm_w[n0 + j]); sq += v[j] * v[j]; }
-                            }
-                        }
-                    }
-                }
-                if (EPI == EPI_ADD_F32 && a.norm_w && m_ok) a.ss_out[(size_t)blockIdx.y * a.M + m] = sq;
-            }
+            epilogue_token_major<BN, EPI>(a, trow, p0, q0, blockIdx.y, prow);
         }
         tc_fence_before();
     }
@@ -489,6 +496,122 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     }
 }
 
+// ---------------------------------------------------------------------------- prefill: persistent tiles
+// Token-major tiles (P = 128 token rows, Q = BN weight rows) for many rows.  One CTA per SM walks
+// the tiles with a stride of the grid; two accumulators in tensor memory alternate, so the
+// epilogue of a tile (tcgen05.ld, conversion, stores) runs while the MMAs of the next tile fill the
+// other accumulator.  Consecutive CTAs take tiles of the same weight rows, so those stay in L2.
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, GemmArgs a,
+                       int n_pt, int n_tiles) {
+    constexpr int P_BYTES = BM * BK * 2, Q_BYTES = BN * BK * 2;
+    constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
+    constexpr int TMEM_COLS = 2 * BN;             // two accumulators: 256 or 512 columns
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+    __shared__ uint32_t tmem_base_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nkb = (a.K + BK - 1) / BK;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+    const uint32_t tfull0 = smem_u32(&bars[2 * STAGES]), tempty0 = smem_u32(&bars[2 * STAGES + 2]);
+    const uint32_t smem0 = smem_u32(smem);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int i = 0; i < 2; i++) { mbar_init(tfull0 + 8 * i, 1); mbar_init(tempty0 + 8 * i, 4); }   // 4 epilogue warps
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+    pdl_launch_dependents();
+    if (threadIdx.x == 32) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmP) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmQ) : "memory");
+    }
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            pdl_wait();
+            int it = 0, issued = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int p0 = (tile % n_pt) * BM, q0 = (tile / n_pt) * BN;
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    int s = it % STAGES;
+                    if (!mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) { raise_error(1); ok = false; break; }
+                    uint32_t dst = smem0 + s * STAGE_BYTES, bar = full0 + 8 * s;
+                    mbar_expect_tx(bar, STAGE_BYTES);
+                    tma_load_2d(dst, &tmP, kb * BK, p0, bar);
+                    tma_load_2d(dst + P_BYTES, &tmQ, kb * BK, q0, bar);
+                    issued = it + 1;
+                }
+            }
+            for (int j = max(0, issued - STAGES); j < issued; j++)      // copies in flight land before the CTA exits
+                mbar_wait(full0 + 8 * (j % STAGES), (j / STAGES) & 1);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(BM, BN);
+            int it = 0, i = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, i++) {
+                const int acc = i & 1;
+                // the epilogue must have emptied this accumulator (its use before the last one)
+                if (!mbar_wait(tempty0 + 8 * acc, ((i >> 1) & 1) ^ 1)) { raise_error(4); break; }
+                tc_fence_after();
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    int s = it % STAGES;
+                    if (!mbar_wait(full0 + 8 * s, (it / STAGES) & 1)) { raise_error(2); ok = false; break; }
+                    tc_fence_after();
+                    uint32_t sa = smem0 + s * STAGE_BYTES;
+                    uint64_t pdesc = make_smem_desc(sa), qdesc = make_smem_desc(sa + P_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
+                        tc_mma_bf16(tmem_base + acc * BN, pdesc + koff, qdesc + koff, idesc, (kb | k) != 0);
+                    }
+                    tc_commit(empty0 + 8 * s);
+                }
+                tc_commit(tfull0 + 8 * acc);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        pdl_wait();
+        const int lg = warp & 3, prow = lg * 32 + lane;
+        int i = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, i++) {
+            const int acc = i & 1;
+            const int pt = tile % n_pt, qt = tile / n_pt;
+            if (!mbar_wait(tfull0 + 8 * acc, (i >> 1) & 1)) { raise_error(3); break; }
+            tc_fence_after();
+            const uint32_t trow = tmem_base + ((uint32_t)(lg * 32) << 16) + acc * BN;
+            epilogue_token_major<BN, EPI>(a, trow, pt * BM, qt * BN, qt, prow);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tempty0 + 8 * acc) : "memory");
+        }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 // ---------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -533,6 +656,25 @@ static int launch(const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs
                              (int)grid.z, tmP, tmQ, a);
 }
 
+template <int BN, int STAGES, int EPI>
+static int launch_prefill(const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs &a, cudaStream_t stream) {
+    constexpr int smem = STAGES * (BM + BN) * BK * 2 + 1024;
+    static bool configured = false;
+    static int n_sm = 0;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_prefill_kernel<BN, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+        configured = true;
+    }
+    int n_pt = (a.M + BM - 1) / BM, n_tiles = n_pt * ((a.N + BN - 1) / BN);
+    dim3 grid(n_tiles < n_sm ? n_tiles : n_sm);
+    return fg_launch(gemm_tc_prefill_kernel<BN, STAGES, EPI>, grid, dim3(GEMM_THREADS), (size_t)smem, stream, tmP, tmQ, a,
+                     n_pt, n_tiles);
+}
+
 template <int EPI>
 static int dispatch(bool swap, int bn, const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs &a, dim3 grid, cudaStream_t st) {
     if (swap) {
@@ -543,8 +685,8 @@ static int dispatch(bool swap, int bn, const CUtensorMap &tmP, const CUtensorMap
         }
     } else {
         switch (bn) {
-        case 128: return launch<128, 6, EPI, false>(tmP, tmQ, a, grid, st);
-        case 256: return launch<256, 4, EPI, false>(tmP, tmQ, a, grid, st);
+        case 128: return launch_prefill<128, 6, EPI>(tmP, tmQ, a, st);
+        case 256: return launch_prefill<256, 4, EPI>(tmP, tmQ, a, st);
         }
     }
     return FG_ERR_BAD_SIZE;
