@@ -1,0 +1,403 @@
+// Prefill attention over the paged bf16 cache on the 5th-generation tensor cores (tcgen05):
+// S = Q K^T and O = P V run as 128-row MMAs with accumulators in tensor memory, K/V pages arrive
+// by TMA, and the softmax works one thread per row straight out of tensor memory.
+//
+// Reference role and formulas: as attention_prefill.cu (fastgguf.c:5022-5039, :3273-3326).
+//
+// Grid (query tile, kv head x head chunk, sequence).  A CTA owns 128 rows = TQ consecutive new
+// tokens x Gc query heads of one KV head (Gc = min(G, 16), row r = token r / Gc, head r % Gc) and
+// walks the sequence's pages two at a time (128 keys):
+//
+//   warp 0 (one lane)  TMA: the K and V tiles of two pages into one of two stages (128B swizzle)
+//   warp 1 (one lane)  MMA: S = Q K^T (128 x 128 x HD), then, once P is in shared memory,
+//                      O_tile = P V (128 x HD x 128); V is the MN-major operand (its rows are keys)
+//   warps 2-5          thread = row: read S from tensor memory, scale, mask, running max and sum in
+//                      f32 (base-2 exponent), write P as bf16 into swizzled shared memory, then add
+//                      O_tile into the row's f32 accumulator in registers, rescaled by the change of
+//                      the maximum; at the end divide by the sum and store the row.
+//
+// Every mbarrier wait is bounded (error flag, tensor memory freed, copies in flight awaited).
+#include <cuda.h>
+#include "common.cuh"
+
+#define FG_ERR_PIPELINE 10003
+#define FG_ERR_TENSORMAP 10004
+#define PAGE 64
+#define ROWS 128
+#define KEYS 128                     // keys per iteration: two pages
+#define ATT_THREADS 192
+#define WAIT_LIMIT_CYCLES 2000000000ll
+#define LOG2E 1.4426950408889634f
+
+__device__ int g_attn_error = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    long long t0 = clock64();
+    for (;;) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// K-major operand tile (rows of 128 B, 8-row groups 1024 B apart), 128-byte swizzle
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand tile: rows of 128 B hold 64 consecutive N elements of one k; groups of 8 k are
+// 1024 B apart (stride offset); blocks of 64 N elements are `mn_block_bytes` apart (leading offset)
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr, uint32_t mn_block_bytes) {
+    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)((mn_block_bytes >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// instruction descriptor: bf16 x bf16 -> f32, M x N; b_mn_major: B's rows are k (keys)
+__device__ __forceinline__ uint32_t make_idesc(int M, int N, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) |
+           ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void raise_error(int role) { atomicCAS(&g_attn_error, 0, (FG_ERR_PIPELINE << 8) | role); }
+
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                       const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out, int ldo,
+                       const int *__restrict__ cu_rows, const int *__restrict__ seq_start,
+                       const int *__restrict__ block_table, int table_width, int KV, int G, float scale_log2, int window) {
+    constexpr int CH = HD / 64;                        // 64-wide chunks of the head dimension
+    constexpr int Q_BYTES = ROWS * HD * 2, KV_TILE = KEYS * HD * 2;
+    constexpr int STAGE = 2 * KV_TILE;                 // K tile then V tile
+    constexpr uint32_t TMEM_COLS = 256;                // S: columns 0..127, O tile: 128..128+HD
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bars[7];
+    __shared__ uint32_t tmem_base_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int Gc = G < 16 ? G : 16, TQ = ROWS / Gc, chunks = (G + Gc - 1) / Gc;
+    const int kvh = blockIdx.y / chunks, g0 = (blockIdx.y % chunks) * Gc;
+    const int b = blockIdx.z;
+    const uint32_t qs = smem_u32(smem), st0 = qs + Q_BYTES, ps = st0 + 2 * STAGE;
+    const uint32_t kv_full = smem_u32(&bars[0]), kv_empty = smem_u32(&bars[2]);
+    const uint32_t s_full = smem_u32(&bars[4]), p_full = smem_u32(&bars[5]), o_full = smem_u32(&bars[6]);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2; i++) { mbar_init(kv_full + 8 * i, 1); mbar_init(kv_empty + 8 * i, 1); }
+        mbar_init(s_full, 1); mbar_init(p_full, ROWS); mbar_init(o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    pdl_launch_dependents();
+    pdl_wait();                                        // q and the cache come from the kernels before
+    const int row0 = cu_rows[b], n_tok = cu_rows[b + 1] - row0, start = seq_start[b];
+    const int q0 = blockIdx.x * TQ;
+    const bool active = q0 < n_tok;                    // a CTA past the sequence's tokens only sets up and leaves
+    const int tq = active ? min(TQ, n_tok - q0) : 0;
+    const int tile_hi = start + q0 + tq - 1;
+    const int tile_lo = (window > 0 && start + q0 - window + 1 > 0) ? start + q0 - window + 1 : 0;
+    const int p_begin = tile_lo / PAGE, p_end = tile_hi / PAGE + 1;
+    const int n_iter = active ? (p_end - p_begin + 1) / 2 : 0;
+    const int *bt = block_table + (size_t)b * table_width;
+
+    // ---- Q tile -> shared memory, swizzled like a TMA tile (rows past the valid ones are zero)
+    int t_row = 0, g_row = 0, hi = -1, lo = 0;
+    bool valid = false;
+    if (warp >= 2) {
+        const int r = (warp & 3) * 32 + lane;
+        t_row = r / Gc; g_row = g0 + r % Gc;
+        valid = t_row < tq && g_row < G;
+        hi = valid ? start + q0 + t_row : -1;
+        lo = (window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0;
+        const bf16 *src = q + (size_t)(row0 + q0 + t_row) * ldq + (size_t)(kvh * G + g_row) * HD;
+#pragma unroll
+        for (int c = 0; c < HD / 8; c++) {
+            uint4 v = valid ? *(const uint4 *)(src + c * 8) : make_uint4(0, 0, 0, 0);
+            uint32_t dst = qs + (c >> 3) * (ROWS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int issued = 0;
+            for (int j = 0; j < n_iter; j++) {
+                const int s = j & 1;
+                if (!mbar_wait(kv_empty + 8 * s, ((j >> 1) & 1) ^ 1)) { raise_error(1); break; }
+                const uint32_t bar = kv_full + 8 * s, kdst = st0 + s * STAGE, vdst = kdst + KV_TILE;
+                mbar_expect_tx(bar, STAGE);
+                for (int h = 0; h < 2; h++) {
+                    int pg = min(p_begin + 2 * j + h, p_end - 1);          // a page past the end is masked anyway
+                    int y = (bt[pg] * KV + kvh) * PAGE;
+                    for (int c = 0; c < CH; c++) {
+                        tma_load_2d(kdst + c * (KEYS * 128) + h * (PAGE * 128), &tmK, c * 64, y, bar);
+                        tma_load_2d(vdst + c * (KEYS * 128) + h * (PAGE * 128), &tmV, c * 64, y, bar);
+                    }
+                }
+                issued = j + 1;
+            }
+            for (int j = max(0, issued - 2); j < issued; j++) mbar_wait(kv_full + 8 * (j & 1), (j >> 1) & 1);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0 && n_iter > 0) {
+            const uint32_t idesc_s = make_idesc(ROWS, KEYS, 0), idesc_o = make_idesc(ROWS, HD, 1);
+            auto issue_s = [&](int s) {
+                const uint32_t kt = st0 + s * STAGE;
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ks++) {
+                    uint32_t off = (ks >> 2) * (ROWS * 128) + (ks & 3) * 32;
+                    tc_mma_bf16(tmem_base, desc_k_major(qs + off), desc_k_major(kt + off), idesc_s, ks != 0);
+                }
+                tc_commit(s_full);
+            };
+            bool ok = mbar_wait(kv_full, 0);
+            if (!ok) raise_error(2);
+            tc_fence_after();
+            if (ok) issue_s(0);
+            for (int j = 0; j < n_iter && ok; j++) {
+                const int s = j & 1;
+                if (!mbar_wait(p_full, j & 1)) { raise_error(3); break; }
+                tc_fence_after();
+                const uint32_t vt = st0 + s * STAGE + KV_TILE;
+#pragma unroll
+                for (int ks = 0; ks < KEYS / 16; ks++) {
+                    // A = P: 64-key chunk ks / 4, 32 B inside its swizzle row; B = V: 16 keys = two 8-key groups
+                    uint64_t adesc = desc_k_major(ps + (ks >> 2) * (ROWS * 128) + (ks & 3) * 32);
+                    uint64_t bdesc = desc_mn_major(vt + ks * 2048, KEYS * 128);
+                    tc_mma_bf16(tmem_base + KEYS, adesc, bdesc, idesc_o, ks != 0);
+                }
+                tc_commit(o_full);
+                tc_commit(kv_empty + 8 * s);
+                if (j + 1 < n_iter) {
+                    if (!mbar_wait(kv_full + 8 * (s ^ 1), ((j + 1) >> 1) & 1)) { raise_error(2); break; }
+                    tc_fence_after();
+                    issue_s(s ^ 1);
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ softmax, one thread per row
+        const int r = (warp & 3) * 32 + lane;
+        const uint32_t trow = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        float o[HD];
+#pragma unroll
+        for (int d = 0; d < HD; d++) o[d] = 0.f;
+        float m = -INFINITY, l = 0.f;
+        for (int j = 0; j < n_iter; j++) {
+            const int key0 = (p_begin + 2 * j) * PAGE;
+            const bool masked = key0 + KEYS - 1 > hi || key0 < lo;
+            if (!mbar_wait(s_full, j & 1)) { raise_error(4); break; }
+            tc_fence_after();
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < KEYS / 32; c++) {
+                float v[32];
+                tc_ld32(trow + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    int key = key0 + c * 32 + i;
+                    float x = v[i] * scale_log2;
+                    if (masked && (key < lo || key > hi)) x = -INFINITY;
+                    mx = fmaxf(mx, x);
+                }
+            }
+            const float m_new = fmaxf(m, mx);
+            const float corr = m == -INFINITY ? 1.f : ex2(m - m_new);     // m_new >= m; nothing seen yet: keep zeros
+            const float base = m_new == -INFINITY ? 0.f : m_new;
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < KEYS / 32; c++) {
+                float v[32];
+                tc_ld32(trow + c * 32, v);
+                uint32_t w[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float x0 = v[i] * scale_log2, x1 = v[i + 1] * scale_log2;
+                    int key = key0 + c * 32 + i;
+                    if (masked && (key < lo || key > hi)) x0 = -INFINITY;
+                    if (masked && (key + 1 < lo || key + 1 > hi)) x1 = -INFINITY;
+                    float p0 = ex2(x0 - base), p1 = ex2(x1 - base);
+                    sum += p0 + p1;
+                    __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
+                    w[i >> 1] = *(uint32_t *)&t;
+                }
+                // 32 keys = four 16-byte chunks of this row, in the 64-key chunk c / 2
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    int cc = (c & 1) * 4 + k;
+                    uint32_t dst = ps + (c >> 1) * (ROWS * 128) + r * 128 + ((cc ^ (r & 7)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(dst), "r"(w[4 * k]), "r"(w[4 * k + 1]), "r"(w[4 * k + 2]), "r"(w[4 * k + 3]) : "memory");
+                }
+            }
+            l = l * corr + sum;
+            m = m_new;
+            tc_fence_before();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(p_full);
+            if (!mbar_wait(o_full, j & 1)) { raise_error(5); break; }
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < HD / 32; c++) {
+                float v[32];
+                tc_ld32(trow + KEYS + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) o[c * 32 + i] = o[c * 32 + i] * corr + v[i];
+            }
+            tc_fence_before();
+        }
+        if (valid) {
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            bf16 *dst = out + (size_t)(row0 + q0 + t_row) * ldo + (size_t)(kvh * G + g_row) * HD;
+#pragma unroll
+            for (int c = 0; c < HD / 8; c++) {
+                uint32_t w[4];
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    __nv_bfloat162 t = __floats2bfloat162_rn(o[c * 8 + 2 * k] * inv, o[c * 8 + 2 * k + 1] * inv);
+                    w[k] = *(uint32_t *)&t;
+                }
+                *(uint4 *)(dst + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// a page pool [pages * KV * 64 rows, hd] bf16 in boxes of 64 rows x 64 elements, 128-byte swizzle
+static int pool_map(CUtensorMap *map, const void *pool, long long rows, int hd) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return FG_ERR_TENSORMAP;
+    cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+    cuuint32_t box[2] = {64, PAGE};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void *)pool, dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : FG_ERR_TENSORMAP;
+}
+
+template <int HD>
+static int launch_tc(const CUtensorMap &tmK, const CUtensorMap &tmV, const void *q, int ldq, void *out, int ldo,
+                     const int *cu_rows, const int *seq_start, const int *block_table, int table_width, int n_seq,
+                     int max_new, int H, int KV, float scale, int window, cudaStream_t stream) {
+    constexpr int smem = ROWS * HD * 2 + 2 * 2 * KEYS * HD * 2 + ROWS * KEYS * 2 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    int G = H / KV, Gc = G < 16 ? G : 16, TQ = ROWS / Gc;
+    dim3 grid((max_new + TQ - 1) / TQ, KV * ((G + Gc - 1) / Gc), n_seq);
+    return fg_launch(attn_prefill_tc_kernel<HD>, grid, dim3(ATT_THREADS), (size_t)smem, stream, tmK, tmV, (const bf16 *)q, ldq,
+                     (bf16 *)out, ldo, cu_rows, seq_start, block_table, table_width, KV, G, scale * LOG2E, window);
+}
+
+// Arguments as fg_attention_prefill, plus the number of pages in the pools.  Takes HD 64 and 128.
+extern "C" int fg_attention_prefill_tc(const void *q, int ldq, void *out, int ldo, const int *cu_rows,
+                                       const int *seq_start, const int *block_table, int table_width,
+                                       const void *k_pool, const void *v_pool, int n_pages, int n_seq, int max_new,
+                                       int H, int KV, int hd, int page_size, float scale, int window,
+                                       cudaStream_t stream) {
+    if (n_seq <= 0 || max_new <= 0) return 0;
+    if (page_size != PAGE || H % KV || n_seq > 65535 || ldq % 8 || ldo % 8 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
+        ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) || (hd != 64 && hd != 128))
+        return FG_ERR_BAD_SIZE;
+    CUtensorMap tmK, tmV;
+    long long rows = (long long)n_pages * KV * PAGE;
+    int e = pool_map(&tmK, k_pool, rows, hd);
+    if (e) return e;
+    e = pool_map(&tmV, v_pool, rows, hd);
+    if (e) return e;
+    if (hd == 64) return launch_tc<64>(tmK, tmV, q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, n_seq, max_new, H, KV, scale, window, stream);
+    return launch_tc<128>(tmK, tmV, q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, n_seq, max_new, H, KV, scale, window, stream);
+}
+
+extern "C" int fg_attention_prefill_tc_error(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_attn_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_attn_error, &zero, sizeof(int));
+    return v;
+}

@@ -30,7 +30,7 @@ CSRC_DIR = os.path.dirname(os.path.abspath(__file__))
 MODULES = {
     "core": ["elementwise.cu", "gemm_generic.cu", "attention_generic.cu", "sampling.cu"],
     "tc": ["gemm_tc.cu"],
-    "attn": ["attention_decode.cu", "attention_prefill.cu"],
+    "attn": ["attention_decode.cu", "attention_prefill.cu", "attention_prefill_tc.cu"],
 }
 HEADERS = ["common.cuh"]
 

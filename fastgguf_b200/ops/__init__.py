@@ -172,9 +172,13 @@ def attention(q: torch.Tensor, batch, block_table: torch.Tensor, k_pool: torch.T
         if batch.single_token:
             return fast_attention.attention_decode(q, batch.positions, block_table, k_pool, v_pool, n_heads,
                                                    n_kv_heads, head_dim, scale, window)
-        return fast_attention.attention_prefill(q, batch.cu_rows, batch.seq_start, block_table, k_pool, v_pool,
-                                                batch.n_seq, batch.max_new, n_heads, n_kv_heads, head_dim, scale,
-                                                window)
+        # many new tokens: 128-row tiles on the tcgen05 tensor cores; a few rows (a short cut of a sequence
+        # fed in pieces): the 64-row mma.sync kernel wastes less of a tile
+        prefill = (fast_attention.attention_prefill_tc
+                   if batch.max_new * (n_heads // n_kv_heads) >= 64 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+                   else fast_attention.attention_prefill)
+        return prefill(q, batch.cu_rows, batch.seq_start, block_table, k_pool, v_pool, batch.n_seq, batch.max_new,
+                       n_heads, n_kv_heads, head_dim, scale, window)
     return attention_generic(q, batch.positions, batch.row_seq, block_table, k_pool, v_pool,
                              n_heads, n_kv_heads, head_dim, scale, window)
 

@@ -14,6 +14,9 @@ from .lib import KernelError, check, lib, ptr, register_signatures, stream
 register_signatures("attn", {
     "fg_attention_decode": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "fg_attention_prefill_tc": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "fg_attention_prefill_tc_error": [],
     "fg_attention_prefill": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
 })
@@ -69,3 +72,22 @@ def attention_prefill(q, cu_rows, seq_start, block_table, k_pool, v_pool, n_seq,
                                            max_new, n_heads, n_kv_heads, head_dim, k_pool.shape[2], float(scale),
                                            int(window), stream()), "attention_prefill")
     return out
+
+
+def attention_prefill_tc(q, cu_rows, seq_start, block_table, k_pool, v_pool, n_seq, max_new, n_heads, n_kv_heads,
+                         head_dim, scale, window=0, out=None):
+    """The same contract as ``attention_prefill`` on the tcgen05 tensor cores (128-row tiles, K/V by TMA,
+    accumulators in tensor memory).  Needs 16-byte aligned rows of ``q`` and ``out``."""
+    if out is None:
+        out = torch.empty((q.shape[0], n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    check(lib("attn").fg_attention_prefill_tc(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cu_rows), ptr(seq_start),
+                                              ptr(block_table), block_table.shape[1], ptr(k_pool), ptr(v_pool),
+                                              k_pool.shape[0], n_seq, max_new, n_heads, n_kv_heads, head_dim,
+                                              k_pool.shape[2], float(scale), int(window), stream()),
+          "attention_prefill_tc")
+    return out
+
+
+def prefill_tc_error() -> int:
+    """0, or the code of the first bounded wait of the tcgen05 attention that ran out (clears it)."""
+    return int(lib("attn").fg_attention_prefill_tc_error())

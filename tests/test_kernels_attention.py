@@ -108,3 +108,16 @@ def test_attention_prefill(H, KV, hd, window):
     got = fast_attention.attention_prefill(case["q"], case["cu_rows"], case["seq_start"], case["table"], case["k_pool"],
                                            case["v_pool"], len(new), max(new), H, KV, hd, scale, window)
     assert _err(got, plain(case, H, KV, hd, scale, window)) < 1.5e-2
+
+
+@pytest.mark.parametrize("H,KV,hd,window", [(8, 2, 64, 0), (3, 1, 128, 0), (24, 8, 128, 0), (20, 1, 64, 0),
+                                            (4, 4, 64, 100)])
+def test_attention_prefill_tcgen05(H, KV, hd, window):
+    from fastgguf_b200.ops import fast_attention
+    new = [200, 1, 67, 5, 300]
+    case = make_case([0, 300, 60, 0, 129], new, H, KV, hd, torch.bfloat16, 14)
+    scale = 1.0 / math.sqrt(hd)
+    got = fast_attention.attention_prefill_tc(case["q"], case["cu_rows"], case["seq_start"], case["table"],
+                                              case["k_pool"], case["v_pool"], len(new), max(new), H, KV, hd, scale, window)
+    assert fast_attention.prefill_tc_error() == 0
+    assert _err(got, plain(case, H, KV, hd, scale, window)) < 1.5e-2
