@@ -8,7 +8,8 @@
 // tokens x Gc query heads of one KV head (Gc = min(G, 16), row r = token r / Gc, head r % Gc) and
 // walks the sequence's pages two at a time (128 keys):
 //
-//   warp 0 (one lane)  TMA: the K and V tiles of two pages into one of two stages (128B swizzle)
+//   warp 0 (one lane)  TMA: the K tile and the V tile of two pages (128B swizzle); the next K tile is
+//                      fetched as soon as S has consumed the current one, the next V tile after P V
 //   warp 1 (one lane)  MMA: S = Q K^T (128 x 128 x HD), then, once P is in shared memory,
 //                      O_tile = P V (128 x HD x 128); V is the MN-major operand (its rows are keys)
 //   warps 2-5          thread = row: read S from tensor memory, scale, mask, running max and sum in
@@ -106,14 +107,13 @@ __device__ __forceinline__ uint32_t make_idesc(int M, int N, int b_mn_major) {
 __device__ __forceinline__ void raise_error(int role) { atomicCAS(&g_attn_error, 0, (FG_ERR_PIPELINE << 8) | role); }
 
 template <int HD>
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+__global__ void __launch_bounds__(ATT_THREADS, HD <= 64 ? 2 : 1)   // head size 64: two CTAs share an SM and overlap
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                        const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out, int ldo,
                        const int *__restrict__ cu_rows, const int *__restrict__ seq_start,
                        const int *__restrict__ block_table, int table_width, int KV, int G, float scale_log2, int window) {
     constexpr int CH = HD / 64;                        // 64-wide chunks of the head dimension
     constexpr int Q_BYTES = ROWS * HD * 2, KV_TILE = KEYS * HD * 2;
-    constexpr int STAGE = 2 * KV_TILE;                 // K tile then V tile
     constexpr uint32_t TMEM_COLS = 256;                // S: columns 0..127, O tile: 128..128+HD
 
     extern __shared__ uint8_t smem_raw[];
@@ -125,12 +125,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     const int Gc = G < 16 ? G : 16, TQ = ROWS / Gc, chunks = (G + Gc - 1) / Gc;
     const int kvh = blockIdx.y / chunks, g0 = (blockIdx.y % chunks) * Gc;
     const int b = blockIdx.z;
-    const uint32_t qs = smem_u32(smem), st0 = qs + Q_BYTES, ps = st0 + 2 * STAGE;
-    const uint32_t kv_full = smem_u32(&bars[0]), kv_empty = smem_u32(&bars[2]);
+    const uint32_t qs = smem_u32(smem), kt = qs + Q_BYTES, vt = kt + KV_TILE, ps = vt + KV_TILE;
+    const uint32_t k_full = smem_u32(&bars[0]), k_empty = smem_u32(&bars[1]);
+    const uint32_t v_full = smem_u32(&bars[2]), v_empty = smem_u32(&bars[3]);
     const uint32_t s_full = smem_u32(&bars[4]), p_full = smem_u32(&bars[5]), o_full = smem_u32(&bars[6]);
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 2; i++) { mbar_init(kv_full + 8 * i, 1); mbar_init(kv_empty + 8 * i, 1); }
+        mbar_init(k_full, 1); mbar_init(k_empty, 1); mbar_init(v_full, 1); mbar_init(v_empty, 1);
         mbar_init(s_full, 1); mbar_init(p_full, ROWS); mbar_init(o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -177,46 +178,46 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            int issued = 0;
+            int k_issued = 0, v_issued = 0;
             for (int j = 0; j < n_iter; j++) {
-                const int s = j & 1;
-                if (!mbar_wait(kv_empty + 8 * s, ((j >> 1) & 1) ^ 1)) { raise_error(1); break; }
-                const uint32_t bar = kv_full + 8 * s, kdst = st0 + s * STAGE, vdst = kdst + KV_TILE;
-                mbar_expect_tx(bar, STAGE);
-                for (int h = 0; h < 2; h++) {
-                    int pg = min(p_begin + 2 * j + h, p_end - 1);          // a page past the end is masked anyway
-                    int y = (bt[pg] * KV + kvh) * PAGE;
-                    for (int c = 0; c < CH; c++) {
-                        tma_load_2d(kdst + c * (KEYS * 128) + h * (PAGE * 128), &tmK, c * 64, y, bar);
-                        tma_load_2d(vdst + c * (KEYS * 128) + h * (PAGE * 128), &tmV, c * 64, y, bar);
-                    }
-                }
-                issued = j + 1;
+                int y[2];
+                for (int h = 0; h < 2; h++)
+                    y[h] = (bt[min(p_begin + 2 * j + h, p_end - 1)] * KV + kvh) * PAGE;   // a page past the end is masked anyway
+                if (!mbar_wait(k_empty, (j & 1) ^ 1)) { raise_error(1); break; }
+                mbar_expect_tx(k_full, KV_TILE);
+                for (int h = 0; h < 2; h++)
+                    for (int c = 0; c < CH; c++) tma_load_2d(kt + c * (KEYS * 128) + h * (PAGE * 128), &tmK, c * 64, y[h], k_full);
+                k_issued = j + 1;
+                if (!mbar_wait(v_empty, (j & 1) ^ 1)) { raise_error(1); break; }
+                mbar_expect_tx(v_full, KV_TILE);
+                for (int h = 0; h < 2; h++)
+                    for (int c = 0; c < CH; c++) tma_load_2d(vt + c * (KEYS * 128) + h * (PAGE * 128), &tmV, c * 64, y[h], v_full);
+                v_issued = j + 1;
             }
-            for (int j = max(0, issued - 2); j < issued; j++) mbar_wait(kv_full + 8 * (j & 1), (j >> 1) & 1);
+            if (k_issued) mbar_wait(k_full, (k_issued - 1) & 1);      // copies in flight land before the CTA exits
+            if (v_issued) mbar_wait(v_full, (v_issued - 1) & 1);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0 && n_iter > 0) {
             const uint32_t idesc_s = make_idesc(ROWS, KEYS, 0), idesc_o = make_idesc(ROWS, HD, 1);
-            auto issue_s = [&](int s) {
-                const uint32_t kt = st0 + s * STAGE;
+            auto issue_s = [&](int j) {
+                if (!mbar_wait(k_full, j & 1)) { raise_error(2); return false; }
+                tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {
                     uint32_t off = (ks >> 2) * (ROWS * 128) + (ks & 3) * 32;
                     tc_mma_bf16(tmem_base, desc_k_major(qs + off), desc_k_major(kt + off), idesc_s, ks != 0);
                 }
                 tc_commit(s_full);
+                tc_commit(k_empty);                  // the K tile is free once S is complete
+                return true;
             };
-            bool ok = mbar_wait(kv_full, 0);
-            if (!ok) raise_error(2);
-            tc_fence_after();
-            if (ok) issue_s(0);
+            bool ok = issue_s(0);
             for (int j = 0; j < n_iter && ok; j++) {
-                const int s = j & 1;
                 if (!mbar_wait(p_full, j & 1)) { raise_error(3); break; }
+                if (!mbar_wait(v_full, j & 1)) { raise_error(2); break; }
                 tc_fence_after();
-                const uint32_t vt = st0 + s * STAGE + KV_TILE;
 #pragma unroll
                 for (int ks = 0; ks < KEYS / 16; ks++) {
                     // A = P: 64-key chunk ks / 4, 32 B inside its swizzle row; B = V: 16 keys = two 8-key groups
@@ -225,12 +226,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                     tc_mma_bf16(tmem_base + KEYS, adesc, bdesc, idesc_o, ks != 0);
                 }
                 tc_commit(o_full);
-                tc_commit(kv_empty + 8 * s);
-                if (j + 1 < n_iter) {
-                    if (!mbar_wait(kv_full + 8 * (s ^ 1), ((j + 1) >> 1) & 1)) { raise_error(2); break; }
-                    tc_fence_after();
-                    issue_s(s ^ 1);
-                }
+                tc_commit(v_empty);
+                if (j + 1 < n_iter) ok = issue_s(j + 1);
             }
         }
     } else {
@@ -362,11 +359,12 @@ template <int HD>
 static int launch_tc(const CUtensorMap &tmK, const CUtensorMap &tmV, const void *q, int ldq, void *out, int ldo,
                      const int *cu_rows, const int *seq_start, const int *block_table, int table_width, int n_seq,
                      int max_new, int H, int KV, float scale, int window, cudaStream_t stream) {
-    constexpr int smem = ROWS * HD * 2 + 2 * 2 * KEYS * HD * 2 + ROWS * KEYS * 2 + 1024;
+    constexpr int smem = ROWS * HD * 2 + 2 * KEYS * HD * 2 + ROWS * KEYS * 2 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
+        cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         configured = true;
     }
     int G = H / KV, Gc = G < 16 ? G : 16, TQ = ROWS / Gc;
