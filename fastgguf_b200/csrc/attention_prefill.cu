@@ -5,19 +5,17 @@
 // the group) pairs of one KV head, each attending to [start, its own position]; the whole chunk's
 // K/V are in the cache, so causality inside the chunk is the per-row upper bound (:5030-5035).
 //
-// Grid (query tile, kv head x head chunk, sequence).  A CTA owns 64 rows = TQ consecutive new
-// tokens x Gc query heads of one KV head (Gc = min(G, 16)), 16 rows a warp, and walks the
-// sequence's pages from the first page any row may see to the page of its last row.  All four
+// Grid (query tile, kv head x head chunk, sequence).  A CTA owns 16 rows a warp (128 rows with
+// eight warps for head size 64, 64 rows with four warps for head size 128) = TQ consecutive new
+// tokens x Gc query heads of one KV head (Gc = min(G, 16)), and walks the sequence's pages from
+// the first page any row may see to the page of its last row.  All
 // warps share each K/V page in shared memory (two stages, cp.async), so the query heads of a
 // group reuse every load.  Scores, running max and sum are f32 (online softmax); P is rounded to
 // bf16 for the PV product.  A row's keys are always visited in ascending page order, so its
 // result does not depend on the other rows of the step.
 #include "attention_mma.cuh"
 
-#define PF_WARPS 4
-#define PF_ROWS 64
-
-template <int HD>
+template <int HD, int PF_WARPS>
 __device__ __forceinline__ void load_page_cta(uint32_t sdst, const bf16 *src, int tid) {
     constexpr int CPR = HD / 8;
 #pragma unroll
@@ -27,8 +25,8 @@ __device__ __forceinline__ void load_page_cta(uint32_t sdst, const bf16 *src, in
     }
 }
 
-template <int HD>
-__global__ void __launch_bounds__(PF_WARPS * 32)
+template <int HD, int PF_WARPS>
+__global__ void __launch_bounds__(PF_WARPS * 32, PF_WARPS == 8 ? 2 : 1)
 attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out, int ldo,
                     const int *__restrict__ cu_rows, const int *__restrict__ seq_start,
                     const int *__restrict__ block_table, int table_width,
@@ -36,6 +34,7 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
                     int KV, int G, float scale, int window) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int TILE_BYTES = PAGE * HD * 2;
+    constexpr int PF_ROWS = PF_WARPS * 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int Gc = G < 16 ? G : 16;
     const int TQ = PF_ROWS / Gc;                       // new tokens per CTA tile
@@ -45,7 +44,7 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
     pdl_launch_dependents();
     pdl_wait();
     const int row0 = cu_rows[b], n_tok = cu_rows[b + 1] - row0, start = seq_start[b];
-    const int q0 = blockIdx.x * TQ;
+    const int q0 = (gridDim.x - 1 - blockIdx.x) * TQ;   // late tiles see the most keys: start them first
     if (q0 >= n_tok) return;
     const int tq = min(TQ, n_tok - q0);                // valid tokens in this tile
     const int *bt = block_table + (size_t)b * table_width;
@@ -95,16 +94,16 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
     auto vaddr = [&](int st) { return s0 + st * 2 * TILE_BYTES + TILE_BYTES; };
     {
         size_t base = ((size_t)bt[p_begin] * KV + kvh) * PAGE * HD;
-        load_page_cta<HD>(kaddr(0), k_pool + base, tid);
-        load_page_cta<HD>(vaddr(0), v_pool + base, tid);
+        load_page_cta<HD, PF_WARPS>(kaddr(0), k_pool + base, tid);
+        load_page_cta<HD, PF_WARPS>(vaddr(0), v_pool + base, tid);
         cp_async_commit();
     }
     for (int p = p_begin; p < p_end; p++) {
         const int st = (p - p_begin) & 1;
         if (p + 1 < p_end) {
             size_t base = ((size_t)bt[p + 1] * KV + kvh) * PAGE * HD;
-            load_page_cta<HD>(kaddr(st ^ 1), k_pool + base, tid);
-            load_page_cta<HD>(vaddr(st ^ 1), v_pool + base, tid);
+            load_page_cta<HD, PF_WARPS>(kaddr(st ^ 1), k_pool + base, tid);
+            load_page_cta<HD, PF_WARPS>(vaddr(st ^ 1), v_pool + base, tid);
         }
         cp_async_commit();
         cp_async_wait<1>();                    // page p has landed (p + 1 may be in flight)
@@ -136,20 +135,20 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
     }
 }
 
-template <int HD>
+template <int HD, int PF_WARPS>
 static int launch_prefill(const void *q, int ldq, void *out, int ldo, const int *cu_rows, const int *seq_start,
                           const int *block_table, int table_width, const void *k_pool, const void *v_pool,
                           int n_seq, int max_new, int H, int KV, float scale, int window, cudaStream_t stream) {
     constexpr int smem = 2 * 2 * PAGE * HD * 2;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD, PF_WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    int G = H / KV, Gc = G < 16 ? G : 16, TQ = PF_ROWS / Gc;
+    int G = H / KV, Gc = G < 16 ? G : 16, TQ = PF_WARPS * 16 / Gc;
     dim3 grid((max_new + TQ - 1) / TQ, KV * ((G + Gc - 1) / Gc), n_seq);
-    return fg_launch(attn_prefill_kernel<HD>, grid, dim3(PF_WARPS * 32), (size_t)smem, stream, (const bf16 *)q, ldq, (bf16 *)out, ldo, cu_rows,
+    return fg_launch(attn_prefill_kernel<HD, PF_WARPS>, grid, dim3(PF_WARPS * 32), (size_t)smem, stream, (const bf16 *)q, ldq, (bf16 *)out, ldo, cu_rows,
         seq_start, block_table, table_width, (const bf16 *)k_pool, (const bf16 *)v_pool, KV, G, scale, window);
 }
 
@@ -163,7 +162,7 @@ extern "C" int fg_attention_prefill(const void *q, int ldq, void *out, int ldo, 
     if (n_seq <= 0 || max_new <= 0) return 0;
     if (page_size != PAGE || H % KV || n_seq > 65535 || ldq % 2 || ldo % 2 || ((uintptr_t)q & 3) || ((uintptr_t)out & 3))
         return FG_ERR_BAD_SIZE;
-    if (hd == 64) return launch_prefill<64>(q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, k_pool, v_pool, n_seq, max_new, H, KV, scale, window, stream);
-    if (hd == 128) return launch_prefill<128>(q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, k_pool, v_pool, n_seq, max_new, H, KV, scale, window, stream);
+    if (hd == 64) return launch_prefill<64, 8>(q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, k_pool, v_pool, n_seq, max_new, H, KV, scale, window, stream);
+    if (hd == 128) return launch_prefill<128, 4>(q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, k_pool, v_pool, n_seq, max_new, H, KV, scale, window, stream);
     return FG_ERR_BAD_SIZE;
 }

@@ -143,7 +143,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     pdl_launch_dependents();
     pdl_wait();                                        // q and the cache come from the kernels before
     const int row0 = cu_rows[b], n_tok = cu_rows[b + 1] - row0, start = seq_start[b];
-    const int q0 = blockIdx.x * TQ;
+    const int q0 = (gridDim.x - 1 - blockIdx.x) * TQ;  // late tiles see the most keys: start them first
     const bool active = q0 < n_tok;                    // a CTA past the sequence's tokens only sets up and leaves
     const int tq = active ? min(TQ, n_tok - q0) : 0;
     const int tile_hi = start + q0 + tq - 1;
