@@ -241,7 +241,7 @@ class DecodeSession:
             if need > self.widths[i]:
                 for gi, t in enumerate(g.tables):
                     row = cache.tables[gi][self.slots[i], self.widths[i]:need]
-                    t[i, self.widths[i]:need] = torch.from_numpy(row.copy()).to(dev)
+                    t[i, self.widths[i]:need].copy_(torch.from_numpy(row.copy()).pin_memory(), non_blocking=True)
                     backend.stats["h2d_bytes"] += 4 * (need - self.widths[i])
                 self.widths[i] = need
         g.replay()
