@@ -275,6 +275,158 @@ sample_kernel(float *__restrict__ logits, int V, int ldl, SampleParams sp,
     }
 }
 
+// ---- top-k sampling in two stages (k <= 128): the vocabulary of a row is split over TOPK_BLOCKS
+// blocks; each selects the k best of its segment as 64-bit words (value key, then lower index first)
+// with a radix select in shared memory; one block per row then sorts the TOPK_BLOCKS * k candidates
+// and draws exactly as the single-block kernel does.  The k best of the row are among the k best of
+// each segment, and the words order them totally, so the result is the single-block kernel's.
+#define TOPK_SEG 4096                  // most vocabulary entries a stage-1 block takes
+#define TOPK_CAND 2048                 // candidates per row after stage 1
+#define TOPK_MAX_K 128
+
+__global__ void __launch_bounds__(64)
+penalty_kernel(float *__restrict__ logits, int V, int ldl, float penalty, int last_n, const int *__restrict__ seq_slot,
+               const int *__restrict__ hist, int hist_cap, const int *__restrict__ hist_count,
+               const int *__restrict__ stop_ids, int n_stop) {
+    pdl_launch_dependents();
+    pdl_wait();
+    float *row = logits + (size_t)blockIdx.x * ldl;
+    int slot = seq_slot[blockIdx.x];
+    const int *h = hist + (size_t)slot * hist_cap;
+    int have = min(hist_count[slot], min(hist_cap, last_n));
+    for (int i = threadIdx.x; i < have; i += blockDim.x) {
+        int id = h[i];
+        bool skip = id < 0 || id >= V;
+        for (int s = 0; s < n_stop && !skip; s++) skip = stop_ids[s] == id;
+        for (int j = 0; j < i && !skip; j++) skip = h[j] == id;
+        if (!skip) {
+            float v = row[id];
+            row[id] = v > 0.f ? v / penalty : v * penalty;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+topk_stage1_kernel(const float *__restrict__ logits, int V, int ldl, int k, int n_blocks,
+                   unsigned long long *__restrict__ cand) {        // [B, n_blocks * k], zero where unused
+    __shared__ uint32_t keys[TOPK_SEG];
+    __shared__ int hist[256];
+    __shared__ int misc[4];
+    __shared__ int wsum[8];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.y, tid = threadIdx.x;
+    const float *row = logits + (size_t)b * ldl;
+    const int per = (V + n_blocks - 1) / n_blocks;
+    const int i0 = blockIdx.x * per, n = max(0, min(V, i0 + per) - i0);
+    unsigned long long *out = cand + ((size_t)b * n_blocks + blockIdx.x) * k;
+    for (int i = tid; i < n; i += blockDim.x) keys[i] = float_key(row[i0 + i]);
+    for (int i = tid; i < k; i += blockDim.x) out[i] = 0ull;
+    __syncthreads();
+    if (n == 0) return;
+    const int kk = min(k, n);
+    uint32_t prefix = 0, mask = 0;
+    int need = kk;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        hist[tid] = 0;
+        __syncthreads();
+        for (int i = tid; i < n; i += blockDim.x)
+            if ((keys[i] & mask) == prefix) atomicAdd(&hist[(keys[i] >> shift) & 255], 1);
+        __syncthreads();
+        if (tid == 0) {
+            int cum = 0, bin = 255;
+            for (; bin > 0; bin--) { if (cum + hist[bin] >= need) break; cum += hist[bin]; }
+            misc[0] = bin; misc[1] = need - cum;
+        }
+        __syncthreads();
+        prefix |= (uint32_t)misc[0] << shift;
+        mask |= 255u << shift;
+        need = misc[1];
+        __syncthreads();
+    }
+    // everything above the k-th key, and the first `need` equal to it in index order
+    if (tid == 0) misc[2] = 0;
+    __syncthreads();
+    int taken_eq = 0;
+    for (int c0 = 0; c0 < n; c0 += blockDim.x) {
+        int i = c0 + tid;
+        uint32_t key = i < n ? keys[i] : 0u;
+        int gt = i < n && key > prefix, eq = i < n && key == prefix;
+        unsigned ball = __ballot_sync(0xffffffffu, eq);
+        int lane = tid & 31, w = tid >> 5;
+        if (lane == 0) wsum[w] = __popc(ball);
+        __syncthreads();
+        int before = 0, tot = 0;
+        for (int j = 0; j < 8; j++) { if (j < w) before += wsum[j]; tot += wsum[j]; }
+        int rank = taken_eq + before + __popc(ball & ((1u << lane) - 1));
+        if (gt || (eq && rank < need)) {
+            int at = atomicAdd(&misc[2], 1);
+            out[at] = ((unsigned long long)key << 32) | (uint32_t)(~(uint32_t)(i0 + i));
+        }
+        taken_eq += tot;
+        __syncthreads();
+    }
+}
+
+__global__ void __launch_bounds__(1024)
+topk_stage2_kernel(const unsigned long long *__restrict__ cand_in, int n_cand, int k, SampleParams sp,
+                   const int *__restrict__ seq_slot, unsigned long long *__restrict__ rng,
+                   int *__restrict__ hist, int hist_cap, int *__restrict__ hist_count, int *__restrict__ out_tokens) {
+    __shared__ unsigned long long cand[TOPK_CAND];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x, tid = threadIdx.x, slot = seq_slot[b];
+    for (int i = tid; i < TOPK_CAND; i += blockDim.x) cand[i] = i < n_cand ? cand_in[(size_t)b * n_cand + i] : 0ull;
+    __syncthreads();
+    for (int size = 2; size <= TOPK_CAND; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int i = tid; i < TOPK_CAND; i += blockDim.x) {
+                int j = i ^ stride;
+                if (j > i) {
+                    unsigned long long x = cand[i], y = cand[j];
+                    bool desc = (i & size) == 0;
+                    if (desc ? x < y : x > y) { cand[i] = y; cand[j] = x; }
+                }
+            }
+            __syncthreads();
+        }
+    }
+    if (tid == 0) {
+        int n = 0;
+        while (n < k && cand[n] != 0ull) n++;
+        float top = key_float((uint32_t)(cand[0] >> 32));
+        float sum = 0.f;
+        for (int i = 0; i < n; i++) sum += expf((key_float((uint32_t)(cand[i] >> 32)) - top) / sp.temp);
+        int keep = n;
+        if (sp.top_p > 0.f && sp.top_p < 1.0f) {
+            float cum = 0.f, lim = sp.top_p * sum;
+            for (int i = 0; i < n; i++) {
+                cum += expf((key_float((uint32_t)(cand[i] >> 32)) - top) / sp.temp);
+                if (cum >= lim) { keep = i + 1; break; }
+            }
+        }
+        float tot = 0.f;
+        for (int i = 0; i < keep; i++) tot += expf((key_float((uint32_t)(cand[i] >> 32)) - top) / sp.temp);
+        uint64_t st = rng[slot];
+        float r = (float)(xorshift64star(&st) >> 40) / 16777216.0f * tot;
+        rng[slot] = st;
+        int pick = keep - 1;
+        for (int i = 0; i < keep; i++) {
+            r -= expf((key_float((uint32_t)(cand[i] >> 32)) - top) / sp.temp);
+            if (r < 0.f) { pick = i; break; }
+        }
+        int chosen = (int)(~(uint32_t)(cand[pick] & 0xffffffffull));
+        out_tokens[b] = chosen;
+        if (hist) {
+            int *h = hist + (size_t)slot * hist_cap;
+            int c = hist_count[slot];
+            if (c < hist_cap) h[c] = chosen;
+            else { for (int i = 1; i < hist_cap; i++) h[i - 1] = h[i]; h[hist_cap - 1] = chosen; }
+            hist_count[slot] = c + 1;
+        }
+    }
+}
+
 // ---- greedy without a repeat penalty: the vocabulary of each row is split over GREEDY_BLOCKS blocks;
 // each folds its best (value, lowest index) into one 64-bit word per row with atomicMax, and the
 // block that arrives last writes the token and clears the word for the next call.  The words
@@ -332,7 +484,8 @@ greedy_kernel(const float *__restrict__ logits, int V, int ldl, const int *__res
 extern "C" int fg_sample(float *logits, int B, int V, int ldl, float temp, int top_k, float top_p,
                          float repeat_penalty, int repeat_last_n, const int *seq_slot,
                          unsigned long long *rng, int *hist, int hist_cap, int *hist_count,
-                         const int *stop_ids, int n_stop, int *out_tokens, cudaStream_t stream) {
+                         const int *stop_ids, int n_stop, int *out_tokens, unsigned long long *scratch,
+                         cudaStream_t stream) {
     if (B <= 0) return 0;
     if (top_k > MAX_TOP_K) return FG_ERR_BAD_SIZE;
     bool penalizes = hist && repeat_penalty > 0.f && repeat_penalty != 1.0f && repeat_last_n > 0;
@@ -340,6 +493,25 @@ extern "C" int fg_sample(float *logits, int B, int V, int ldl, float temp, int t
         return fg_launch(greedy_kernel, dim3(GREEDY_BLOCKS, B), dim3(256), 0, stream, (const float *)logits, V, ldl,
                          seq_slot, hist, hist_cap, hist_count, out_tokens);
     SampleParams sp{temp, top_p, repeat_penalty, top_k, repeat_last_n};
+    if (temp > 0.f && top_k > 0 && top_k <= TOPK_MAX_K && scratch && B <= 65535) {
+        // two stages; `scratch` holds B * 2048 words
+        int k = top_k < V ? top_k : V;
+        int n_blocks = TOPK_CAND / (k <= 64 ? 64 : 128);
+        if ((V + n_blocks - 1) / n_blocks <= TOPK_SEG) {
+            int kc = k <= 64 ? 64 : 128;                   // slots per block (>= k); unused ones stay zero
+            if (penalizes) {
+                int e = fg_launch(penalty_kernel, dim3(B), dim3(64), 0, stream, logits, V, ldl, repeat_penalty,
+                                  repeat_last_n, seq_slot, (const int *)hist, hist_cap, (const int *)hist_count, stop_ids, n_stop);
+                if (e) return e;
+            }
+            int e = fg_launch(topk_stage1_kernel, dim3(n_blocks, B), dim3(256), 0, stream, (const float *)logits, V, ldl,
+                              kc < k ? kc : k, n_blocks, scratch);
+            if (e) return e;
+            int per_block = kc < k ? kc : k;
+            return fg_launch(topk_stage2_kernel, dim3(B), dim3(1024), 0, stream, (const unsigned long long *)scratch,
+                             n_blocks * per_block, k, sp, seq_slot, rng, hist, hist_cap, hist_count, out_tokens);
+        }
+    }
     sample_kernel<<<B, SAMPLE_THREADS, 0, stream>>>(logits, V, ldl, sp, seq_slot, rng, hist, hist_cap,
                                                     hist_count, stop_ids, n_stop, out_tokens);
     return FG_LAUNCH_CHECK();

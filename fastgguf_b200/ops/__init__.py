@@ -219,9 +219,14 @@ def sample(logits: torch.Tensor, *, temp: float, top_k: int, top_p: float, repea
         out = torch.empty((B,), dtype=torch.int32, device=logits.device)
     cap = 0 if hist is None else hist.shape[1]
     n_stop = 0 if stop_ids is None else stop_ids.numel()
+    scratch = None
+    if temp > 0 and 0 < top_k <= 128:
+        # candidates of the two-stage top-k: 2048 words a row
+        scratch = torch.empty((B, 2048), dtype=torch.int64, device=logits.device)
     check(lib().fg_sample(ptr(logits), B, V, logits.stride(0), float(temp), int(top_k), float(top_p),
                           float(repeat_penalty), int(repeat_last_n), ptr(_i32(seq_slot, "seq_slot")), ptr(rng),
-                          ptr(hist), cap, ptr(hist_count), ptr(stop_ids), n_stop, ptr(out), stream()), "sample")
+                          ptr(hist), cap, ptr(hist_count), ptr(stop_ids), n_stop, ptr(out), ptr(scratch), stream()),
+          "sample")
     return out
 
 

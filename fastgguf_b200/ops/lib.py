@@ -84,7 +84,7 @@ _SIGNATURES = {
         "fg_attention_generic": [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "fg_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_float, c_int, c_void_p,
-                      c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+                      c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
         "fg_argmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
         "fg_decode_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     },
