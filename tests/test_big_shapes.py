@@ -1,0 +1,41 @@
+"""One layer with the layer sizes of the large configurations (Llama 3.2 3B: 24 heads in groups of 3,
+head size 128; Llama 3.1 8B: d_ff 14336), a small vocabulary, bfloat16: prompts of unequal lengths in
+one step, then a few decoded tokens, against the plain implementation (float32 on the CPU)."""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama
+from helpers import TINY_B, make_model_dir, random_tokens, rel_err
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = {
+    "3b": dict(hidden_size=3072, num_attention_heads=24, num_key_value_heads=8, head_dim=128, intermediate_size=8192),
+    "8b": dict(hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336),
+}
+
+
+@pytest.mark.parametrize("which", ["3b", "8b"])
+def test_one_layer_of_a_large_configuration(tmp_path, which):
+    from fastgguf_b200.engine.api import Engine
+    from fastgguf_b200.engine.batch import StepEntry
+    cfg_dict = dict(TINY_B, num_hidden_layers=1, vocab_size=515, max_position_embeddings=4096, **SHAPES[which])
+    cfg_dict["rope_scaling"] = dict(TINY_B["rope_scaling"], factor=8.0, original_max_position_embeddings=128)
+    model_dir = make_model_dir(tmp_path, cfg_dict, 11, torch.bfloat16)
+    cfg, W = plain_llama.read_model_folder(model_dir)
+    lens, extra = [150, 3, 70], 4
+    seqs = [random_tokens(n + extra, cfg["vocab_size"], 200 + i) for i, n in enumerate(lens)]
+    want = [plain_llama.plain_forward(cfg, W, s, torch.float32).numpy() for s in seqs]
+    engine = Engine.from_dir(model_dir, dtype="bfloat16", max_tokens=1024, max_batch=4)
+    slots = [engine.acquire() for _ in seqs]
+    out = engine.step([StepEntry(sl, s[:n], list(range(n))) for sl, s, n in zip(slots, seqs, lens)]).cpu().numpy()
+    got = [list(out[sum(lens[:i]):sum(lens[:i + 1])]) for i in range(len(seqs))]
+    for k in range(extra):
+        out = engine.step([StepEntry(sl, [s[n + k]], [0]) for sl, s, n in zip(slots, seqs, lens)]).cpu().numpy()
+        for g, row in zip(got, out):
+            g.append(row)
+    for g, w in zip(got, want):
+        assert rel_err(np.stack(g), w) < 3e-2
+    from fastgguf_b200.ops import fast_attention, fast_gemm
+    assert fast_gemm.pipeline_error() == 0 and fast_attention.prefill_tc_error() == 0
