@@ -14,7 +14,7 @@ from __future__ import annotations
 import json
 import os
 from dataclasses import dataclass, fields, asdict
-from typing import Any, ClassVar
+from typing import ClassVar
 
 
 class ConfigError(ValueError):

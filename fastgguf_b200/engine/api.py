@@ -10,7 +10,7 @@ fastgguf.c:6957-6982), and ``ctx`` is its context length argument (default 2048,
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence, Union
+from typing import Optional, Sequence, Union
 
 import torch
 

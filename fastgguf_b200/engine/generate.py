@@ -15,7 +15,7 @@ tests drive with a fake on the CPU.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence
+from typing import List, Sequence
 
 from .batch import StepEntry
 

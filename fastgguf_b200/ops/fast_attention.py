@@ -9,7 +9,7 @@ from typing import Optional
 
 import torch
 
-from .lib import KernelError, check, lib, ptr, register_signatures, stream
+from .lib import check, lib, ptr, register_signatures, stream
 
 register_signatures("attn", {
     "fg_attention_decode": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,

@@ -4,9 +4,6 @@ The two tiny Llama configurations differ in every size and option: layers 2/3, w
 heads 4/6, KV heads 2/1, head size 16/24, vocabulary 256/509, eps 1e-5/1e-6,
 theta 1e4/5e5, no rotary scaling / llama3 scaling, tied / untied head.
 """
-import json
-import os
-
 import numpy as np
 import torch
 
@@ -32,7 +29,10 @@ TINY_C = dict(TINY_A, hidden_size=256, num_hidden_layers=2, num_attention_heads=
               head_dim=64, intermediate_size=448, vocab_size=300, max_position_embeddings=2048)
 TINY_D = dict(TINY_B, hidden_size=200, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2,
               head_dim=128, intermediate_size=320, vocab_size=333, max_position_embeddings=2048)
-TINY = {"a": (TINY_A, 0), "b": (TINY_B, 1), "c": (TINY_C, 2), "d": (TINY_D, 3)}
+# sizes the tensor-core kernels refuse (reduction lengths that are no multiple of 8): the plain kernels in bfloat16
+TINY_E = dict(TINY_A, hidden_size=100, num_attention_heads=3, num_key_value_heads=3, head_dim=16,
+              intermediate_size=52, vocab_size=131, tie_word_embeddings=False)
+TINY = {"a": (TINY_A, 0), "b": (TINY_B, 1), "c": (TINY_C, 2), "d": (TINY_D, 3), "e": (TINY_E, 4)}
 
 
 def make_model_dir(tmp_path, cfg_dict, seed, dtype=torch.bfloat16):

@@ -1,5 +1,4 @@
 """Each request alone and whole, through the engine's step function, against the plain implementation."""
-import numpy as np
 import pytest
 import torch
 
@@ -10,7 +9,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["a", "b", "c", "d"])
+@pytest.mark.parametrize("which", ["a", "b", "c", "d", "e"])
 def test_whole_requests(tmp_path, which, dtype):
     from fastgguf_b200.engine.api import Engine
     from fastgguf_b200.engine.batch import StepEntry

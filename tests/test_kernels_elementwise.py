@@ -1,7 +1,5 @@
 """The row-wise kernels and the sampler alone, against the plain implementation's functions, at
 sizes other than the engine's."""
-import math
-
 import numpy as np
 import pytest
 import torch

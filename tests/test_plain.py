@@ -2,11 +2,9 @@
 in the style of the reference's selftest (fastgguf.c:5414-5475 sampler, :5826-5869 attention,
 :5921-5936 RoPE)."""
 import json
-import math
 import os
 
 import numpy as np
-import pytest
 import torch
 
 import plain_llama as P

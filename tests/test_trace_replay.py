@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import plain_llama
-from helpers import TINY, TOL, make_model_dir, random_tokens, rel_err
+from helpers import TINY, TOL, make_model_dir, random_tokens
 from trace_tools import batched_trace, collect, run_trace, tail_trace, whole_trace
 
 pytestmark = pytest.mark.gpu
