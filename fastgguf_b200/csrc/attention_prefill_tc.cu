@@ -243,50 +243,88 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             const bool masked = key0 + KEYS - 1 > hi || key0 < lo;
             if (!mbar_wait(s_full, j & 1)) { raise_error(4); break; }
             tc_fence_after();
-            float mx = -INFINITY;
+            // One pass when the running base is still good: probabilities relative to m, which may lag the
+            // true maximum by up to 2^8 (harmless in f32 / bf16, and the same factor is in l and in O).  A row
+            // whose new scores exceed that makes its warp redo the tile in two passes with the true maximum.
+            float corr = 1.f, sum = 0.f;
+            bool redo = !__all_sync(0xffffffffu, m != -INFINITY);
+            if (!redo) {
+                float mx = -INFINITY;
 #pragma unroll 1
-            for (int c = 0; c < KEYS / 32; c++) {
-                float v[32];
-                tc_ld32(trow + c * 32, v);
+                for (int c = 0; c < KEYS / 32; c++) {
+                    float v[32];
+                    tc_ld32(trow + c * 32, v);
+                    uint32_t w[16];
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    int key = key0 + c * 32 + i;
-                    float x = v[i] * scale_log2;
-                    if (masked && (key < lo || key > hi)) x = -INFINITY;
-                    mx = fmaxf(mx, x);
+                    for (int i = 0; i < 32; i += 2) {
+                        float x0 = v[i] * scale_log2, x1 = v[i + 1] * scale_log2;
+                        int key = key0 + c * 32 + i;
+                        if (masked && (key < lo || key > hi)) x0 = -INFINITY;
+                        if (masked && (key + 1 < lo || key + 1 > hi)) x1 = -INFINITY;
+                        mx = fmaxf(mx, fmaxf(x0, x1));
+                        float p0 = ex2(x0 - m), p1 = ex2(x1 - m);
+                        sum += p0 + p1;
+                        __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
+                        w[i >> 1] = *(uint32_t *)&t;
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        int cc = (c & 1) * 4 + k;
+                        uint32_t dst = ps + (c >> 1) * (ROWS * 128) + r * 128 + ((cc ^ (r & 7)) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                     ::"r"(dst), "r"(w[4 * k]), "r"(w[4 * k + 1]), "r"(w[4 * k + 2]), "r"(w[4 * k + 3]) : "memory");
+                    }
                 }
+                redo = __any_sync(0xffffffffu, mx > m + 8.0f);
             }
-            const float m_new = fmaxf(m, mx);
-            const float corr = m == -INFINITY ? 1.f : ex2(m - m_new);     // m_new >= m; nothing seen yet: keep zeros
-            const float base = m_new == -INFINITY ? 0.f : m_new;
-            float sum = 0.f;
+            float m_keep = m;
+            if (redo) {
+                float mx = -INFINITY;
 #pragma unroll 1
-            for (int c = 0; c < KEYS / 32; c++) {
-                float v[32];
-                tc_ld32(trow + c * 32, v);
-                uint32_t w[16];
+                for (int c = 0; c < KEYS / 32; c++) {
+                    float v[32];
+                    tc_ld32(trow + c * 32, v);
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float x0 = v[i] * scale_log2, x1 = v[i + 1] * scale_log2;
-                    int key = key0 + c * 32 + i;
-                    if (masked && (key < lo || key > hi)) x0 = -INFINITY;
-                    if (masked && (key + 1 < lo || key + 1 > hi)) x1 = -INFINITY;
-                    float p0 = ex2(x0 - base), p1 = ex2(x1 - base);
-                    sum += p0 + p1;
-                    __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
-                    w[i >> 1] = *(uint32_t *)&t;
+                    for (int i = 0; i < 32; i++) {
+                        int key = key0 + c * 32 + i;
+                        float x = v[i] * scale_log2;
+                        if (masked && (key < lo || key > hi)) x = -INFINITY;
+                        mx = fmaxf(mx, x);
+                    }
                 }
-                // 32 keys = four 16-byte chunks of this row, in the 64-key chunk c / 2
+                const float m_new = fmaxf(m, mx);
+                corr = m == -INFINITY ? 1.f : ex2(m - m_new);                 // m_new >= m; nothing seen yet: keep zeros
+                const float base = m_new == -INFINITY ? 0.f : m_new;
+                sum = 0.f;
+#pragma unroll 1
+                for (int c = 0; c < KEYS / 32; c++) {
+                    float v[32];
+                    tc_ld32(trow + c * 32, v);
+                    uint32_t w[16];
 #pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    int cc = (c & 1) * 4 + k;
-                    uint32_t dst = ps + (c >> 1) * (ROWS * 128) + r * 128 + ((cc ^ (r & 7)) << 4);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                                 ::"r"(dst), "r"(w[4 * k]), "r"(w[4 * k + 1]), "r"(w[4 * k + 2]), "r"(w[4 * k + 3]) : "memory");
+                    for (int i = 0; i < 32; i += 2) {
+                        float x0 = v[i] * scale_log2, x1 = v[i + 1] * scale_log2;
+                        int key = key0 + c * 32 + i;
+                        if (masked && (key < lo || key > hi)) x0 = -INFINITY;
+                        if (masked && (key + 1 < lo || key + 1 > hi)) x1 = -INFINITY;
+                        float p0 = ex2(x0 - base), p1 = ex2(x1 - base);
+                        sum += p0 + p1;
+                        __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
+                        w[i >> 1] = *(uint32_t *)&t;
+                    }
+                    // 32 keys = four 16-byte chunks of this row, in the 64-key chunk c / 2
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        int cc = (c & 1) * 4 + k;
+                        uint32_t dst = ps + (c >> 1) * (ROWS * 128) + r * 128 + ((cc ^ (r & 7)) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                     ::"r"(dst), "r"(w[4 * k]), "r"(w[4 * k + 1]), "r"(w[4 * k + 2]), "r"(w[4 * k + 3]) : "memory");
+                    }
                 }
+                m_keep = m_new;
             }
             l = l * corr + sum;
-            m = m_new;
+            m = m_keep;
             tc_fence_before();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(p_full);
