@@ -26,14 +26,26 @@ __device__ __forceinline__ float ld_dsmem(const float *p, int rank) {
     return v;
 }
 
-template <int HD, bool CLUSTER>
+// What the fused variant (FUSE) also does, so that no separate RoPE kernel runs in a decode step:
+// q arrives unrotated, with the new token's k and v behind it in the same row (the output of the
+// fused q/k/v projection); q is rotated in registers, and the warp that reads the sequence's last
+// page puts the rotated k and the v of the new token into its shared-memory copy of that page
+// (and, in one CTA per KV head, into the cache).  Pages hold only older tokens otherwise, so every
+// page load starts BEFORE the wait on the preceding kernel.
+struct RopeArgs {
+    const float *cos_t, *sin_t;      // [positions, HD / 2]
+    bf16 *k_pool, *v_pool;           // the cache, writable
+    int q_heads;                     // H: k starts at q + H * HD, v at q + (H + KV) * HD
+};
+
+template <int HD, bool CLUSTER, bool FUSE>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ positions,
                    const int *__restrict__ block_table, int table_width,
                    const bf16 *__restrict__ k_pool, const bf16 *__restrict__ v_pool,
                    int KV, int G, float scale, int window, int n_splits,
                    float *__restrict__ part_o, float *__restrict__ part_ml,
-                   bf16 *__restrict__ out, int ldo) {
+                   bf16 *__restrict__ out, int ldo, RopeArgs rope) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int TILE_BYTES = PAGE * HD * 2;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -42,7 +54,8 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
     const int rows = min(16, G - g0);
     const int b = blockIdx.z, split = blockIdx.x;
     pdl_launch_dependents();
-    pdl_wait();
+    if (!FUSE) pdl_wait();
+    // positions and page tables are written between steps, never by the kernel just before this one
     const int pos = positions[b];
     const int lo_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int first_page = lo_key / PAGE, n_pages = pos / PAGE - first_page + 1;
@@ -53,20 +66,6 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
     uint8_t *kbuf = smem + (size_t)warp * 2 * TILE_BYTES, *vbuf = kbuf + TILE_BYTES;
     const uint32_t ks = smem_addr(kbuf), vs = smem_addr(vbuf);
 
-    // Q fragments of rows g0 .. g0+15 of this KV head's group (rows past the group are zero)
-    uint32_t qf[HD / 16][4];
-    {
-        const int r0 = lane >> 2, c = (lane & 3) * 2;
-        const bf16 *qrow = q + (size_t)b * ldq + (size_t)(kvh * G + g0) * HD;
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; kk++) {
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                int r = r0 + (e & 1) * 8, k = kk * 16 + c + (e >> 1) * 8;
-                qf[kk][e] = r < rows ? *(const uint32_t *)(qrow + (size_t)r * HD + k) : 0u;
-            }
-        }
-    }
     float o[HD / 8][4];
 #pragma unroll
     for (int d = 0; d < HD / 8; d++) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
@@ -81,11 +80,73 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
         load_page_warp<HD>(vs, v_pool + base, lane);
         cp_async_commit();
     }
+    if (FUSE) pdl_wait();                      // q, k, v of the new token come from the kernel before
+    // Q fragments of rows g0 .. g0+15 of this KV head's group (rows past the group are zero)
+    uint32_t qf[HD / 16][4];
+    {
+        const int r0 = lane >> 2, c = (lane & 3) * 2;
+        const bf16 *qrow = q + (size_t)b * ldq + (size_t)(kvh * G + g0) * HD;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; kk++) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                int r = r0 + (e & 1) * 8, k = kk * 16 + c + (e >> 1) * 8;
+                qf[kk][e] = r < rows ? *(const uint32_t *)(qrow + (size_t)r * HD + k) : 0u;
+            }
+        }
+        if (FUSE) {
+            // rotate: dims (j, j + HD/2) are the same registers of k-steps kk and kk + HD/32
+            const float *cs = rope.cos_t + (size_t)pos * (HD / 2), *sn = rope.sin_t + (size_t)pos * (HD / 2);
+#pragma unroll
+            for (int kk = 0; kk < HD / 32; kk++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    int j = kk * 16 + c + (e >> 1) * 8;
+                    float2 lo2 = __bfloat1622float2(*(__nv_bfloat162 *)&qf[kk][e]);
+                    float2 hi2 = __bfloat1622float2(*(__nv_bfloat162 *)&qf[kk + HD / 32][e]);
+                    float c0 = cs[j], c1 = cs[j + 1], s0 = sn[j], s1 = sn[j + 1];
+                    qf[kk][e] = pack_bf16(lo2.x * c0 - hi2.x * s0, lo2.y * c1 - hi2.y * s1);
+                    qf[kk + HD / 32][e] = pack_bf16(lo2.x * s0 + hi2.x * c0, lo2.y * s1 + hi2.y * c1);
+                }
+            }
+        }
+    }
     for (; p < p_end; p += DEC_WARPS) {
         const int pn = p + DEC_WARPS;
         const size_t nbase = pn < p_end ? ((size_t)bt[pn] * KV + kvh) * PAGE * HD : 0;
         cp_async_wait<1>();                    // K of this page has landed (V may still be in flight)
         __syncwarp();
+        const bool newest = FUSE && p == pos / PAGE;      // this page holds the new token's row
+        if (newest) {
+            // rotated k of the new token -> row pos % 64 of the K tile (and the cache, once per KV head)
+            const int off = pos % PAGE;
+            const bool to_cache = blockIdx.y % chunks == 0;
+            const bf16 *ksrc = q + (size_t)b * ldq + (size_t)(rope.q_heads + kvh) * HD;
+            const float *cs = rope.cos_t + (size_t)pos * (HD / 2), *sn = rope.sin_t + (size_t)pos * (HD / 2);
+            if (lane < HD / 16) {
+                const int j0 = lane * 8;
+                uint4 lo4 = *(const uint4 *)(ksrc + j0), hi4 = *(const uint4 *)(ksrc + HD / 2 + j0);
+                const __nv_bfloat162 *lp = (const __nv_bfloat162 *)&lo4, *hp = (const __nv_bfloat162 *)&hi4;
+                uint4 olo, ohi;
+                uint32_t *ol = (uint32_t *)&olo, *oh = (uint32_t *)&ohi;
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    float2 a = __bfloat1622float2(lp[e]), bb = __bfloat1622float2(hp[e]);
+                    float c0 = cs[j0 + 2 * e], c1 = cs[j0 + 2 * e + 1], s0 = sn[j0 + 2 * e], s1 = sn[j0 + 2 * e + 1];
+                    ol[e] = pack_bf16(a.x * c0 - bb.x * s0, a.y * c1 - bb.y * s1);
+                    oh[e] = pack_bf16(a.x * s0 + bb.x * c0, a.y * s1 + bb.y * c1);
+                }
+                const int clo = lane, chi = lane + HD / 16;
+                *(uint4 *)(kbuf + off * (HD * 2) + ((clo ^ (off & 7)) << 4)) = olo;
+                *(uint4 *)(kbuf + off * (HD * 2) + ((chi ^ (off & 7)) << 4)) = ohi;
+                if (to_cache) {
+                    bf16 *dst = rope.k_pool + (((size_t)bt[p] * KV + kvh) * PAGE + off) * HD;
+                    *(uint4 *)(dst + j0) = olo;
+                    *(uint4 *)(dst + HD / 2 + j0) = ohi;
+                }
+            }
+            __syncwarp();
+        }
         float s[8][4];
 #pragma unroll
         for (int j = 0; j < 8; j++) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
@@ -99,6 +160,17 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
             softmax_update<HD / 8, true>(s, o, m, l, scale * LOG2E, p * PAGE, lo, hi, lane);
         cp_async_wait<1>();                    // V of this page has landed
         __syncwarp();
+        if (newest) {
+            const int off = pos % PAGE;
+            const bf16 *vsrc = q + (size_t)b * ldq + (size_t)(rope.q_heads + KV + kvh) * HD;
+            if (lane < HD / 8) {
+                uint4 v4 = *(const uint4 *)(vsrc + lane * 8);
+                *(uint4 *)(vbuf + off * (HD * 2) + ((lane ^ (off & 7)) << 4)) = v4;
+                if (blockIdx.y % chunks == 0)
+                    *(uint4 *)(rope.v_pool + (((size_t)bt[p] * KV + kvh) * PAGE + off) * HD + lane * 8) = v4;
+            }
+            __syncwarp();
+        }
         pv_page<HD>(o, s, vs, lane);
         __syncwarp();
         if (pn < p_end) load_page_warp<HD>(vs, v_pool + nbase, lane);
@@ -203,15 +275,15 @@ __global__ void attn_decode_merge_kernel(const float *__restrict__ part_o, const
     out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
 }
 
-template <int HD, bool CLUSTER>
+template <int HD, bool CLUSTER, bool FUSE = false>
 static int launch_decode_kernel(dim3 grid, int cluster_x, cudaStream_t stream, const void *q, int ldq, void *out, int ldo,
                                 const int *positions, const int *block_table, int table_width, const void *k_pool,
                                 const void *v_pool, int KV, int G, float scale, int window, int n_splits,
-                                float *part_o, float *part_ml) {
+                                float *part_o, float *part_ml, RopeArgs rope = RopeArgs{}) {
     constexpr int smem = DEC_WARPS * 2 * PAGE * HD * 2 + 16 * HD * 4 + 16 * 2 * 4;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, CLUSTER, FUSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -230,9 +302,9 @@ static int launch_decode_kernel(dim3 grid, int cluster_x, cudaStream_t stream, c
         n++;
     }
     cfg.attrs = attr; cfg.numAttrs = n;
-    return (int)cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, CLUSTER>, (const bf16 *)q, ldq, positions, block_table,
+    return (int)cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, CLUSTER, FUSE>, (const bf16 *)q, ldq, positions, block_table,
                                    table_width, (const bf16 *)k_pool, (const bf16 *)v_pool, KV, G, scale, window, n_splits,
-                                   part_o, part_ml, (bf16 *)out, ldo);
+                                   part_o, part_ml, (bf16 *)out, ldo, rope);
 }
 
 template <int HD>
@@ -268,6 +340,31 @@ extern "C" int fg_attention_decode(const void *q, int ldq, void *out, int ldo, c
     if (!part_o && n_splits != 1 && n_splits != 2 && n_splits != 4 && n_splits != 8) return FG_ERR_BAD_SIZE;
     if (hd == 64) return launch_decode<64>(q, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, B, H, KV, scale, window, n_splits, part_o, part_ml, stream);
     if (hd == 128) return launch_decode<128>(q, ldq, out, ldo, positions, block_table, table_width, k_pool, v_pool, B, H, KV, scale, window, n_splits, part_o, part_ml, stream);
+    return FG_ERR_BAD_SIZE;
+}
+
+// The fused decode step of an attention layer: RoPE of q and of the new k, cache append of k and v, and
+// attention, in one kernel.  qkv: [B, ldq] rows of (q heads | k heads | v heads) straight from the
+// projection; cos/sin: [positions, hd / 2] f32; n_splits 1, 2, 4 or 8 (merged inside a cluster).
+extern "C" int fg_attention_decode_fused(const void *qkv, int ldq, void *out, int ldo, const int *positions,
+                                         const int *block_table, int table_width, void *k_pool, void *v_pool,
+                                         const float *cos_t, const float *sin_t, int B, int H, int KV, int hd,
+                                         int page_size, float scale, int window, int n_splits, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (page_size != PAGE || H % KV || B > 65535 || ldq % 8 || ((uintptr_t)qkv & 15) || ((uintptr_t)k_pool & 15) ||
+        ((uintptr_t)v_pool & 15) || (n_splits != 1 && n_splits != 2 && n_splits != 4 && n_splits != 8))
+        return FG_ERR_BAD_SIZE;
+    int G = H / KV;
+    dim3 grid(n_splits, KV * ((G + 15) / 16), B);
+    RopeArgs rope{cos_t, sin_t, (bf16 *)k_pool, (bf16 *)v_pool, H};
+    if (hd == 64)
+        return launch_decode_kernel<64, true, true>(grid, n_splits, stream, qkv, ldq, out, ldo, positions, block_table,
+                                                    table_width, k_pool, v_pool, KV, G, scale, window, n_splits, nullptr,
+                                                    nullptr, rope);
+    if (hd == 128)
+        return launch_decode_kernel<128, true, true>(grid, n_splits, stream, qkv, ldq, out, ldo, positions, block_table,
+                                                     table_width, k_pool, v_pool, KV, G, scale, window, n_splits, nullptr,
+                                                     nullptr, rope);
     return FG_ERR_BAD_SIZE;
 }
 

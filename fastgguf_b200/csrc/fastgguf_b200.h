@@ -55,6 +55,10 @@ int fg_attention_decode(const void *q, int ldq, void *out, int ldo, const int *p
                         int table_width, const void *k_pool, const void *v_pool, int B, int H, int KV, int hd,
                         int page_size, float scale, int window, int n_splits, float *part_o, float *part_ml,
                         cudaStream_t stream);
+int fg_attention_decode_fused(const void *qkv, int ldq, void *out, int ldo, const int *positions,
+                              const int *block_table, int table_width, void *k_pool, void *v_pool, const float *cos_t,
+                              const float *sin_t, int B, int H, int KV, int hd, int page_size, float scale, int window,
+                              int n_splits, cudaStream_t stream);
 int fg_attention_prefill(const void *q, int ldq, void *out, int ldo, const int *cu_rows, const int *seq_start,
                          const int *block_table, int table_width, const void *k_pool, const void *v_pool, int n_seq,
                          int max_new, int H, int KV, int hd, int page_size, float scale, int window, cudaStream_t stream);

@@ -10,7 +10,7 @@ from .lib import KernelError, check, dtype_code, lib, ptr, require_cuda, stream
 
 __all__ = [
     "KernelError", "embed_gather", "embed_gather_norm", "rmsnorm", "rope_append", "silu_mul", "gemm_generic",
-    "attention_generic", "attention", "sample", "argmax", "decode_advance",
+    "attention_generic", "attention", "rope_attention", "sample", "argmax", "decode_advance",
 ]
 
 
@@ -183,6 +183,24 @@ def attention(q: torch.Tensor, batch, block_table: torch.Tensor, k_pool: torch.T
                        n_heads, n_kv_heads, head_dim, scale, window)
     return attention_generic(q, batch.positions, batch.row_seq, block_table, k_pool, v_pool,
                              n_heads, n_kv_heads, head_dim, scale, window)
+
+
+def rope_attention(qkv: torch.Tensor, batch, block_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                   cos: torch.Tensor, sin: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                   window: int = 0, write_kv: bool = True) -> torch.Tensor:
+    """Rotary encoding of q (and k), cache append (when ``write_kv``) and attention of a step's rows.
+    A decode step in bfloat16 with head size 64 / 128 runs as one kernel; everything else as RoPE + append
+    followed by the attention kernel the step's shape calls for."""
+    from . import fast_attention
+    if (write_kv and batch.single_token and fast_attention.supported(qkv, k_pool, head_dim)
+            and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0):
+        out = fast_attention.attention_decode_fused(qkv, batch.positions, block_table, k_pool, v_pool, cos, sin,
+                                                    n_heads, n_kv_heads, head_dim, scale, window)
+        if out is not None:
+            return out
+    rope_append(qkv, batch.positions, batch.row_seq, block_table, k_pool, v_pool, cos, sin, n_heads, n_kv_heads,
+                head_dim, write_kv=write_kv)
+    return attention(qkv, batch, block_table, k_pool, v_pool, n_heads, n_kv_heads, head_dim, scale, window)
 
 
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:

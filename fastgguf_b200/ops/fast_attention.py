@@ -14,6 +14,8 @@ from .lib import check, lib, ptr, register_signatures, stream
 register_signatures("attn", {
     "fg_attention_decode": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "fg_attention_decode_fused": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
     "fg_attention_prefill_tc": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "fg_attention_prefill_tc_error": [],
@@ -91,3 +93,23 @@ def attention_prefill_tc(q, cu_rows, seq_start, block_table, k_pool, v_pool, n_s
 def prefill_tc_error() -> int:
     """0, or the code of the first bounded wait of the tcgen05 attention that ran out (clears it)."""
     return int(lib("attn").fg_attention_prefill_tc_error())
+
+
+def attention_decode_fused(qkv, positions, block_table, k_pool, v_pool, cos, sin, n_heads, n_kv_heads, head_dim,
+                           scale, window=0, n_splits: Optional[int] = None, out=None):
+    """RoPE of q and of the new k, cache append and attention of one new token per sequence in ONE kernel.
+    qkv: [B, >= (H + 2 KV) * hd] bf16 straight from the projection.  None when the step needs more than 8 splits
+    (very long contexts): the caller then runs RoPE + append and attention separately."""
+    B = qkv.shape[0]
+    if n_splits is None:
+        n_splits = decode_splits(B, n_heads, n_kv_heads, block_table.shape[1])
+    if n_splits not in (1, 2, 4, 8):
+        return None
+    if out is None:
+        out = torch.empty((B, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    check(lib("attn").fg_attention_decode_fused(ptr(qkv), qkv.stride(0), ptr(out), out.stride(0), ptr(positions),
+                                                ptr(block_table), block_table.shape[1], ptr(k_pool), ptr(v_pool),
+                                                ptr(cos), ptr(sin), B, n_heads, n_kv_heads, head_dim, k_pool.shape[2],
+                                                float(scale), int(window), n_splits, stream()),
+          "attention_decode_fused")
+    return out

@@ -63,14 +63,11 @@ class GQAAttention(Mixer):
         proj = self.qkv if io.write_cache else self.q_only
         qkv = proj.forward(xn, out_dtype=self.runtime.dtype)
         table = batch.block_tables[io.group]
-        if self.position is not None:
-            ops.rope_append(qkv, batch.positions, batch.row_seq, table, io.k_pool, io.v_pool,
-                            self.position.cos, self.position.sin, self.n_heads, self.n_kv_heads,
-                            self.head_dim, write_kv=io.write_cache)
-        else:
+        if self.position is None:
             raise NotImplementedError("attention without a position encoding is not built")
-        attn = ops.attention(qkv, batch, table, io.k_pool, io.v_pool, self.n_heads, self.n_kv_heads,
-                             self.head_dim, self.scale, self.window or 0)
+        attn = ops.rope_attention(qkv, batch, table, io.k_pool, io.v_pool, self.position.cos, self.position.sin,
+                                  self.n_heads, self.n_kv_heads, self.head_dim, self.scale, self.window or 0,
+                                  write_kv=io.write_cache)
         if emit_norm is None:
             self.o.forward(attn, out=residual, accumulate=True)
             return None

@@ -121,3 +121,30 @@ def test_attention_prefill_tcgen05(H, KV, hd, window):
                                               case["k_pool"], case["v_pool"], len(new), max(new), H, KV, hd, scale, window)
     assert fast_attention.prefill_tc_error() == 0
     assert _err(got, plain(case, H, KV, hd, scale, window)) < 1.5e-2
+
+
+@pytest.mark.parametrize("n_splits", [None, 1, 4, 8])
+@pytest.mark.parametrize("H,KV,hd,window", [(8, 2, 64, 0), (6, 2, 128, 0), (20, 1, 64, 0), (4, 4, 64, 100)])
+def test_attention_decode_fused_with_rope_and_append(H, KV, hd, window, n_splits):
+    """One kernel for RoPE, cache append and attention of a decode step, against the separate kernels."""
+    from fastgguf_b200 import ops
+    from fastgguf_b200.ops import fast_attention
+    lens = [0, 63, 64, 700, 2047, 129]
+    case = make_case(lens, [1] * 6, H, KV, hd, torch.bfloat16, 15)
+    g = torch.Generator().manual_seed(16)
+    qkv = torch.randn(6, (H + 2 * KV) * hd, generator=g).bfloat16().cuda()
+    ang = torch.arange(2100, dtype=torch.float64)[:, None] * torch.pow(torch.tensor(10000.0, dtype=torch.float64),
+                                                                       -2.0 * torch.arange(hd // 2) / hd)
+    cos, sin = torch.cos(ang).float().cuda(), torch.sin(ang).float().cuda()
+    scale = 1.0 / math.sqrt(hd)
+    row_seq = torch.arange(6, dtype=torch.int32).cuda()
+    # separate kernels on copies of the cache
+    k1, v1, q1 = case["k_pool"].clone(), case["v_pool"].clone(), qkv.clone()
+    ops.rope_append(q1, case["positions"], row_seq, case["table"], k1, v1, cos, sin, H, KV, hd)
+    want = fast_attention.attention_decode(q1, case["positions"], case["table"], k1, v1, H, KV, hd, scale, window,
+                                           n_splits=n_splits)
+    k2, v2 = case["k_pool"].clone(), case["v_pool"].clone()
+    got = fast_attention.attention_decode_fused(qkv, case["positions"], case["table"], k2, v2, cos, sin, H, KV, hd,
+                                                scale, window, n_splits=n_splits)
+    assert (got.float() - want.float()).abs().max() <= 2e-2 * want.float().abs().max()
+    assert torch.equal(k2, k1) and torch.equal(v2, v1)          # the cache received the same rows
