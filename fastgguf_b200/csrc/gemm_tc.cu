@@ -7,8 +7,10 @@
 // One CTA computes a 128 x BN tile of the MMA: "P" rows are its M side (128), "Q" rows its N side.
 //   SWAP (decode, up to 64 tokens): P = weight rows, Q = token rows (BN = 16/32/64).  The kernel
 //     streams the weights once; when there are too few tiles to fill the GPU, a thread-block
-//     cluster of 2/4/8 CTAs splits K, and the CTAs sum their partial tiles in rank order
-//     (deterministic) through distributed shared memory - no scratch in global memory.
+//     cluster of 2/4/8 CTAs splits K: every CTA pushes the columns of its partial tile into the
+//     shared memory of the CTA that owns them (st.shared::cluster), one cluster barrier makes the
+//     pushes visible, and the owner sums them in rank order (deterministic) from its own shared
+//     memory - no scratch in global memory, no remote loads.
 //   not SWAP (prefill): P = 128 token rows, Q = BN = 128/256 weight rows; a thread of the epilogue
 //     owns one token row and writes runs of consecutive features with 16-byte stores.
 //
@@ -67,6 +69,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+// the same with an L2 eviction policy: weights of a decode step are read once, and marking them evict-first keeps
+// them from pushing everything else (activations, the cache, norm weights, the kernels' own code) out of L2
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar), "l"(policy) : "memory");
+}
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -111,16 +124,29 @@ __device__ __forceinline__ void cluster_sync() {
     __syncwarp();                                 // lanes that skipped a single-lane role rejoin first
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// read a float at the same shared-memory offset in the CTA of rank `rank` of this cluster
-__device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, int rank) {
+// write a float to the same shared-memory offset in the CTA of rank `rank` of this cluster
+__device__ __forceinline__ void st_dsmem_f32(uint32_t local_addr, int rank, float v) {
     uint32_t remote;
-    float v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
+// warp sums of N independent values: the shuffles of one round are issued back to back, so the latency of a round
+// is paid once, not once per value
+template <int N> __device__ __forceinline__ void warp_sum_n(float (&v)[N]) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float t[N];
+#pragma unroll
+        for (int i = 0; i < N; i++) t[i] = __shfl_xor_sync(0xffffffffu, v[i], o);
+#pragma unroll
+        for (int i = 0; i < N; i++) v[i] += t[i];
+    }
+}
 
 struct GemmArgs {
     void *out;            // [M, ldc] bf16 or f32 by epilogue
@@ -251,7 +277,7 @@ __device__ __forceinline__ void epilogue_token_major(const GemmArgs &a, uint32_t
     }
 }
 
-template <int BN, int STAGES, int EPI, bool SWAP>
+template <int BN, int STAGES, int EPI, bool SWAP, bool SPLIT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, GemmArgs a) {
     constexpr int P_BYTES = BM * BK * 2, Q_BYTES = BN * BK * 2;
@@ -267,6 +293,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     __shared__ float inv_s[SWAP ? BN : 1];        // 1/rms of the token columns (deferred norm), else 1
     __shared__ float red_s[SWAP ? BN : 1][4];     // per-column partial sums of squares of the four epilogue warps
 
+    constexpr int RES_AHEAD = 8;                  // residual values of the split-K reduce fetched during the main loop
+    float res_pre[RES_AHEAD], nw_pre = 0.f;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int p0 = blockIdx.x * BM, q0 = blockIdx.y * BN;
     const int total_kb = (a.K + BK - 1) / BK;
@@ -274,6 +302,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     const int nkb = min(a.kb_per_split, total_kb - kb0);
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), tfull = smem_u32(&bars[2 * STAGES]);
     const uint32_t smem0 = smem_u32(smem);
+    // split-K: partial columns arrive here from the whole cluster, [rank][BN / S columns][128 rows] f32; a region
+    // of its own, since a faster CTA pushes while this one is still in its main loop
+    float *recv = (float *)(smem + STAGES * STAGE_BYTES);
+    if (SPLIT) cluster_arrive_relaxed();          // matched before the first push: every CTA of the cluster runs
     const CUtensorMap *tmW = SWAP ? &tmP : &tmQ, *tmX = SWAP ? &tmQ : &tmP;
     const int w_row = SWAP ? p0 : q0, x_row = SWAP ? q0 : p0;
 
@@ -301,9 +333,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             const int pre = min(STAGES, nkb);
+            const uint64_t stream_once = l2_evict_first_policy();
             for (int kb = 0; kb < pre; kb++) {             // weights of the first stages: no dependency
                 mbar_expect_tx(full0 + 8 * kb, STAGE_BYTES);
-                tma_load_2d(smem0 + kb * STAGE_BYTES + W_OFF, tmW, (kb0 + kb) * BK, w_row, full0 + 8 * kb);
+                tma_load_2d_hint(smem0 + kb * STAGE_BYTES + W_OFF, tmW, (kb0 + kb) * BK, w_row, full0 + 8 * kb, stream_once);
             }
             pdl_wait();                                    // activations come from the kernel before
             for (int kb = 0; kb < pre; kb++)
@@ -314,7 +347,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                 if (!mbar_wait(empty0 + 8 * s, ((kb / STAGES) & 1) ^ 1)) { raise_error(1); break; }
                 uint32_t dst = smem0 + s * STAGE_BYTES, bar = full0 + 8 * s;
                 mbar_expect_tx(bar, STAGE_BYTES);
-                tma_load_2d(dst + W_OFF, tmW, (kb0 + kb) * BK, w_row, bar);
+                tma_load_2d_hint(dst + W_OFF, tmW, (kb0 + kb) * BK, w_row, bar, stream_once);
                 tma_load_2d(dst + X_OFF, tmX, (kb0 + kb) * BK, x_row, bar);
                 issued = kb + 1;
             }
@@ -343,16 +376,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
-        pdl_wait();
         const int lg = warp & 3;                  // the TMEM lane group this warp may read
         const int prow = lg * 32 + lane;          // row of the tile this thread owns
+        // the next norm's weight of this thread's feature: a weight, so it is fetched before the wait on the
+        // preceding kernel (a miss in L2 behind the weight tiles in flight takes microseconds)
+        if (SWAP && EPI == EPI_ADD_F32 && a.norm_w && p0 + prow < a.N)
+            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(nw_pre) : "l"(a.norm_w + p0 + prow));     // volatile: stays here
+        pdl_wait();
         if (SWAP) {
             // 1/rms of the token columns of this tile, while the main loop runs
             for (int c = prow; c < BN; c += 128)
                 inv_s[c] = (a.ss_in && q0 + c < a.M) ? inv_rms(a, q0 + c) : 1.0f;
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
-        bool ok = nkb > 0 ? mbar_wait(tfull, 0) : true;
+        if (SPLIT && EPI == EPI_ADD_F32) {
+            // split-K: the residual values and the norm weight this thread will need after the main loop
+            const int per = BN / (int)gridDim.z, c_begin = blockIdx.z * per, n = p0 + prow;
+#pragma unroll
+            for (int i = 0; i < RES_AHEAD; i++) {
+                const int m = q0 + c_begin + i;
+                res_pre[i] = (i < per && n < a.N && m < a.M) ? __ldcg((const float *)a.out + (size_t)m * a.ldc + n) : 0.f;
+            }
+        }
+        // one lane of each warp polls the barrier: 128 polling threads would crowd the shared-memory pipeline
+        // that the other CTA on this SM needs for its own epilogue
+        int ok_i = 1;
+        if (lane == 0 && nkb > 0) ok_i = mbar_wait(tfull, 0) ? 1 : 0;
+        const bool ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
         if (!ok) raise_error(3);
         tc_fence_after();
         const uint32_t trow = tmem_base + ((uint32_t)(lg * 32) << 16);
@@ -360,50 +410,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
             // thread = weight row (feature), columns = tokens
             const int n = p0 + prow;
             const bool n_ok = n < a.N;
-            const int splits = gridDim.z;
             if (EPI == EPI_SILU_MUL) {
-                // rows 0..63 of the tile are gate, 64..127 up of the same 64 features: meet through smem
-                float *ex = (float *)smem;        // [64][BN]; the stages are idle once tfull has fired
-                if (ok && prow >= 64) {
-                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                // rows 0..63 of the tile are gate, 64..127 up of the same 64 features: both halves go to
+                // shared memory as [token][feature], then all 128 threads share the activations
+                float *exg = (float *)smem;       // [BN][64]; the stages are idle once tfull has fired
+                float *exu = exg + BN * 64;
+                const int ncol = min(BN, a.M - q0);
+                if (ok) {
+                    float *ex = prow < 64 ? exg : exu;
+                    for (int c0 = 0; c0 < ncol; c0 += 16) {
                         float v[16];
                         tc_ld16(trow + c0, v);
 #pragma unroll
-                        for (int j = 0; j < 16; j++) ex[(prow - 64) * BN + c0 + j] = v[j];
+                        for (int j = 0; j < 16; j++) ex[(c0 + j) * 64 + (prow & 63)] = v[j];
                     }
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                const int f = (p0 >> 1) + prow;
-                if (ok && prow < 64) {
-                    for (int c0 = 0; c0 < BN; c0 += 16) {
-                        float v[16];
-                        tc_ld16(trow + c0, v);
-#pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            int m = q0 + c0 + j;
-                            float iv = inv_s[c0 + j];
-                            if (m < a.M && f < (a.N >> 1))
-                                ((bf16 *)a.out)[(size_t)m * a.ldc + f] =
-                                    __float2bfloat16_rn(silu_mul(v[j] * iv, ex[prow * BN + c0 + j] * iv));
-                        }
+                const int fl = prow & 63, f = (p0 >> 1) + fl;
+                if (ok && f < (a.N >> 1)) {
+                    for (int c = prow >> 6; c < ncol; c += 2) {     // the halves take alternate tokens
+                        const float iv = inv_s[c];
+                        ((bf16 *)a.out)[(size_t)(q0 + c) * a.ldc + f] =
+                            __float2bfloat16_rn(silu_mul(exg[c * 64 + fl] * iv, exu[c * 64 + fl] * iv));
                     }
                 }
-            } else if (splits > 1) {
-                // partial tile -> own shared memory, column-major so that a warp touches consecutive words;
-                // the cluster then sums the partials of its CTAs (below)
-                float *part = (float *)smem;      // [BN][128]; the stages are idle once tfull has fired
-                if (ok) {
-                    for (int c0 = 0; c0 < BN; c0 += 16) {
-                        float v[16];
-                        tc_ld16(trow + c0, v);
+            } else if (SPLIT) {
+                // partial tile -> the owners of its columns: CTA r of the cluster sums columns [r * per, (r + 1) * per)
+                const int S = gridDim.z, per = BN / S, per_log = __ffs(per) - 1;      // BN and S are powers of two
+                cluster_wait();                   // every CTA of the cluster has started (arrived at its top)
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
+                    if (ok && nkb > 0) tc_ld16(trow + c0, v);
 #pragma unroll
-                        for (int j = 0; j < 16; j++) part[(c0 + j) * BM + prow] = nkb > 0 ? v[j] : 0.f;
+                    for (int j = 0; j < 16; j++) {
+                        const int c = c0 + j, r = c >> per_log, cl = c & (per - 1);
+                        st_dsmem_f32(smem_u32(&recv[((int)blockIdx.z * per + cl) * BM + prow]), r, (ok && nkb > 0) ? v[j] : 0.f);
                     }
                 }
             } else {
                 for (int c0 = 0; c0 < BN; c0 += 16) {
                     float v[16];
                     if (ok) tc_ld16(trow + c0, v);
+                    float sqs[16];
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         int m = q0 + c0 + j;
@@ -417,15 +465,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                                 val += ((float *)a.out)[idx];
                                 ((float *)a.out)[idx] = val;
                                 if (a.norm_w) {
-                                    a.xw_out[(size_t)m * a.N + n] = __float2bfloat16_rn(val * a.norm_w[n]);
+                                    a.xw_out[(size_t)m * a.N + n] = __float2bfloat16_rn(val * nw_pre);
                                     sq = val * val;
                                 }
                             }
                         }
-                        if (EPI == EPI_ADD_F32 && a.norm_w) {
-                            sq = warp_sum(sq);
-                            if (lane == 0) red_s[c0 + j][lg] = sq;
-                        }
+                        sqs[j] = sq;
+                    }
+                    if (EPI == EPI_ADD_F32 && a.norm_w) {
+                        warp_sum_n(sqs);
+                        // every lane holds the sums and writes them (same values, same addresses): a branch on
+                        // the lane here made the compiler split lane 0 from the others for the rest of the epilogue
+#pragma unroll
+                        for (int j = 0; j < 16; j++) red_s[c0 + j][lg] = sqs[j];
                     }
                 }
                 if (EPI == EPI_ADD_F32 && a.norm_w) {
@@ -440,45 +492,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         }
         tc_fence_before();
     }
-    if (SWAP && EPI != EPI_SILU_MUL && gridDim.z > 1) {
-        // ---- split-K: the CTAs of a cluster hold partial tiles of the same outputs in their shared
-        // memory; CTA r sums columns [r * BN / S, (r + 1) * BN / S) over all CTAs in rank order
-        // (deterministic) through distributed shared memory and runs the epilogue on them
+    if (SPLIT) {
+        // ---- split-K: after the barrier this CTA's shared memory holds, for its columns, the partial sums of
+        // every CTA of the cluster; they are added in rank order and the epilogue runs on the totals
         const int S = gridDim.z;
+        if (warp < 2) { __syncwarp(); cluster_wait(); }        // the barrier phase opened at the top
         cluster_sync();
         if (warp >= 2) {
             const int lg = warp & 3, prow = lg * 32 + lane, n = p0 + prow;
-            const float *part = (const float *)smem;
             const int per = BN / S, c_begin = blockIdx.z * per;
             const bool emit = EPI == EPI_ADD_F32 && a.norm_w != nullptr;
-            for (int c = c_begin; c < c_begin + per; c++) {
-                const int m = q0 + c;
-                const bool in = n < a.N && m < a.M;
-                const size_t idx = (size_t)m * a.ldc + n;
-                float res = 0.f;
-                if (EPI == EPI_ADD_F32 && in) res = ((const float *)a.out)[idx];   // in flight during the remote reads
-                const uint32_t local = smem_u32(&part[c * BM + prow]);
+            // One pass of this code per launch: it is fetched cold, so it is kept small (a rolled loop over the
+            // columns); only the loads of one column's partial sums are unrolled, to have them in flight together.
+#pragma unroll 1
+            for (int cl = 0; cl < per; cl++) {
+                const int c = c_begin + cl, m = q0 + c;
                 float pz[8];
 #pragma unroll
-                for (int z = 0; z < 8; z++) pz[z] = z < S ? ld_dsmem_f32(local, z) : 0.f;
+                for (int z = 0; z < 8; z++) pz[z] = z < S ? recv[(z * per + cl) * BM + prow] : 0.f;
                 float v = 0.f;
 #pragma unroll
                 for (int z = 0; z < 8; z++) v += pz[z];                            // rank order; absent ranks add 0
                 v *= inv_s[c];
                 float sq = 0.f;
-                if (in) {
+                if (n < a.N && m < a.M) {
+                    const size_t idx = (size_t)m * a.ldc + n;
                     if (EPI == EPI_BF16) ((bf16 *)a.out)[idx] = __float2bfloat16_rn(v);
                     else if (EPI == EPI_F32) ((float *)a.out)[idx] = v;
                     else {
-                        v += res;
+                        v += cl < RES_AHEAD ? res_pre[cl] : ((const float *)a.out)[idx];
                         ((float *)a.out)[idx] = v;
-                        if (emit) { a.xw_out[(size_t)m * a.N + n] = __float2bfloat16_rn(v * a.norm_w[n]); sq = v * v; }
+                        if (emit) { a.xw_out[(size_t)m * a.N + n] = __float2bfloat16_rn(v * nw_pre); sq = v * v; }
                     }
                 }
-                if (emit) {
-                    sq = warp_sum(sq);
-                    if (lane == 0) red_s[c - c_begin][lg] = sq;
-                }
+                if (emit) red_s[cl][lg] = warp_sum(sq);                            // by every lane: same value, same address
             }
             if (emit) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -487,7 +534,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                         red_s[prow][0] + red_s[prow][1] + red_s[prow][2] + red_s[prow][3];
             }
         }
-        cluster_sync();                           // no CTA leaves while its partial is still being read
     }
     __syncthreads();
     if (warp == 1) {
@@ -643,16 +689,16 @@ static int make_map(CUtensorMap *map, const void *base, int rows, int K, int ld,
     return r == CUDA_SUCCESS ? 0 : FG_ERR_TENSORMAP;
 }
 
-template <int BN, int STAGES, int EPI, bool SWAP>
+template <int BN, int STAGES, int EPI, bool SWAP, bool SPLIT>
 static int launch(const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs &a, dim3 grid, cudaStream_t stream) {
-    constexpr int smem = STAGES * (BM + BN) * BK * 2 + 1024;
+    constexpr int smem = STAGES * (BM + BN) * BK * 2 + 1024 + (SPLIT ? BN * BM * 4 : 0);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI, SWAP, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return fg_launch_cluster(gemm_tc_kernel<BN, STAGES, EPI, SWAP>, grid, dim3(GEMM_THREADS), (size_t)smem, stream,
+    return fg_launch_cluster(gemm_tc_kernel<BN, STAGES, EPI, SWAP, SPLIT>, grid, dim3(GEMM_THREADS), (size_t)smem, stream,
                              (int)grid.z, tmP, tmQ, a);
 }
 
@@ -677,11 +723,20 @@ static int launch_prefill(const CUtensorMap &tmP, const CUtensorMap &tmQ, const 
 
 template <int EPI>
 static int dispatch(bool swap, int bn, const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs &a, dim3 grid, cudaStream_t st) {
-    if (swap) {
+    if (swap && grid.z > 1) {
+        // stages and the receive buffer of the split-K sum together leave room for two CTAs per SM
+        if (EPI != EPI_SILU_MUL) {
+            switch (bn) {
+            case 16: return launch<16, 5, EPI, true, true>(tmP, tmQ, a, grid, st);
+            case 32: return launch<32, 4, EPI, true, true>(tmP, tmQ, a, grid, st);
+            case 64: return launch<64, 3, EPI, true, true>(tmP, tmQ, a, grid, st);
+            }
+        }
+    } else if (swap) {
         switch (bn) {
-        case 16: return launch<16, 6, EPI, true>(tmP, tmQ, a, grid, st);
-        case 32: return launch<32, 5, EPI, true>(tmP, tmQ, a, grid, st);
-        case 64: return launch<64, 4, EPI, true>(tmP, tmQ, a, grid, st);
+        case 16: return launch<16, 6, EPI, true, false>(tmP, tmQ, a, grid, st);
+        case 32: return launch<32, 5, EPI, true, false>(tmP, tmQ, a, grid, st);
+        case 64: return launch<64, 4, EPI, true, false>(tmP, tmQ, a, grid, st);
         }
     } else {
         switch (bn) {
