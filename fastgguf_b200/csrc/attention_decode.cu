@@ -48,7 +48,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
                    bf16 *__restrict__ out, int ldo, RopeArgs rope) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int TILE_BYTES = PAGE * HD * 2;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = warp_index(), lane = threadIdx.x & 31;
     const int chunks = (G + 15) / 16;
     const int kvh = blockIdx.y / chunks, g0 = (blockIdx.y % chunks) * 16;
     const int rows = min(16, G - g0);

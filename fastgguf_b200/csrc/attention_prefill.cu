@@ -35,7 +35,7 @@ attn_prefill_kernel(const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out,
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int TILE_BYTES = PAGE * HD * 2;
     constexpr int PF_ROWS = PF_WARPS * 16;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    const int warp = warp_index(), lane = threadIdx.x & 31, tid = threadIdx.x;
     const int Gc = G < 16 ? G : 16;
     const int TQ = PF_ROWS / Gc;                       // new tokens per CTA tile
     const int chunks = (G + Gc - 1) / Gc;

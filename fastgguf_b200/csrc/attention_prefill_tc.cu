@@ -121,7 +121,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     __shared__ __align__(8) uint64_t bars[7];
     __shared__ uint32_t tmem_base_s;
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = warp_index(), lane = threadIdx.x & 31;
     const int Gc = G < 16 ? G : 16, TQ = ROWS / Gc, chunks = (G + Gc - 1) / Gc;
     const int kvh = blockIdx.y / chunks, g0 = (blockIdx.y % chunks) * Gc;
     const int b = blockIdx.z;

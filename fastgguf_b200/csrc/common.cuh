@@ -33,6 +33,12 @@ __device__ __forceinline__ float load_as(const void *base, int dtype, size_t idx
     return dtype == FG_F32 ? ((const float *)base)[idx] : __bfloat162float(((const bf16 *)base)[idx]);
 }
 
+// The index of this thread's warp, read through a shuffle from lane 0.  The value is the same as threadIdx.x >> 5,
+// but the compiler then knows that it does not differ between the lanes of a warp, and branches on it (the roles
+// of a warp-specialised kernel) are uniform.  With the plain shift such branches counted as divergent, and warp
+// shuffles inside them were measured at eight times their usual latency.
+__device__ __forceinline__ int warp_index() { return __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

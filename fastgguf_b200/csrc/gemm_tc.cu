@@ -52,7 +52,7 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// bounded wait: false when the limit ran out
+// bounded wait: false when the limit ran out (not inlined: it has many call sites, and code size counts)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     long long t0 = clock64();
     for (;;) {
@@ -164,6 +164,7 @@ struct GemmArgs {
     const float *norm_w;  // [N], or null
     bf16 *xw_out;         // [M, N]
     float *ss_out;        // [tiles, M]
+    int epi, stages;      // decode kernel: epilogue and ring depth are run-time values
 };
 
 __device__ __forceinline__ float inv_rms(const GemmArgs &a, int m) {
@@ -277,40 +278,44 @@ __device__ __forceinline__ void epilogue_token_major(const GemmArgs &a, uint32_t
     }
 }
 
-template <int BN, int STAGES, int EPI, bool SWAP, bool SPLIT>
+// ---------------------------------------------------------------------------- decode: weights stream once
+// One kernel for every projection of a decode step: the epilogue, the number of K splits and the depth of the
+// ring are run-time values.  A decode step alternates between four or five projections per layer, each launch
+// runs its code once, and code that has left the SM's instruction cache is fetched again at hundreds of cycles
+// a line: one small kernel that every projection shares stays resident, a family of specialised ones does not.
+// For the same reason the once-per-launch epilogue code is written as rolled loops.
+#define MAX_STAGES 6
+
+template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, GemmArgs a) {
-    constexpr int P_BYTES = BM * BK * 2, Q_BYTES = BN * BK * 2;
-    constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
+gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmArgs a) {
+    constexpr int W_BYTES = BM * BK * 2, X_BYTES = BN * BK * 2;
+    constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
     constexpr int TMEM_COLS = BN <= 32 ? 32 : BN;
-    // which part of a stage holds weights: they are fetched before the wait on the previous kernel
-    constexpr int W_OFF = SWAP ? 0 : P_BYTES, X_OFF = SWAP ? P_BYTES : 0;
+    constexpr int RES_AHEAD = 8;                  // residual values of the split-K sum fetched during the main loop
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms need 1 KB alignment
-    __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+    __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 1];
     __shared__ uint32_t tmem_base_s;
-    __shared__ float inv_s[SWAP ? BN : 1];        // 1/rms of the token columns (deferred norm), else 1
-    __shared__ float red_s[SWAP ? BN : 1][4];     // per-column partial sums of squares of the four epilogue warps
+    __shared__ float inv_s[BN];                   // 1/rms of the token columns (deferred norm), else 1
 
-    constexpr int RES_AHEAD = 8;                  // residual values of the split-K reduce fetched during the main loop
-    float res_pre[RES_AHEAD], nw_pre = 0.f;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int p0 = blockIdx.x * BM, q0 = blockIdx.y * BN;
+    const int warp = warp_index(), lane = threadIdx.x & 31;      // uniform: the role branches below are not divergent
+    const int stages = a.stages, epi = a.epi, S = gridDim.z;
+    const bool split = S > 1;
+    const int p0 = blockIdx.x * BM;               // first weight row (feature) of the tile; tokens are columns 0 .. BN
     const int total_kb = (a.K + BK - 1) / BK;
     const int kb0 = blockIdx.z * a.kb_per_split;
     const int nkb = min(a.kb_per_split, total_kb - kb0);
-    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), tfull = smem_u32(&bars[2 * STAGES]);
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[MAX_STAGES]), tfull = smem_u32(&bars[2 * MAX_STAGES]);
     const uint32_t smem0 = smem_u32(smem);
     // split-K: partial columns arrive here from the whole cluster, [rank][BN / S columns][128 rows] f32; a region
     // of its own, since a faster CTA pushes while this one is still in its main loop
-    float *recv = (float *)(smem + STAGES * STAGE_BYTES);
-    if (SPLIT) cluster_arrive_relaxed();          // matched before the first push: every CTA of the cluster runs
-    const CUtensorMap *tmW = SWAP ? &tmP : &tmQ, *tmX = SWAP ? &tmQ : &tmP;
-    const int w_row = SWAP ? p0 : q0, x_row = SWAP ? q0 : p0;
+    float *recv = (float *)(smem + stages * STAGE_BYTES);
+    if (split) cluster_arrive_relaxed();          // matched before the first push: every CTA of the cluster runs
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int s = 0; s < stages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(tfull, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -325,52 +330,57 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     const uint32_t tmem_base = tmem_base_s;
     pdl_launch_dependents();
     if (threadIdx.x == 32) {                      // descriptors into the cache before their first use
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmP) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmQ) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmX) : "memory");
     }
+    float res_pre[RES_AHEAD], nw_pre[4] = {0.f, 0.f, 0.f, 0.f};
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            const int pre = min(STAGES, nkb);
+            const int pre = min(stages, nkb);
             const uint64_t stream_once = l2_evict_first_policy();
             for (int kb = 0; kb < pre; kb++) {             // weights of the first stages: no dependency
                 mbar_expect_tx(full0 + 8 * kb, STAGE_BYTES);
-                tma_load_2d_hint(smem0 + kb * STAGE_BYTES + W_OFF, tmW, (kb0 + kb) * BK, w_row, full0 + 8 * kb, stream_once);
+                tma_load_2d_hint(smem0 + kb * STAGE_BYTES, &tmW, (kb0 + kb) * BK, p0, full0 + 8 * kb, stream_once);
             }
             pdl_wait();                                    // activations come from the kernel before
             for (int kb = 0; kb < pre; kb++)
-                tma_load_2d(smem0 + kb * STAGE_BYTES + X_OFF, tmX, (kb0 + kb) * BK, x_row, full0 + 8 * kb);
-            int issued = pre;
-            for (int kb = pre; kb < nkb; kb++) {
-                int s = kb % STAGES;
-                if (!mbar_wait(empty0 + 8 * s, ((kb / STAGES) & 1) ^ 1)) { raise_error(1); break; }
-                uint32_t dst = smem0 + s * STAGE_BYTES, bar = full0 + 8 * s;
+                tma_load_2d(smem0 + kb * STAGE_BYTES + W_BYTES, &tmX, (kb0 + kb) * BK, 0, full0 + 8 * kb);
+            int s = 0, ph = 1;                             // ring position of K-block `kb`, parity of its empty barrier
+            bool ok = true;
+            for (int kb = pre; kb < nkb && ok; kb++) {
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { raise_error(1); ok = false; break; }
+                const uint32_t dst = smem0 + s * STAGE_BYTES, bar = full0 + 8 * s;
                 mbar_expect_tx(bar, STAGE_BYTES);
-                tma_load_2d_hint(dst + W_OFF, tmW, (kb0 + kb) * BK, w_row, bar, stream_once);
-                tma_load_2d(dst + X_OFF, tmX, (kb0 + kb) * BK, x_row, bar);
-                issued = kb + 1;
+                tma_load_2d_hint(dst, &tmW, (kb0 + kb) * BK, p0, bar, stream_once);
+                tma_load_2d(dst + W_BYTES, &tmX, (kb0 + kb) * BK, 0, bar);
+                if (++s == stages) { s = 0; ph ^= 1; }
             }
-            // copies still in flight must land before the CTA may exit
-            for (int kb = max(0, issued - STAGES); kb < issued; kb++)
-                mbar_wait(full0 + 8 * (kb % STAGES), (kb / STAGES) & 1);
+            // copies still in flight must land before the CTA may exit: the last pass over the ring
+            if (!ok || nkb <= stages) { for (int j = 0; j < min(stages, nkb); j++) mbar_wait(full0 + 8 * j, 0); }
+            else {
+                // K-block kb sits in stage kb % stages with parity (kb / stages) & 1; wait for the last `stages` of them
+                for (int kb = nkb - stages; kb < nkb; kb++) mbar_wait(full0 + 8 * (kb % stages), (kb / stages) & 1);
+            }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = make_idesc(BM, BN);
+            int s = 0, ph = 0;
             for (int kb = 0; kb < nkb; kb++) {
-                int s = kb % STAGES;
-                if (!mbar_wait(full0 + 8 * s, (kb / STAGES) & 1)) { raise_error(2); break; }
+                if (!mbar_wait(full0 + 8 * s, ph)) { raise_error(2); break; }
                 tc_fence_after();
-                uint32_t sa = smem0 + s * STAGE_BYTES;
-                uint64_t pdesc = make_smem_desc(sa), qdesc = make_smem_desc(sa + P_BYTES);
+                const uint32_t sa = smem0 + s * STAGE_BYTES;
+                const uint64_t wdesc = make_smem_desc(sa), xdesc = make_smem_desc(sa + W_BYTES);
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; k++) {
-                    uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);     // advance inside the swizzle row
-                    tc_mma_bf16(tmem_base, pdesc + koff, qdesc + koff, idesc, (kb | k) != 0);
+                    const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);     // advance inside the swizzle row
+                    tc_mma_bf16(tmem_base, wdesc + koff, xdesc + koff, idesc, (kb | k) != 0);
                 }
                 tc_commit(empty0 + 8 * s);        // arrives when these MMAs have read the stage
+                if (++s == stages) { s = 0; ph ^= 1; }
             }
             tc_commit(tfull);                     // arrives when every MMA above is complete
         }
@@ -378,160 +388,137 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         // ------------------------------------------------------------ epilogue (warps 2..5)
         const int lg = warp & 3;                  // the TMEM lane group this warp may read
         const int prow = lg * 32 + lane;          // row of the tile this thread owns
-        // the next norm's weight of this thread's feature: a weight, so it is fetched before the wait on the
-        // preceding kernel (a miss in L2 behind the weight tiles in flight takes microseconds)
-        if (SWAP && EPI == EPI_ADD_F32 && a.norm_w && p0 + prow < a.N)
-            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(nw_pre) : "l"(a.norm_w + p0 + prow));     // volatile: stays here
-        pdl_wait();
-        if (SWAP) {
-            // 1/rms of the token columns of this tile, while the main loop runs
-            for (int c = prow; c < BN; c += 128)
-                inv_s[c] = (a.ss_in && q0 + c < a.M) ? inv_rms(a, q0 + c) : 1.0f;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-        }
-        if (SPLIT && EPI == EPI_ADD_F32) {
-            // split-K: the residual values and the norm weight this thread will need after the main loop
-            const int per = BN / (int)gridDim.z, c_begin = blockIdx.z * per, n = p0 + prow;
+        const bool emit = epi == EPI_ADD_F32 && a.norm_w != nullptr;
+        // the next norm's weights of the features this thread finishes (lane + 32 i): weights, so they are fetched
+        // before the wait on the preceding kernel (a miss in L2 behind the weight tiles in flight takes microseconds)
+        if (emit) {
 #pragma unroll
-            for (int i = 0; i < RES_AHEAD; i++) {
-                const int m = q0 + c_begin + i;
-                res_pre[i] = (i < per && n < a.N && m < a.M) ? __ldcg((const float *)a.out + (size_t)m * a.ldc + n) : 0.f;
-            }
+            for (int i = 0; i < 4; i++)
+                if (p0 + lane + 32 * i < a.N)
+                    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(nw_pre[i]) : "l"(a.norm_w + p0 + lane + 32 * i));
         }
-        // one lane of each warp polls the barrier: 128 polling threads would crowd the shared-memory pipeline
-        // that the other CTA on this SM needs for its own epilogue
+        pdl_wait();
+        // 1/rms of the token columns of this tile, while the main loop runs
+        for (int c = prow; c < BN; c += 128) inv_s[c] = (a.ss_in && c < a.M) ? inv_rms(a, c) : 1.0f;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (split && epi == EPI_ADD_F32) {
+            // the residual values this thread adds to after the main loop: columns w and w + 4 of this CTA's share
+            const int per = BN / S, c_begin = blockIdx.z * per, w = warp - 2;
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int cl = w + 4 * j, m = c_begin + cl, nn = p0 + lane + 32 * i;
+                    res_pre[4 * j + i] = (cl < per && nn < a.N && m < a.M) ? __ldcg((const float *)a.out + (size_t)m * a.ldc + nn) : 0.f;
+                }
+        }
+        // one lane of each warp polls the barrier, the others wait for it at the shuffle
         int ok_i = 1;
         if (lane == 0 && nkb > 0) ok_i = mbar_wait(tfull, 0) ? 1 : 0;
         const bool ok = __shfl_sync(0xffffffffu, ok_i, 0) != 0;
         if (!ok) raise_error(3);
         tc_fence_after();
         const uint32_t trow = tmem_base + ((uint32_t)(lg * 32) << 16);
-        if (SWAP) {
-            // thread = weight row (feature), columns = tokens
-            const int n = p0 + prow;
-            const bool n_ok = n < a.N;
-            if (EPI == EPI_SILU_MUL) {
-                // rows 0..63 of the tile are gate, 64..127 up of the same 64 features: both halves go to
-                // shared memory as [token][feature], then all 128 threads share the activations
-                float *exg = (float *)smem;       // [BN][64]; the stages are idle once tfull has fired
-                float *exu = exg + BN * 64;
-                const int ncol = min(BN, a.M - q0);
-                if (ok) {
-                    float *ex = prow < 64 ? exg : exu;
-                    for (int c0 = 0; c0 < ncol; c0 += 16) {
-                        float v[16];
-                        tc_ld16(trow + c0, v);
-#pragma unroll
-                        for (int j = 0; j < 16; j++) ex[(c0 + j) * 64 + (prow & 63)] = v[j];
-                    }
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                const int fl = prow & 63, f = (p0 >> 1) + fl;
-                if (ok && f < (a.N >> 1)) {
-                    for (int c = prow >> 6; c < ncol; c += 2) {     // the halves take alternate tokens
-                        const float iv = inv_s[c];
-                        ((bf16 *)a.out)[(size_t)(q0 + c) * a.ldc + f] =
-                            __float2bfloat16_rn(silu_mul(exg[c * 64 + fl] * iv, exu[c * 64 + fl] * iv));
-                    }
-                }
-            } else if (SPLIT) {
-                // partial tile -> the owners of its columns: CTA r of the cluster sums columns [r * per, (r + 1) * per)
-                const int S = gridDim.z, per = BN / S, per_log = __ffs(per) - 1;      // BN and S are powers of two
-                cluster_wait();                   // every CTA of the cluster has started (arrived at its top)
-                for (int c0 = 0; c0 < BN; c0 += 16) {
+        const bool have = ok && nkb > 0;          // the accumulator holds this CTA's part of the sum
+        if (epi == EPI_SILU_MUL) {
+            // rows 0..63 of the tile are gate, 64..127 up of the same 64 features: both halves go to
+            // shared memory as [token][feature], then all 128 threads share the activations
+            float *exg = (float *)smem;           // [BN][64]; the stages are idle once tfull has fired
+            float *exu = exg + BN * 64;
+            const int ncol = min(BN, a.M);
+            if (ok) {
+                float *ex = prow < 64 ? exg : exu;
+#pragma unroll 1
+                for (int c0 = 0; c0 < ncol; c0 += 16) {
                     float v[16];
-                    if (ok && nkb > 0) tc_ld16(trow + c0, v);
+                    tc_ld16(trow + c0, v);
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const int c = c0 + j, r = c >> per_log, cl = c & (per - 1);
-                        st_dsmem_f32(smem_u32(&recv[((int)blockIdx.z * per + cl) * BM + prow]), r, (ok && nkb > 0) ? v[j] : 0.f);
-                    }
-                }
-            } else {
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    float v[16];
-                    if (ok) tc_ld16(trow + c0, v);
-                    float sqs[16];
-#pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        int m = q0 + c0 + j;
-                        float sq = 0.f;
-                        if (ok && n_ok && m < a.M) {
-                            size_t idx = (size_t)m * a.ldc + n;
-                            float val = v[j] * inv_s[c0 + j];
-                            if (EPI == EPI_BF16) ((bf16 *)a.out)[idx] = __float2bfloat16_rn(val);
-                            else if (EPI == EPI_F32) ((float *)a.out)[idx] = val;
-                            else {
-                                val += ((float *)a.out)[idx];
-                                ((float *)a.out)[idx] = val;
-                                if (a.norm_w) {
-                                    a.xw_out[(size_t)m * a.N + n] = __float2bfloat16_rn(val * nw_pre);
-                                    sq = val * val;
-                                }
-                            }
-                        }
-                        sqs[j] = sq;
-                    }
-                    if (EPI == EPI_ADD_F32 && a.norm_w) {
-                        warp_sum_n(sqs);
-                        // every lane holds the sums and writes them (same values, same addresses): a branch on
-                        // the lane here made the compiler split lane 0 from the others for the rest of the epilogue
-#pragma unroll
-                        for (int j = 0; j < 16; j++) red_s[c0 + j][lg] = sqs[j];
-                    }
-                }
-                if (EPI == EPI_ADD_F32 && a.norm_w) {
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    for (int c = prow; c < BN; c += 128)
-                        if (q0 + c < a.M)
-                            a.ss_out[(size_t)blockIdx.x * a.M + q0 + c] = red_s[c][0] + red_s[c][1] + red_s[c][2] + red_s[c][3];
+                    for (int j = 0; j < 16; j++) ex[(c0 + j) * 64 + (prow & 63)] = v[j];
                 }
             }
-        } else if (ok) {
-            epilogue_token_major<BN, EPI>(a, trow, p0, q0, blockIdx.y, prow);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int fl = prow & 63, f = (p0 >> 1) + fl;
+            if (ok && f < (a.N >> 1)) {
+#pragma unroll 1
+                for (int c = prow >> 6; c < ncol; c += 2) {         // the halves take alternate tokens
+                    const float iv = inv_s[c];
+                    ((bf16 *)a.out)[(size_t)c * a.ldc + f] =
+                        __float2bfloat16_rn(silu_mul(exg[c * 64 + fl] * iv, exu[c * 64 + fl] * iv));
+                }
+            }
+        } else {
+            // partial tile -> the owners of its columns: CTA r of the cluster sums columns [r * per, (r + 1) * per).
+            // Without a split the CTA is its own owner and the tile passes through its (now idle) ring instead.
+            const int per = BN / S, per_log = __ffs(per) - 1;       // BN and S are powers of two
+            if (split) cluster_wait();            // every CTA of the cluster has started (arrived at its top)
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                if (have) tc_ld16(trow + c0, v);
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int c = c0 + j, r = c >> per_log, cl = c & (per - 1);
+                    const float val = have ? v[j] : 0.f;
+                    if (split) st_dsmem_f32(smem_u32(&recv[((int)blockIdx.z * per + cl) * BM + prow]), r, val);
+                    else ((float *)smem)[c * BM + prow] = val;
+                }
+            }
         }
         tc_fence_before();
     }
-    if (SPLIT) {
-        // ---- split-K: after the barrier this CTA's shared memory holds, for its columns, the partial sums of
-        // every CTA of the cluster; they are added in rank order and the epilogue runs on the totals
-        const int S = gridDim.z;
-        if (warp < 2) { __syncwarp(); cluster_wait(); }        // the barrier phase opened at the top
-        cluster_sync();
+    if (epi != EPI_SILU_MUL) {
+        // ---- after the barrier this CTA's shared memory holds, for its columns, the partial sums of every CTA of
+        // the cluster; they are added in rank order and the epilogue runs on the totals
+        if (split) {
+            if (warp < 2) { __syncwarp(); cluster_wait(); }    // the barrier phase opened at the top
+            cluster_sync();
+        } else if (warp >= 2) asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp >= 2) {
-            const int lg = warp & 3, prow = lg * 32 + lane, n = p0 + prow;
+            // A warp takes whole columns (tokens) here: its lanes cover the 128 features in four steps, so the sum of
+            // squares of a column needs one warp reduction and no exchange between warps, and it comes before the
+            // column's stores (a shuffle queues behind the warp's earlier stores in the memory pipeline).
+            const int w = warp - 2;
             const int per = BN / S, c_begin = blockIdx.z * per;
-            const bool emit = EPI == EPI_ADD_F32 && a.norm_w != nullptr;
-            // One pass of this code per launch: it is fetched cold, so it is kept small (a rolled loop over the
-            // columns); only the loads of one column's partial sums are unrolled, to have them in flight together.
+            const bool emit = epi == EPI_ADD_F32 && a.norm_w != nullptr;
+            const float *part = split ? recv : (const float *)smem;
 #pragma unroll 1
-            for (int cl = 0; cl < per; cl++) {
-                const int c = c_begin + cl, m = q0 + c;
-                float pz[8];
+            for (int cl = w; cl < per; cl += 4) {
+                const int m = c_begin + cl;
+                if (m >= a.M) break;                                               // tokens fill the columns from 0
+                float v[4];
 #pragma unroll
-                for (int z = 0; z < 8; z++) pz[z] = z < S ? recv[(z * per + cl) * BM + prow] : 0.f;
-                float v = 0.f;
+                for (int i = 0; i < 4; i++) {
+                    float pz[8];
 #pragma unroll
-                for (int z = 0; z < 8; z++) v += pz[z];                            // rank order; absent ranks add 0
-                v *= inv_s[c];
+                    for (int z = 0; z < 8; z++) pz[z] = z < S ? part[(z * per + cl) * BM + lane + 32 * i] : 0.f;
+                    v[i] = 0.f;
+#pragma unroll
+                    for (int z = 0; z < 8; z++) v[i] += pz[z];                     // rank order; absent ranks add 0
+                }
+                const float iv = inv_s[m];
                 float sq = 0.f;
-                if (n < a.N && m < a.M) {
-                    const size_t idx = (size_t)m * a.ldc + n;
-                    if (EPI == EPI_BF16) ((bf16 *)a.out)[idx] = __float2bfloat16_rn(v);
-                    else if (EPI == EPI_F32) ((float *)a.out)[idx] = v;
-                    else {
-                        v += cl < RES_AHEAD ? res_pre[cl] : ((const float *)a.out)[idx];
-                        ((float *)a.out)[idx] = v;
-                        if (emit) { a.xw_out[(size_t)m * a.N + n] = __float2bfloat16_rn(v * nw_pre); sq = v * v; }
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int n = p0 + lane + 32 * i;
+                    v[i] *= iv;
+                    if (epi == EPI_ADD_F32 && n < a.N) {
+                        v[i] += (split && cl < 8) ? (cl < 4 ? res_pre[i] : res_pre[4 + i]) : ((const float *)a.out)[(size_t)m * a.ldc + n];
+                        sq += v[i] * v[i];
                     }
                 }
-                if (emit) red_s[cl][lg] = warp_sum(sq);                            // by every lane: same value, same address
-            }
-            if (emit) {
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (prow < per && q0 + c_begin + prow < a.M)
-                    a.ss_out[(size_t)blockIdx.x * a.M + q0 + c_begin + prow] =
-                        red_s[prow][0] + red_s[prow][1] + red_s[prow][2] + red_s[prow][3];
+                if (emit) sq = warp_sum(sq);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int n = p0 + lane + 32 * i;
+                    if (n >= a.N) continue;
+                    const size_t idx = (size_t)m * a.ldc + n;
+                    if (epi == EPI_BF16) ((bf16 *)a.out)[idx] = __float2bfloat16_rn(v[i]);
+                    else {
+                        ((float *)a.out)[idx] = v[i];
+                        if (emit) a.xw_out[(size_t)m * a.N + n] = __float2bfloat16_rn(v[i] * nw_pre[i]);
+                    }
+                }
+                if (emit && lane == 0) a.ss_out[(size_t)blockIdx.x * a.M + m] = sq;
             }
         }
     }
@@ -560,7 +547,7 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_con
     __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
     __shared__ uint32_t tmem_base_s;
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = warp_index(), lane = threadIdx.x & 31;
     const int nkb = (a.K + BK - 1) / BK;
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
     const uint32_t tfull0 = smem_u32(&bars[2 * STAGES]), tempty0 = smem_u32(&bars[2 * STAGES + 2]);
@@ -689,17 +676,21 @@ static int make_map(CUtensorMap *map, const void *base, int rows, int K, int ld,
     return r == CUDA_SUCCESS ? 0 : FG_ERR_TENSORMAP;
 }
 
-template <int BN, int STAGES, int EPI, bool SWAP, bool SPLIT>
-static int launch(const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs &a, dim3 grid, cudaStream_t stream) {
-    constexpr int smem = STAGES * (BM + BN) * BK * 2 + 1024 + (SPLIT ? BN * BM * 4 : 0);
+template <int BN>
+static int launch_decode(const CUtensorMap &tmW, const CUtensorMap &tmX, GemmArgs a, dim3 grid, cudaStream_t stream) {
+    // two CTAs share an SM: ring and (split-K) receive buffer together stay under half its shared memory
+    const bool split = grid.z > 1;
+    constexpr int stage_bytes = (BM + BN) * BK * 2;
+    a.stages = BN == 16 ? (split ? 5 : 6) : BN == 32 ? (split ? 4 : 5) : (split ? 3 : 4);
+    const int smem = a.stages * stage_bytes + 1024 + (split ? BN * BM * 4 : 0);
+    constexpr int smem_max = MAX_STAGES * stage_bytes + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI, SWAP, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_decode_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return fg_launch_cluster(gemm_tc_kernel<BN, STAGES, EPI, SWAP, SPLIT>, grid, dim3(GEMM_THREADS), (size_t)smem, stream,
-                             (int)grid.z, tmP, tmQ, a);
+    return fg_launch_cluster(gemm_tc_decode_kernel<BN>, grid, dim3(GEMM_THREADS), (size_t)smem, stream, (int)grid.z, tmW, tmX, a);
 }
 
 template <int BN, int STAGES, int EPI>
@@ -723,20 +714,13 @@ static int launch_prefill(const CUtensorMap &tmP, const CUtensorMap &tmQ, const 
 
 template <int EPI>
 static int dispatch(bool swap, int bn, const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs &a, dim3 grid, cudaStream_t st) {
-    if (swap && grid.z > 1) {
-        // stages and the receive buffer of the split-K sum together leave room for two CTAs per SM
-        if (EPI != EPI_SILU_MUL) {
-            switch (bn) {
-            case 16: return launch<16, 5, EPI, true, true>(tmP, tmQ, a, grid, st);
-            case 32: return launch<32, 4, EPI, true, true>(tmP, tmQ, a, grid, st);
-            case 64: return launch<64, 3, EPI, true, true>(tmP, tmQ, a, grid, st);
-            }
-        }
-    } else if (swap) {
+    if (swap) {
+        GemmArgs d = a;
+        d.epi = EPI;
         switch (bn) {
-        case 16: return launch<16, 6, EPI, true, false>(tmP, tmQ, a, grid, st);
-        case 32: return launch<32, 5, EPI, true, false>(tmP, tmQ, a, grid, st);
-        case 64: return launch<64, 4, EPI, true, false>(tmP, tmQ, a, grid, st);
+        case 16: return launch_decode<16>(tmP, tmQ, d, grid, st);
+        case 32: return launch_decode<32>(tmP, tmQ, d, grid, st);
+        case 64: return launch_decode<64>(tmP, tmQ, d, grid, st);
         }
     } else {
         switch (bn) {
@@ -797,7 +781,7 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
     int vec_ok = ((uintptr_t)out % 16 == 0) && ((size_t)ldc * esz % 16 == 0);
     if (norm_w && (epi != EPI_ADD_F32 || !xw_out || !ss_out)) return FG_ERR_BAD_DTYPE;
     if (ss_tiles_out) *ss_tiles_out = swap ? (int)grid.x : (int)grid.y;
-    GemmArgs a{out, M, N, K, ldc, kb_per_split, vec_ok, ss_in, ss_tiles, ss_size, ss_eps, norm_w, (bf16 *)xw_out, ss_out};
+    GemmArgs a{out, M, N, K, ldc, kb_per_split, vec_ok, ss_in, ss_tiles, ss_size, ss_eps, norm_w, (bf16 *)xw_out, ss_out, epi, 0};
     switch (epi) {
     case EPI_BF16: return dispatch<EPI_BF16>(swap, bn, tmP, tmQ, a, grid, stream);
     case EPI_F32: return dispatch<EPI_F32>(swap, bn, tmP, tmQ, a, grid, stream);
