@@ -682,7 +682,11 @@ static int launch_decode(const CUtensorMap &tmW, const CUtensorMap &tmX, GemmArg
     const bool split = grid.z > 1;
     constexpr int stage_bytes = (BM + BN) * BK * 2;
     a.stages = BN == 16 ? (split ? 5 : 6) : BN == 32 ? (split ? 4 : 5) : (split ? 3 : 4);
-    const int smem = a.stages * stage_bytes + 1024 + (split ? BN * BM * 4 : 0);
+    if (a.stages > a.kb_per_split) a.stages = a.kb_per_split;      // a short K loop needs no deeper ring: room for other CTAs
+    // without a split the epilogue passes the f32 tile (BN x 128) through the idle ring: the ring is at least that large
+    int ring = a.stages * stage_bytes;
+    if (!split && ring < BN * BM * 4) ring = BN * BM * 4;
+    const int smem = ring + 1024 + (split ? BN * BM * 4 : 0);
     constexpr int smem_max = MAX_STAGES * stage_bytes + 1024;
     static bool configured = false;
     if (!configured) {

@@ -32,11 +32,13 @@ def supported(q: torch.Tensor, k_pool: torch.Tensor, head_dim: int) -> bool:
 
 
 def decode_splits(n_seq: int, n_heads: int, n_kv_heads: int, table_width: int) -> int:
-    """How many CTAs share one sequence's pages: enough to give every SM two CTAs.  Up to 8 splits
-    (a power of two) are merged inside a thread-block cluster; only contexts beyond 16K positions
-    take more splits and the scratch-memory path."""
+    """How many CTAs share one sequence's pages: about one and a half CTAs per SM in all.  More than fit on
+    the GPU at once (three per SM, fewer beside the contraction kernels that are already resident) run as a
+    second wave whose page loads start late; measured at batch 8 with 8 KV heads, 4 splits (256 CTAs) beat
+    both 2 and 8.  Up to 8 splits (a power of two) are merged inside a thread-block cluster; only contexts
+    beyond 16K positions take more splits and the scratch-memory path."""
     ctas = n_seq * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
-    want = max(1, min((2 * N_SM + ctas - 1) // ctas, table_width))
+    want = max(1, min((3 * N_SM // 2 + ctas - 1) // ctas, table_width))
     if want > 8 and table_width > 256:
         return want
     s = 1
