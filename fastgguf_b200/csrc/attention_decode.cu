@@ -11,6 +11,11 @@
 // n_splits > 1 the CTAs of a sequence and KV head either form a thread-block cluster (2, 4 or 8
 // splits) and merge their partial (O, max, sum) through distributed shared memory, or (more
 // splits, very long contexts) write them to scratch memory for a second kernel to merge.
+//
+// The merge inside a cluster: CTA r owns the slice [r * HD / S, (r + 1) * HD / S) of the head dimension.  Every
+// warp that read pages pushes its running (max, sum) to all CTAs and the slices of its O to their owners
+// (st.shared::cluster), one cluster barrier makes the pushes visible, and each owner combines the up to 4 S
+// partial results of its slice in (split, warp) order from its own shared memory and writes the output.
 #include "attention_mma.cuh"
 
 #define DEC_WARPS 4
@@ -18,13 +23,14 @@
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float ld_dsmem(const float *p, int rank) {
+// two floats to the same shared-memory offset in the CTA of rank `rank` of this cluster (p 8-byte aligned)
+__device__ __forceinline__ void st_dsmem2(const float *p, int rank, float a, float b) {
     uint32_t remote;
-    float v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(p)), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(remote), "f"(a), "f"(b) : "memory");
 }
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
 // What the fused variant (FUSE) also does, so that no separate RoPE kernel runs in a decode step:
 // q arrives unrotated, with the new token's k and v behind it in the same row (the output of the
@@ -53,6 +59,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
     const int kvh = blockIdx.y / chunks, g0 = (blockIdx.y % chunks) * 16;
     const int rows = min(16, G - g0);
     const int b = blockIdx.z, split = blockIdx.x;
+    if (CLUSTER && n_splits > 1) cluster_arrive_relaxed();       // matched before the first push: every CTA runs
     pdl_launch_dependents();
     if (!FUSE) pdl_wait();
     // positions and page tables are written between steps, never by the kernel just before this one
@@ -81,6 +88,16 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
         cp_async_commit();
     }
     if (FUSE) pdl_wait();                      // q, k, v of the new token come from the kernel before
+    // the warp that will read the sequence's last page fetches the new token's k and v now, with q
+    const int p_new = pos / PAGE;
+    const bool mine = FUSE && p_new >= p_begin && p_new < p_end && ((p_new - p_begin) & (DEC_WARPS - 1)) == warp;
+    uint4 knew_lo = make_uint4(0, 0, 0, 0), knew_hi = knew_lo, vnew = knew_lo;
+    if (mine) {
+        const bf16 *ksrc = q + (size_t)b * ldq + (size_t)(rope.q_heads + kvh) * HD;
+        const bf16 *vsrc = q + (size_t)b * ldq + (size_t)(rope.q_heads + KV + kvh) * HD;
+        if (lane < HD / 16) { knew_lo = *(const uint4 *)(ksrc + lane * 8); knew_hi = *(const uint4 *)(ksrc + HD / 2 + lane * 8); }
+        if (lane < HD / 8) vnew = *(const uint4 *)(vsrc + lane * 8);
+    }
     // Q fragments of rows g0 .. g0+15 of this KV head's group (rows past the group are zero)
     uint32_t qf[HD / 16][4];
     {
@@ -121,11 +138,10 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
             // rotated k of the new token -> row pos % 64 of the K tile (and the cache, once per KV head)
             const int off = pos % PAGE;
             const bool to_cache = blockIdx.y % chunks == 0;
-            const bf16 *ksrc = q + (size_t)b * ldq + (size_t)(rope.q_heads + kvh) * HD;
             const float *cs = rope.cos_t + (size_t)pos * (HD / 2), *sn = rope.sin_t + (size_t)pos * (HD / 2);
             if (lane < HD / 16) {
                 const int j0 = lane * 8;
-                uint4 lo4 = *(const uint4 *)(ksrc + j0), hi4 = *(const uint4 *)(ksrc + HD / 2 + j0);
+                uint4 lo4 = knew_lo, hi4 = knew_hi;
                 const __nv_bfloat162 *lp = (const __nv_bfloat162 *)&lo4, *hp = (const __nv_bfloat162 *)&hi4;
                 uint4 olo, ohi;
                 uint32_t *ol = (uint32_t *)&olo, *oh = (uint32_t *)&ohi;
@@ -162,9 +178,8 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
         __syncwarp();
         if (newest) {
             const int off = pos % PAGE;
-            const bf16 *vsrc = q + (size_t)b * ldq + (size_t)(rope.q_heads + KV + kvh) * HD;
             if (lane < HD / 8) {
-                uint4 v4 = *(const uint4 *)(vsrc + lane * 8);
+                uint4 v4 = vnew;
                 *(uint4 *)(vbuf + off * (HD * 2) + ((lane ^ (off & 7)) << 4)) = v4;
                 if (blockIdx.y % chunks == 0)
                     *(uint4 *)(rope.v_pool + (((size_t)bt[p] * KV + kvh) * PAGE + off) * HD + lane * 8) = v4;
@@ -177,9 +192,69 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
         cp_async_commit();
     }
     cp_async_wait<0>();
+    if (CLUSTER) {
+        // ---- every warp's partial result goes to the owners of its slices; see the head of this file
+        const int S = n_splits, dsl = HD / S, dsl_log = __ffs(dsl) - 1;          // HD and S are powers of two
+        float *recv_o = (float *)(smem + (size_t)DEC_WARPS * 2 * TILE_BYTES);     // [4 S][rows][dsl]
+        float *recv_ml = recv_o + DEC_WARPS * rows * HD;                           // [4 S][16][2]
+        if (S > 1) cluster_wait();                                                // the phase opened at the top
+        if (p_begin + warp < p_end) {                                             // this warp read at least one page
+            const int slot = split * DEC_WARPS + warp, r0 = lane >> 2, c = (lane & 3) * 2;
+#pragma unroll
+            for (int d = 0; d < HD / 8; d++) {
+                const int col = d * 8 + c, owner = col >> dsl_log, cc = col & (dsl - 1);
+                if (r0 < rows) st_dsmem2(&recv_o[(slot * rows + r0) * dsl + cc], owner, o[d][0], o[d][1]);
+                if (r0 + 8 < rows) st_dsmem2(&recv_o[(slot * rows + r0 + 8) * dsl + cc], owner, o[d][2], o[d][3]);
+            }
+            if ((lane & 3) == 0) {
+                for (int z = 0; z < S; z++) {
+                    if (r0 < rows) st_dsmem2(&recv_ml[(slot * 16 + r0) * 2], z, m[0], l[0]);
+                    if (r0 + 8 < rows) st_dsmem2(&recv_ml[(slot * 16 + r0 + 8) * 2], z, m[1], l[1]);
+                }
+            }
+        }
+        if (S > 1) cluster_sync_all(); else __syncthreads();
+        // this CTA's slice: columns [split * dsl, (split + 1) * dsl) of every row, over the warps that had pages
+        for (int e = threadIdx.x; e < rows * dsl; e += DEC_WARPS * 32) {
+            const int r = e >> dsl_log, cc = e & (dsl - 1);
+            // the four warps of a split at a time, their loads in flight together; a warp without pages counts as -inf
+            float M = -INFINITY;
+#pragma unroll 1
+            for (int z = 0; z < S; z++) {
+                const int have = min(first_page + n_pages, first_page + (z + 1) * per) - (first_page + z * per);
+                float mw[DEC_WARPS];
+#pragma unroll
+                for (int w = 0; w < DEC_WARPS; w++) mw[w] = w < have ? recv_ml[((z * DEC_WARPS + w) * 16 + r) * 2] : -INFINITY;
+#pragma unroll
+                for (int w = 0; w < DEC_WARPS; w++) M = fmaxf(M, mw[w]);
+            }
+            float O = 0.f, L = 0.f;
+#pragma unroll 1
+            for (int z = 0; z < S; z++) {
+                const int have = min(first_page + n_pages, first_page + (z + 1) * per) - (first_page + z * per);
+                float mw[DEC_WARPS], lw[DEC_WARPS], ow[DEC_WARPS];
+#pragma unroll
+                for (int w = 0; w < DEC_WARPS; w++) {
+                    const int sl = z * DEC_WARPS + w;
+                    const bool in = w < have;
+                    mw[w] = in ? recv_ml[(sl * 16 + r) * 2] : -INFINITY;
+                    lw[w] = in ? recv_ml[(sl * 16 + r) * 2 + 1] : 0.f;
+                    ow[w] = in ? recv_o[(sl * rows + r) * dsl + cc] : 0.f;
+                }
+#pragma unroll
+                for (int w = 0; w < DEC_WARPS; w++) {                              // (split, warp) order
+                    const float wgt = mw[w] == -INFINITY ? 0.f : ex2(mw[w] - M);
+                    O += wgt * ow[w];
+                    L += wgt * lw[w];
+                }
+            }
+            out[(size_t)b * ldo + (size_t)(kvh * G + g0 + r) * HD + split * dsl + cc] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        }
+        return;
+    }
     __syncthreads();
 
-    // ---- merge the four warps: each leaves (m, l) and O[16][HD] in its own buffer
+    // ---- scratch path: merge the four warps, each leaves (m, l) and O[16][HD] in its own buffer
     float *wo = (float *)kbuf;                 // 16 * HD floats <= TILE_BYTES
     float *wml = (float *)vbuf;                // 16 * 2 floats
     {
@@ -195,8 +270,6 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
         }
     }
     __syncthreads();
-    float *cta_o = (float *)(smem + (size_t)DEC_WARPS * 2 * TILE_BYTES);     // [16][HD] result of this CTA
-    float *cta_ml = cta_o + 16 * HD;                                          // [16][2]
     for (int i = threadIdx.x; i < rows * HD; i += DEC_WARPS * 32) {
         int r = i / HD, d = i % HD;
         float M = -INFINITY;
@@ -215,43 +288,11 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
         int h = kvh * G + g0 + r;
         if (n_splits == 1) {
             out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
-        } else if (CLUSTER) {
-            cta_o[i] = O;
-            if (d == 0) { cta_ml[r * 2] = M; cta_ml[r * 2 + 1] = L; }
         } else {
             size_t prow = ((size_t)b * KV * G + h) * n_splits + split;
             part_o[prow * HD + d] = O;
             if (d == 0) { part_ml[prow * 2] = M; part_ml[prow * 2 + 1] = L; }
         }
-    }
-    if (CLUSTER && n_splits > 1) {
-        // the splits of this (sequence, KV head) are the CTAs of one cluster: CTA `split` merges its
-        // share of the (row, dim) elements over all of them, in rank order
-        cluster_sync_all();
-        const int total = rows * HD, per = (total + n_splits - 1) / n_splits;
-        for (int i = split * per + threadIdx.x; i < min(total, (split + 1) * per); i += DEC_WARPS * 32) {
-            int r = i / HD, d = i % HD;
-            float ms[8], ls[8], os[8];
-#pragma unroll
-            for (int z = 0; z < 8; z++) {
-                bool in = z < n_splits;
-                ms[z] = in ? ld_dsmem(&cta_ml[r * 2], z) : -INFINITY;
-                ls[z] = in ? ld_dsmem(&cta_ml[r * 2 + 1], z) : 0.f;
-                os[z] = in ? ld_dsmem(&cta_o[i], z) : 0.f;
-            }
-            float M = -INFINITY;
-#pragma unroll
-            for (int z = 0; z < 8; z++) M = fmaxf(M, ms[z]);
-            float O = 0.f, L = 0.f;
-#pragma unroll
-            for (int z = 0; z < 8; z++) {
-                float wgt = ms[z] == -INFINITY ? 0.f : ex2(ms[z] - M);
-                O += wgt * os[z];
-                L += wgt * ls[z];
-            }
-            out[(size_t)b * ldo + (size_t)(kvh * G + g0 + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
-        }
-        cluster_sync_all();                    // no CTA leaves while its partial is still being read
     }
 }
 
@@ -280,10 +321,13 @@ static int launch_decode_kernel(dim3 grid, int cluster_x, cudaStream_t stream, c
                                 const int *positions, const int *block_table, int table_width, const void *k_pool,
                                 const void *v_pool, int KV, int G, float scale, int window, int n_splits,
                                 float *part_o, float *part_ml, RopeArgs rope = RopeArgs{}) {
-    constexpr int smem = DEC_WARPS * 2 * PAGE * HD * 2 + 16 * HD * 4 + 16 * 2 * 4;
+    // behind the page buffers: the cluster merge receives 4 S partial slices [rows][HD / S] and (max, sum) pairs
+    constexpr int smem_max = DEC_WARPS * 2 * PAGE * HD * 2 + (CLUSTER ? DEC_WARPS * 16 * HD * 4 + DEC_WARPS * 8 * 16 * 2 * 4 : 0);
+    const int rows_cap = G < 16 ? G : 16;
+    const int smem = DEC_WARPS * 2 * PAGE * HD * 2 + (CLUSTER ? DEC_WARPS * rows_cap * HD * 4 + DEC_WARPS * n_splits * 16 * 2 * 4 : 0);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, CLUSTER, FUSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, CLUSTER, FUSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }

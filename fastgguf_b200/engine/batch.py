@@ -39,6 +39,7 @@ class Batch:
     max_new: int = 1              # most rows any sequence brings
     max_len: int = 1              # longest sequence after the step
     single_token: bool = True     # every sequence brings exactly one token (a decode step)
+    want_all: bool = False        # the wanted rows are all rows, in order (the head may take the rows as they are)
     host_cu_rows: List[int] = field(default_factory=list)
     host_seq_start: List[int] = field(default_factory=list)
 
@@ -94,5 +95,6 @@ def build_batch(entries: Sequence[StepEntry], cache, device: torch.device) -> Ba
         seq_start=view(4), slots=view(5), want_rows=view(6) if want.size else None,
         block_tables=[view(7 + gi).view(n_seq, width) for gi in range(len(tables))],
         n_want=int(want.size), max_new=max(lens), max_len=max_len, single_token=all(n == 1 for n in lens),
+        want_all=bool(want.size == M and np.array_equal(want, np.arange(M, dtype=np.int32))),
         host_cu_rows=cu.tolist(), host_seq_start=starts,
     )

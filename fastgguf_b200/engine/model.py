@@ -149,13 +149,20 @@ class DecoderModel:
             return block.mixer_norm if ok and self.runtime.dtype == torch.bfloat16 else None
 
         first = entry_norm(blocks[0]) if blocks else None
+        # the final norm can be started by the last block when the head takes every row as it is
+        head_norm = None
+        if (batch.want_all and self.runtime.dtype == torch.bfloat16 and getattr(self.final_norm, "deferrable", False)
+                and getattr(self.head, "supports_deferred_norm", False)):
+            head_norm = self.final_norm
         if first is not None:
             x, pending = self.embedding.forward(batch.tokens, emit_norm=first)
         else:
             x, pending = self.embedding.forward(batch.tokens), None      # [M, E] float32 residual stream
         for i, block in enumerate(blocks):
-            nxt = entry_norm(blocks[i + 1]) if i + 1 < len(blocks) else None
+            nxt = entry_norm(blocks[i + 1]) if i + 1 < len(blocks) else head_norm
             pending = block.forward(x, batch, self._io[i], pending=pending, next_norm=nxt)
         if batch.want_rows is None:
             return None
+        if head_norm is not None and pending is not None and blocks:
+            return self.head.forward(pending)
         return self.head.forward(self.final_norm.forward(x, rows=batch.want_rows))

@@ -62,7 +62,7 @@ class DecodeGraph:
         self.batch = Batch(n_seq=B, n_rows=B, tokens=self.tokens, positions=self.positions, row_seq=self.row_seq,
                            cu_rows=self.cu_rows, seq_start=self.positions, slots=self.rows, want_rows=self.want,
                            block_tables=self.tables, n_want=B, max_new=1, max_len=cache.max_seq_len,
-                           single_token=True)
+                           single_token=True, want_all=True)
         self.model = model
         from ..ops.lib import launches
         before = launches()

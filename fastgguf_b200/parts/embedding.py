@@ -40,6 +40,9 @@ class TokenEmbedding(Part):
 
 
 class LMHead(Part):
+    #: ``forward`` also takes rows whose RMSNorm was started by the contraction before (x * w and partial sums of squares)
+    supports_deferred_norm = True
+
     def __init__(self, runtime: Runtime, vocab_size: int, hidden_size: int):
         super().__init__(runtime)
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
@@ -51,6 +54,6 @@ class LMHead(Part):
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.linear = Linear(tensors["weight"])
 
-    def forward(self, xn: torch.Tensor) -> torch.Tensor:
-        """Float32 logits [rows, vocab] of normalized rows."""
+    def forward(self, xn) -> torch.Tensor:
+        """Float32 logits [rows, vocab] of normalized rows (a tensor, or a ``DeferredNorm``)."""
         return self.linear.forward(xn, out_dtype=torch.float32)
