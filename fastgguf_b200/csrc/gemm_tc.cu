@@ -278,6 +278,107 @@ __device__ __forceinline__ void epilogue_token_major(const GemmArgs &a, uint32_t
     }
 }
 
+#define EPI_STAGE_BYTES 6144      // per epilogue warp: a 32 x 32 f32 tile and a 32 x 32 bf16 tile
+
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+}
+
+// Residual-add epilogue of a token-major tile for whole, aligned rows (N % 32 == 0, 16-byte aligned rows).
+// In tensor memory a thread owns one token row, and if it also did the global accesses every warp instruction
+// would touch 32 different lines, 16 bytes each - the load/store unit then bounds the epilogue (18 us for a
+// 128 x 256 tile, against 11 us of MMAs).  Here a warp passes each 32-column chunk through a tile of its own in
+// shared memory, so that the global loads and stores are four whole 128-byte lines per instruction:
+//   residual: global -> (coalesced) -> tile;   thread = row: tile + accumulator -> new residual, x * w, sum of squares
+//   -> tile;   tile -> (coalesced) -> global.   16-byte chunks are swizzled by row, all accesses are conflict-free.
+template <int BN>
+__device__ __forceinline__ void epilogue_add_coalesced(const GemmArgs &a, uint32_t trow, int p0, int q0, int qt, int lg,
+                                                       int lane, uint8_t *stage) {
+    float *T = (float *)stage;                    // [32][32] f32
+    uint8_t *X = stage + 4096;                    // [32][32] bf16
+    const int m_base = p0 + lg * 32, m_own = m_base + lane;
+    const float iv = (a.ss_in && m_own < a.M) ? inv_rms(a, m_own) : 1.0f;
+    float sq = 0.f;
+    // Every global load of a chunk is requested one chunk ahead, the norm weights too (behind the stores into the
+    // tile the compiler would not move them, and each would wait for L2 on its own).
+    float4 rl[8], g[8], rl_next[8], g_next[8];
+    auto request = [&](int c, float4 (&r)[8], float4 (&gw)[8]) {
+        const int n0 = q0 + c * 32;
+#pragma unroll
+        for (int pass = 0; pass < 8; pass++) {
+            const int row = pass * 4 + (lane >> 3), ch = lane & 7, m = m_base + row;
+            r[pass] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (m < a.M && n0 < a.N) r[pass] = __ldcg((const float4 *)((const float *)a.out + (size_t)m * a.ldc + n0) + ch);
+        }
+#pragma unroll
+        for (int ch = 0; ch < 8; ch++)
+            gw[ch] = (a.norm_w && n0 < a.N) ? __ldg((const float4 *)(a.norm_w + n0) + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    request(0, rl, g);
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; c++) {
+        const int n0 = q0 + c * 32;
+        if (n0 >= a.N) break;
+        if (c + 1 < BN / 32) request(c + 1, rl_next, g_next);
+#pragma unroll
+        for (int pass = 0; pass < 8; pass++) {
+            const int row = pass * 4 + (lane >> 3), ch = lane & 7;
+            *(float4 *)(T + row * 32 + ((ch ^ (row & 7)) << 2)) = rl[pass];
+        }
+        __syncwarp();
+        float v[32];
+        tc_ld32(trow + c * 32, v);
+        uint32_t xb[16];
+#pragma unroll
+        for (int ch = 0; ch < 8; ch++) {
+            float4 *tp = (float4 *)(T + lane * 32 + ((ch ^ (lane & 7)) << 2));
+            const float4 r = *tp;
+            const float4 o = make_float4(v[4 * ch] * iv + r.x, v[4 * ch + 1] * iv + r.y, v[4 * ch + 2] * iv + r.z, v[4 * ch + 3] * iv + r.w);
+            *tp = o;
+            if (a.norm_w) {
+                __nv_bfloat162 t0 = __floats2bfloat162_rn(o.x * g[ch].x, o.y * g[ch].y), t1 = __floats2bfloat162_rn(o.z * g[ch].z, o.w * g[ch].w);
+                xb[2 * ch] = *(uint32_t *)&t0; xb[2 * ch + 1] = *(uint32_t *)&t1;
+                sq += o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w;
+            }
+        }
+        if (a.norm_w) {
+#pragma unroll
+            for (int ch = 0; ch < 4; ch++)
+                *(uint4 *)(X + lane * 64 + ((ch ^ ((lane >> 1) & 3)) << 4)) = make_uint4(xb[4 * ch], xb[4 * ch + 1], xb[4 * ch + 2], xb[4 * ch + 3]);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int pass = 0; pass < 8; pass++) {
+            const int row = pass * 4 + (lane >> 3), ch = lane & 7, m = m_base + row;
+            const float4 t = *(const float4 *)(T + row * 32 + ((ch ^ (row & 7)) << 2));
+            if (m < a.M) ((float4 *)((float *)a.out + (size_t)m * a.ldc + n0))[ch] = t;
+        }
+        if (a.norm_w) {
+#pragma unroll
+            for (int pass = 0; pass < 4; pass++) {
+                const int row = pass * 8 + (lane >> 2), ch = lane & 3, m = m_base + row;
+                const uint4 t = *(const uint4 *)(X + row * 64 + ((ch ^ ((row >> 1) & 3)) << 4));
+                if (m < a.M) ((uint4 *)(a.xw_out + (size_t)m * a.N + n0))[ch] = t;
+            }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; i++) { rl[i] = rl_next[i]; g[i] = g_next[i]; }
+    }
+    if (a.norm_w && m_own < a.M) a.ss_out[(size_t)qt * a.M + m_own] = sq;
+}
+
 // ---------------------------------------------------------------------------- decode: weights stream once
 // One kernel for every projection of a decode step: the epilogue, the number of K splits and the depth of the
 // ring are run-time values.  A decode step alternates between four or five projections per layer, each launch
@@ -632,7 +733,10 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_con
             if (!mbar_wait(tfull0 + 8 * acc, (i >> 1) & 1)) { raise_error(3); break; }
             tc_fence_after();
             const uint32_t trow = tmem_base + ((uint32_t)(lg * 32) << 16) + acc * BN;
-            epilogue_token_major<BN, EPI>(a, trow, pt * BM, qt * BN, qt, prow);
+            if (EPI == EPI_ADD_F32 && a.vec_ok && (a.N & 31) == 0)
+                epilogue_add_coalesced<BN>(a, trow, pt * BM, qt * BN, qt, lg, lane, smem + STAGES * STAGE_BYTES + lg * EPI_STAGE_BYTES);
+            else
+                epilogue_token_major<BN, EPI>(a, trow, pt * BM, qt * BN, qt, prow);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tempty0 + 8 * acc) : "memory");
@@ -699,7 +803,7 @@ static int launch_decode(const CUtensorMap &tmW, const CUtensorMap &tmX, GemmArg
 
 template <int BN, int STAGES, int EPI>
 static int launch_prefill(const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs &a, cudaStream_t stream) {
-    constexpr int smem = STAGES * (BM + BN) * BK * 2 + 1024;
+    constexpr int smem = STAGES * (BM + BN) * BK * 2 + 1024 + (EPI == EPI_ADD_F32 ? 4 * EPI_STAGE_BYTES : 0);
     static bool configured = false;
     static int n_sm = 0;
     if (!configured) {
