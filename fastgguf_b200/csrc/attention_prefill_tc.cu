@@ -4,7 +4,8 @@
 //
 // Reference role and formulas: as attention_prefill.cu (fastgguf.c:5022-5039, :3273-3326).
 //
-// Grid (query tile, kv head x head chunk, sequence).  A CTA owns 128 rows = TQ consecutive new
+// Grid (kv head x head chunk, query tile, sequence): CTAs are dispatched x first, so the tiles that see the most
+// keys (the late ones, y = 0) all start before any light one and the tail of the kernel is short.  A CTA owns 128 rows = TQ consecutive new
 // tokens x Gc query heads of one KV head (Gc = min(G, 16), row r = token r / Gc, head r % Gc) and
 // walks the sequence's pages two at a time (128 keys):
 //
@@ -123,7 +124,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 
     const int warp = warp_index(), lane = threadIdx.x & 31;
     const int Gc = G < 16 ? G : 16, TQ = ROWS / Gc, chunks = (G + Gc - 1) / Gc;
-    const int kvh = blockIdx.y / chunks, g0 = (blockIdx.y % chunks) * Gc;
+    const int kvh = blockIdx.x / chunks, g0 = (blockIdx.x % chunks) * Gc;
     const int b = blockIdx.z;
     const uint32_t qs = smem_u32(smem), kt = qs + Q_BYTES, vt = kt + KV_TILE, ps = vt + KV_TILE;
     const uint32_t k_full = smem_u32(&bars[0]), k_empty = smem_u32(&bars[1]);
@@ -143,7 +144,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     pdl_launch_dependents();
     pdl_wait();                                        // q and the cache come from the kernels before
     const int row0 = cu_rows[b], n_tok = cu_rows[b + 1] - row0, start = seq_start[b];
-    const int q0 = (gridDim.x - 1 - blockIdx.x) * TQ;  // late tiles see the most keys: start them first
+    const int q0 = (gridDim.y - 1 - blockIdx.y) * TQ;  // late tiles see the most keys: start them first
     const bool active = q0 < n_tok;                    // a CTA past the sequence's tokens only sets up and leaves
     const int tq = active ? min(TQ, n_tok - q0) : 0;
     const int tile_hi = start + q0 + tq - 1;
@@ -406,7 +407,7 @@ static int launch_tc(const CUtensorMap &tmK, const CUtensorMap &tmV, const void 
         configured = true;
     }
     int G = H / KV, Gc = G < 16 ? G : 16, TQ = ROWS / Gc;
-    dim3 grid((max_new + TQ - 1) / TQ, KV * ((G + Gc - 1) / Gc), n_seq);
+    dim3 grid(KV * ((G + Gc - 1) / Gc), (max_new + TQ - 1) / TQ, n_seq);
     return fg_launch(attn_prefill_tc_kernel<HD>, grid, dim3(ATT_THREADS), (size_t)smem, stream, tmK, tmV, (const bf16 *)q, ldq,
                      (bf16 *)out, ldo, cu_rows, seq_start, block_table, table_width, KV, G, scale * LOG2E, window);
 }

@@ -172,11 +172,10 @@ def attention(q: torch.Tensor, batch, block_table: torch.Tensor, k_pool: torch.T
         if batch.single_token:
             return fast_attention.attention_decode(q, batch.positions, block_table, k_pool, v_pool, n_heads,
                                                    n_kv_heads, head_dim, scale, window)
-        # Head size 128 with many new tokens: 128-row tiles on the tcgen05 tensor cores.  Head size 64 is bound
-        # by the exponentials, not the MMAs, and the mma.sync kernel with its twelve warps an SM hides their
-        # latency better (measured); a few rows (a sequence fed in short pieces) also waste less of its 64-row tile.
+        # Many new tokens: 128-row tiles on the tcgen05 tensor cores.  A few rows (a sequence fed in short pieces)
+        # waste less of the mma.sync kernel's 64-row tile.
         prefill = (fast_attention.attention_prefill_tc
-                   if head_dim == 128 and batch.max_new * (n_heads // n_kv_heads) >= 64
+                   if head_dim in (64, 128) and batch.max_new * (n_heads // n_kv_heads) >= 64
                    and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
                    else fast_attention.attention_prefill)
         return prefill(q, batch.cu_rows, batch.seq_start, block_table, k_pool, v_pool, batch.n_seq, batch.max_new,
