@@ -641,7 +641,7 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_con
                        int n_pt, int n_tiles) {
     constexpr int P_BYTES = BM * BK * 2, Q_BYTES = BN * BK * 2;
     constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
-    constexpr int TMEM_COLS = 2 * BN;             // two accumulators: 256 or 512 columns
+    constexpr int TMEM_COLS = BN <= 128 ? 256 : 512;   // two accumulators of BN columns; allocations are powers of two
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -833,6 +833,7 @@ static int dispatch(bool swap, int bn, const CUtensorMap &tmP, const CUtensorMap
     } else {
         switch (bn) {
         case 128: return launch_prefill<128, 6, EPI>(tmP, tmQ, a, st);
+        case 192: if (EPI != EPI_SILU_MUL) return launch_prefill<192, 5, EPI == EPI_SILU_MUL ? EPI_BF16 : EPI>(tmP, tmQ, a, st); break;
         case 256: return launch_prefill<256, 4, EPI>(tmP, tmQ, a, st);
         }
     }
@@ -872,10 +873,13 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
         }
         grid = dim3(tiles, 1, 1);
     } else {
+        // tile width: rounds of tiles over the 148 persistent CTAs times the width (a 128-wide tile costs a tenth
+        // more per column); 192 is there for feature counts like 3072 that quantise badly at 128 and 256
         int pt = (M + BM - 1) / BM;
-        long long t256 = (long long)pt * ((N + 255) / 256), t128 = (long long)pt * ((N + 127) / 128);
-        double c256 = (double)((t256 + 147) / 148), c128 = 0.55 * (double)((t128 + 147) / 148);
+        long long t256 = (long long)pt * ((N + 255) / 256), t192 = (long long)pt * ((N + 191) / 192), t128 = (long long)pt * ((N + 127) / 128);
+        double c256 = (double)((t256 + 147) / 148), c192 = 0.75 * (double)((t192 + 147) / 148), c128 = 0.55 * (double)((t128 + 147) / 148);
         bn = (N <= 128 || c128 < c256) ? 128 : 256;
+        if (epi != EPI_SILU_MUL && N > 128 && c192 < (bn == 128 ? c128 : c256)) bn = 192;
         grid = dim3(pt, (N + bn - 1) / bn, 1);
     }
     int kb_per_split = (total_kb + splits - 1) / splits;       // a split may be empty: it adds zeros
