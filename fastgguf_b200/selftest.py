@@ -98,6 +98,17 @@ def run_selftest(quick: bool = False) -> int:
         want = gg / (1 + torch.exp(-gg)) * uu
         got = fast_gemm.gemm_tc(a, fast_gemm.interleave_gate_up(w[:F], w[F:]), silu=True)
         r.check(f"gemm_tc silu(gate)*up {M}x{F}x{K}", _rel(got, want), 2 ** -7)
+    # an RMSNorm started by the contraction that writes the residual stream and finished by the one that reads it
+    M, E, N = 8, 512, 384
+    x0, a_in = torch.randn(M, E, generator=g).to(dev), (torch.randn(M, E, generator=g) * 0.5).bfloat16().to(dev)
+    w1, w2 = (torch.randn(E, E, generator=g) / 16).bfloat16().to(dev), (torch.randn(N, E, generator=g) / 16).bfloat16().to(dev)
+    nw = (1 + 0.1 * torch.randn(E, generator=g)).to(dev)
+    x = x0.clone()
+    _, started = fast_gemm.gemm_tc(a_in, w1, out=x, accumulate=True, emit_norm_weight=nw, emit_eps=1e-5)
+    got = fast_gemm.gemm_tc(started.xw, w2, deferred=started, out_dtype=torch.float32)
+    xd = x0.double() + a_in.double() @ w1.double().T
+    want = (xd / torch.sqrt((xd * xd).mean(1, keepdim=True) + 1e-5) * nw.double()) @ w2.double().T
+    r.check("gemm_tc deferred RMSNorm (started in one epilogue, finished in the next)", _rel(got, want), 2 ** -7)
     r.check("gemm_tc pipeline error flag", float(fast_gemm.pipeline_error()), 0.0)
 
     # ---- row-wise kernels
@@ -158,8 +169,25 @@ def run_selftest(quick: bool = False) -> int:
         cu = torch.tensor([0, 200, 201, 268], dtype=torch.int32).to(dev)
         got = fast_attention.attention_prefill(q, cu, torch.tensor(before, dtype=torch.int32).to(dev), tbl, kp, vp, 3, 200,
                                                H, KV, hd, 1 / math.sqrt(hd))
-        r.check(f"attention_prefill heads {H}/{KV} size {hd}",
-                _rel(got, _attn_plain(q, dense, before, new, H, KV, hd, 1 / math.sqrt(hd))), 1.5e-2)
+        want = _attn_plain(q, dense, before, new, H, KV, hd, 1 / math.sqrt(hd))
+        r.check(f"attention_prefill heads {H}/{KV} size {hd}", _rel(got, want), 1.5e-2)
+        got = fast_attention.attention_prefill_tc(q, cu, torch.tensor(before, dtype=torch.int32).to(dev), tbl, kp, vp, 3, 200,
+                                                  H, KV, hd, 1 / math.sqrt(hd))
+        r.check(f"attention_prefill_tc (tcgen05) heads {H}/{KV} size {hd}", _rel(got, want), 1.5e-2)
+        r.check("attention_prefill_tc pipeline error flag", float(fast_attention.prefill_tc_error()), 0.0)
+        # the decode step's kernel: rotary encoding of q and the new k, cache append and attention in one
+        before = [0, 63, 64, 700]
+        dense, kp, vp, tbl = _paged([b + 1 for b in before], KV, hd, torch.bfloat16, g)
+        qkv = torch.randn(4, (H + 2 * KV) * hd, generator=g).bfloat16().to(dev)
+        positions = torch.tensor(before, dtype=torch.int32).to(dev)
+        ang = torch.arange(1024).double()[:, None] * torch.pow(torch.tensor(10000.0, dtype=torch.float64), -2.0 * torch.arange(hd // 2) / hd)
+        cos, sin = torch.cos(ang).float().to(dev), torch.sin(ang).float().to(dev)
+        k1, v1, q1 = kp.clone(), vp.clone(), qkv.clone()
+        ops.rope_append(q1, positions, torch.arange(4, dtype=torch.int32, device=dev), tbl, k1, v1, cos, sin, H, KV, hd)
+        want = fast_attention.attention_decode(q1, positions, tbl, k1, v1, H, KV, hd, 1 / math.sqrt(hd), n_splits=1)
+        got = fast_attention.attention_decode_fused(qkv, positions, tbl, kp, vp, cos, sin, H, KV, hd, 1 / math.sqrt(hd), n_splits=4)
+        r.check(f"attention_decode_fused vs rope + append + attention, heads {H}/{KV} size {hd}", _rel(got, want), 1.5e-2)
+        r.check("attention_decode_fused wrote the same cache rows", float((kp != k1).sum() + (vp != v1).sum()), 0.0)
 
     # ---- sampler: greedy is the first maximum; draws follow the probabilities (fastgguf.c:5426-5444)
     lg = torch.randn(3, 70001, generator=g).to(dev)
