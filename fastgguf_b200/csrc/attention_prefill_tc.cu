@@ -7,16 +7,20 @@
 // Grid (kv head x head chunk, query tile, sequence): CTAs are dispatched x first, so the tiles that see the most
 // keys (the late ones, y = 0) all start before any light one and the tail of the kernel is short.  A CTA owns 128 rows = TQ consecutive new
 // tokens x Gc query heads of one KV head (Gc = min(G, 16), row r = token r / Gc, head r % Gc) and
-// walks the sequence's pages two at a time (128 keys):
+// walks the sequence's pages, two at a time (128 keys) at head size 64 and one at a time at head size 128, so
+// that two CTAs fit on an SM at either size and the softmax of one runs under the MMAs of the other:
 //
-//   warp 0 (one lane)  TMA: the K tile and the V tile of two pages (128B swizzle); the next K tile is
+//   warp 0 (one lane)  TMA: the K tile and the V tile of an iteration (128B swizzle); the next K tile is
 //                      fetched as soon as S has consumed the current one, the next V tile after P V
-//   warp 1 (one lane)  MMA: S = Q K^T (128 x 128 x HD), then, once P is in shared memory,
-//                      O_tile = P V (128 x HD x 128); V is the MN-major operand (its rows are keys)
+//   warp 1 (one lane)  MMA: S = Q K^T (128 x KEYS x HD), then, once P is in shared memory,
+//                      O += P V (128 x HD x KEYS) into the same tensor-memory accumulator, iteration after
+//                      iteration; V is the MN-major operand (its rows are keys)
 //   warps 2-5          thread = row: read S from tensor memory, scale, mask, running max and sum in
-//                      f32 (base-2 exponent), write P as bf16 into swizzled shared memory, then add
-//                      O_tile into the row's f32 accumulator in registers, rescaled by the change of
-//                      the maximum; at the end divide by the sum and store the row.
+//                      f32 (base-2 exponent), write P as bf16 into swizzled shared memory.  Probabilities are
+//                      taken relative to a base that may lag the row's true maximum (see below); only when a
+//                      row's base has to move does its warp rescale its rows of O in tensor memory
+//                      (tcgen05.ld / st), after the MMAs before have finished.  At the end the row is read
+//                      once, divided by the sum and stored.
 //
 // Every mbarrier wait is bounded (error flag, tensor memory freed, copies in flight awaited).
 #include <cuda.h>
@@ -26,7 +30,6 @@
 #define FG_ERR_TENSORMAP 10004
 #define PAGE 64
 #define ROWS 128
-#define KEYS 128                     // keys per iteration: two pages
 #define ATT_THREADS 192
 #define WAIT_LIMIT_CYCLES 2000000000ll
 #define LOG2E 1.4426950408889634f
@@ -83,6 +86,22 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
 #pragma unroll
     for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
 }
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 ::"r"(taddr),
+                   "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+                   "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+                   "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+                   "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+                   "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+                   "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+                   "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+                   "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+                 : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -108,14 +127,15 @@ __device__ __forceinline__ uint32_t make_idesc(int M, int N, int b_mn_major) {
 __device__ __forceinline__ void raise_error(int role) { atomicCAS(&g_attn_error, 0, (FG_ERR_PIPELINE << 8) | role); }
 
 template <int HD>
-__global__ void __launch_bounds__(ATT_THREADS, HD <= 64 ? 2 : 1)   // head size 64: two CTAs share an SM and overlap
+__global__ void __launch_bounds__(ATT_THREADS, 2)                  // two CTAs share an SM and overlap
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                        const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out, int ldo,
                        const int *__restrict__ cu_rows, const int *__restrict__ seq_start,
                        const int *__restrict__ block_table, int table_width, int KV, int G, float scale_log2, int window) {
     constexpr int CH = HD / 64;                        // 64-wide chunks of the head dimension
+    constexpr int KEYS = HD > 64 ? 64 : 128, NPG = KEYS / PAGE;      // keys and pages per iteration
     constexpr int Q_BYTES = ROWS * HD * 2, KV_TILE = KEYS * HD * 2;
-    constexpr uint32_t TMEM_COLS = 256;                // S: columns 0..127, O tile: 128..128+HD
+    constexpr uint32_t TMEM_COLS = 256;                // S: columns 0..KEYS-1, O: KEYS..KEYS+HD-1
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -150,7 +170,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     const int tile_hi = start + q0 + tq - 1;
     const int tile_lo = (window > 0 && start + q0 - window + 1 > 0) ? start + q0 - window + 1 : 0;
     const int p_begin = tile_lo / PAGE, p_end = tile_hi / PAGE + 1;
-    const int n_iter = active ? (p_end - p_begin + 1) / 2 : 0;
+    const int n_iter = active ? (p_end - p_begin + NPG - 1) / NPG : 0;
     const int *bt = block_table + (size_t)b * table_width;
 
     // ---- Q tile -> shared memory, swizzled like a TMA tile (rows past the valid ones are zero)
@@ -181,17 +201,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         if (lane == 0) {
             int k_issued = 0, v_issued = 0;
             for (int j = 0; j < n_iter; j++) {
-                int y[2];
-                for (int h = 0; h < 2; h++)
-                    y[h] = (bt[min(p_begin + 2 * j + h, p_end - 1)] * KV + kvh) * PAGE;   // a page past the end is masked anyway
+                int y[NPG];
+                for (int h = 0; h < NPG; h++)
+                    y[h] = (bt[min(p_begin + NPG * j + h, p_end - 1)] * KV + kvh) * PAGE;   // a page past the end is masked anyway
                 if (!mbar_wait(k_empty, (j & 1) ^ 1)) { raise_error(1); break; }
                 mbar_expect_tx(k_full, KV_TILE);
-                for (int h = 0; h < 2; h++)
+                for (int h = 0; h < NPG; h++)
                     for (int c = 0; c < CH; c++) tma_load_2d(kt + c * (KEYS * 128) + h * (PAGE * 128), &tmK, c * 64, y[h], k_full);
                 k_issued = j + 1;
                 if (!mbar_wait(v_empty, (j & 1) ^ 1)) { raise_error(1); break; }
                 mbar_expect_tx(v_full, KV_TILE);
-                for (int h = 0; h < 2; h++)
+                for (int h = 0; h < NPG; h++)
                     for (int c = 0; c < CH; c++) tma_load_2d(vt + c * (KEYS * 128) + h * (PAGE * 128), &tmV, c * 64, y[h], v_full);
                 v_issued = j + 1;
             }
@@ -207,8 +227,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {
-                    uint32_t off = (ks >> 2) * (ROWS * 128) + (ks & 3) * 32;
-                    tc_mma_bf16(tmem_base, desc_k_major(qs + off), desc_k_major(kt + off), idesc_s, ks != 0);
+                    // 64-wide chunk ks / 4 of the head dimension (ROWS rows of Q, KEYS rows of K), 32 B inside its swizzle row
+                    const uint32_t qoff = (ks >> 2) * (ROWS * 128) + (ks & 3) * 32, koff = (ks >> 2) * (KEYS * 128) + (ks & 3) * 32;
+                    tc_mma_bf16(tmem_base, desc_k_major(qs + qoff), desc_k_major(kt + koff), idesc_s, ks != 0);
                 }
                 tc_commit(s_full);
                 tc_commit(k_empty);                  // the K tile is free once S is complete
@@ -224,7 +245,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                     // A = P: 64-key chunk ks / 4, 32 B inside its swizzle row; B = V: 16 keys = two 8-key groups
                     uint64_t adesc = desc_k_major(ps + (ks >> 2) * (ROWS * 128) + (ks & 3) * 32);
                     uint64_t bdesc = desc_mn_major(vt + ks * 2048, KEYS * 128);
-                    tc_mma_bf16(tmem_base + KEYS, adesc, bdesc, idesc_o, ks != 0);
+                    tc_mma_bf16(tmem_base + KEYS, adesc, bdesc, idesc_o, (j | ks) != 0);     // O accumulates over the iterations
                 }
                 tc_commit(o_full);
                 tc_commit(v_empty);
@@ -235,14 +256,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         // ------------------------------------------------------------ softmax, one thread per row
         const int r = (warp & 3) * 32 + lane;
         const uint32_t trow = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-        float o[HD];
-#pragma unroll
-        for (int d = 0; d < HD; d++) o[d] = 0.f;
         float m = -INFINITY, l = 0.f;
+        bool ok = true;
         for (int j = 0; j < n_iter; j++) {
-            const int key0 = (p_begin + 2 * j) * PAGE;
+            const int key0 = (p_begin + NPG * j) * PAGE;
             const bool masked = key0 + KEYS - 1 > hi || key0 < lo;
-            if (!mbar_wait(s_full, j & 1)) { raise_error(4); break; }
+            if (!mbar_wait(s_full, j & 1)) { raise_error(4); ok = false; break; }
             tc_fence_after();
             // One pass when the running base is still good: probabilities relative to m, which may lag the
             // true maximum by up to 2^8 (harmless in f32 / bf16, and the same factor is in l and in O).  A row
@@ -326,32 +345,44 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             }
             l = l * corr + sum;
             m = m_keep;
+            if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+                // a base moved: the rows of O so far are rescaled in tensor memory, once the MMAs before this
+                // iteration have finished (the next P V is not issued before every row has arrived below)
+                if (!mbar_wait(o_full, (j - 1) & 1)) { raise_error(5); ok = false; break; }
+                tc_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < HD / 32; c++) {
+                    float v[32];
+                    tc_ld32(trow + KEYS + c * 32, v);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) v[i] *= corr;
+                    tc_st32(trow + KEYS + c * 32, v);
+                }
+            }
             tc_fence_before();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(p_full);
-            if (!mbar_wait(o_full, j & 1)) { raise_error(5); break; }
-            tc_fence_after();
-#pragma unroll
+        }
+        if (ok && n_iter > 0 && !mbar_wait(o_full, (n_iter - 1) & 1)) { raise_error(5); ok = false; }
+        tc_fence_after();
+        if (n_iter > 0 && __all_sync(0xffffffffu, ok)) {           // the tensor-memory loads are warp-wide: every lane takes part
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            bf16 *dst = out + (size_t)(row0 + q0 + t_row) * ldo + (size_t)(kvh * G + g_row) * HD;
+#pragma unroll 1
             for (int c = 0; c < HD / 32; c++) {
                 float v[32];
                 tc_ld32(trow + KEYS + c * 32, v);
+                if (!valid) continue;
 #pragma unroll
-                for (int i = 0; i < 32; i++) o[c * 32 + i] = o[c * 32 + i] * corr + v[i];
-            }
-            tc_fence_before();
-        }
-        if (valid) {
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
-            bf16 *dst = out + (size_t)(row0 + q0 + t_row) * ldo + (size_t)(kvh * G + g_row) * HD;
+                for (int k8 = 0; k8 < 4; k8++) {
+                    uint32_t w[4];
 #pragma unroll
-            for (int c = 0; c < HD / 8; c++) {
-                uint32_t w[4];
-#pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    __nv_bfloat162 t = __floats2bfloat162_rn(o[c * 8 + 2 * k] * inv, o[c * 8 + 2 * k + 1] * inv);
-                    w[k] = *(uint32_t *)&t;
+                    for (int k = 0; k < 4; k++) {
+                        __nv_bfloat162 t = __floats2bfloat162_rn(v[k8 * 8 + 2 * k] * inv, v[k8 * 8 + 2 * k + 1] * inv);
+                        w[k] = *(uint32_t *)&t;
+                    }
+                    *(uint4 *)(dst + c * 32 + k8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
-                *(uint4 *)(dst + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
     }
@@ -398,6 +429,7 @@ template <int HD>
 static int launch_tc(const CUtensorMap &tmK, const CUtensorMap &tmV, const void *q, int ldq, void *out, int ldo,
                      const int *cu_rows, const int *seq_start, const int *block_table, int table_width, int n_seq,
                      int max_new, int H, int KV, float scale, int window, cudaStream_t stream) {
+    constexpr int KEYS = HD > 64 ? 64 : 128;
     constexpr int smem = ROWS * HD * 2 + 2 * KEYS * HD * 2 + ROWS * KEYS * 2 + 1024;
     static bool configured = false;
     if (!configured) {

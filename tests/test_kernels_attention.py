@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 PAGE = 64
 
 
-def make_case(lens_before, new, H, KV, hd, dtype, seed, boost=True):
+def make_case(lens_before, new, H, KV, hd, dtype, seed, boost=True, ramp=0.0):
     """Sequences with `lens_before[i]` cached tokens that bring `new[i]` more.  Returns everything
     the kernels need plus dense per-sequence K, V (float64) for the plain computation."""
     g = torch.Generator(device="cpu").manual_seed(seed)
@@ -30,6 +30,9 @@ def make_case(lens_before, new, H, KV, hd, dtype, seed, boost=True):
         V = torch.randn(total[s], KV, hd, generator=g)
         if boost and total[s] > 3:
             K[total[s] // 3] *= 4.0                                      # one key that stands out
+        if ramp:
+            # scores that keep growing with the key's position: the running maximum moves in every block of keys
+            K += (torch.arange(total[s]) / 16.0)[:, None, None] * ramp / hd ** 0.5
         K, V = K.to(dtype).float(), V.to(dtype).float()
         dense.append((K.double(), V.double()))
         for p in range((total[s] + PAGE - 1) // PAGE):
@@ -39,7 +42,10 @@ def make_case(lens_before, new, H, KV, hd, dtype, seed, boost=True):
             k_pool[page, :, :n] = K[p * PAGE:p * PAGE + n].transpose(0, 1)
             v_pool[page, :, :n] = V[p * PAGE:p * PAGE + n].transpose(0, 1)
     M = sum(new)
-    q = torch.randn(M, H * hd, generator=g).to(dtype)
+    q = torch.randn(M, H * hd, generator=g)
+    if ramp:
+        q += hd ** 0.5
+    q = q.to(dtype)
     positions = torch.tensor([lens_before[s] + i for s in range(n_seq) for i in range(new[s])], dtype=torch.int32)
     row_seq = torch.tensor([s for s in range(n_seq) for _ in range(new[s])], dtype=torch.int32)
     cu = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32)
@@ -148,3 +154,17 @@ def test_attention_decode_fused_with_rope_and_append(H, KV, hd, window, n_splits
                                                 scale, window, n_splits=n_splits)
     assert (got.float() - want.float()).abs().max() <= 2e-2 * want.float().abs().max()
     assert torch.equal(k2, k1) and torch.equal(v2, v1)          # the cache received the same rows
+
+
+@pytest.mark.parametrize("H,KV,hd", [(8, 2, 64), (4, 1, 128)])
+def test_attention_prefill_tcgen05_growing_maximum(H, KV, hd):
+    """Scores that grow by tens of binary orders every 128 keys: every iteration moves the running base, and
+    the rows of the output accumulated so far are rescaled in tensor memory."""
+    from fastgguf_b200.ops import fast_attention
+    scale = 1.0 / math.sqrt(hd)
+    case = make_case([0, 300], [600, 200], H, KV, hd, torch.bfloat16, 21, boost=False, ramp=2.0)
+    got = fast_attention.attention_prefill_tc(case["q"], case["cu_rows"], case["seq_start"], case["table"], case["k_pool"],
+                                              case["v_pool"], 2, 600, H, KV, hd, scale, 0)
+    assert fast_attention.prefill_tc_error() == 0
+    want = plain(case, H, KV, hd, scale, 0)
+    assert (got.double().cpu() - want).abs().max().item() <= 2e-2 * want.abs().max().item()
