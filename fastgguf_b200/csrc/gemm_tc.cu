@@ -4,15 +4,15 @@
 // Role in the reference: matvec / matvec_multi / matmul (fastgguf.c:2575-2622, :2552-2573,
 // :3004-3093) - every projection of the decoder, for one token or a batch of prompt tokens.
 //
-// One CTA computes a 128 x BN tile of the MMA: "P" rows are its M side (128), "Q" rows its N side.
-//   SWAP (decode, up to 64 tokens): P = weight rows, Q = token rows (BN = 16/32/64).  The kernel
-//     streams the weights once; when there are too few tiles to fill the GPU, a thread-block
-//     cluster of 2/4/8 CTAs splits K: every CTA pushes the columns of its partial tile into the
-//     shared memory of the CTA that owns them (st.shared::cluster), one cluster barrier makes the
-//     pushes visible, and the owner sums them in rank order (deterministic) from its own shared
-//     memory - no scratch in global memory, no remote loads.
-//   not SWAP (prefill): P = 128 token rows, Q = BN = 128/256 weight rows; a thread of the epilogue
-//     owns one token row and writes runs of consecutive features with 16-byte stores.
+// Two kernels share the building blocks of this file:
+//   gemm_tc_decode_kernel (up to 64 tokens): the 128 rows of the MMA's M side are weight rows, its N side the
+//     token rows (BN = 16/32/64).  The kernel streams the weights once; when there are too few tiles to fill
+//     the GPU, a thread-block cluster of 2/4/8 CTAs splits K: every CTA pushes the columns of its partial
+//     tile into the shared memory of the CTA that owns them (st.shared::cluster), one cluster barrier makes
+//     the pushes visible, and the owner sums them in rank order (deterministic) from its own shared memory -
+//     no scratch in global memory, no remote loads.
+//   gemm_tc_prefill_kernel: 128 token rows x BN = 128/192/256 weight rows per tile, persistent CTAs, two
+//     accumulators in tensor memory.
 //
 //   warp 0      TMA producer (one lane): K-blocks of 64 into a ring of smem stages, 128B swizzle.
 //               The weight tiles of the first stages are fetched BEFORE the wait on the preceding
@@ -136,19 +136,6 @@ __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.w
 // silu(g) * u in f32 with the fast exponential and division (2 ulp each): the result is rounded to bfloat16
 // (8 bits of mantissa) right after, and the precise forms made the epilogue of a 64-token tile several us long
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
-
-// warp sums of N independent values: the shuffles of one round are issued back to back, so the latency of a round
-// is paid once, not once per value
-template <int N> __device__ __forceinline__ void warp_sum_n(float (&v)[N]) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        float t[N];
-#pragma unroll
-        for (int i = 0; i < N; i++) t[i] = __shfl_xor_sync(0xffffffffu, v[i], o);
-#pragma unroll
-        for (int i = 0; i < N; i++) v[i] += t[i];
-    }
-}
 
 struct GemmArgs {
     void *out;            // [M, ldc] bf16 or f32 by epilogue

@@ -1,6 +1,7 @@
 """bfloat16 tensor-core attention over the paged cache: a decode kernel (one new token per
-sequence, pages split over CTAs) and a prefill kernel (tiles of new tokens x query heads).
-Both take head sizes 64 and 128 and pages of 64 positions; ``supported`` says so, and the
+sequence, pages split over CTAs; its fused form also rotates q and k and appends k and v), a
+tcgen05 prefill kernel (128-row tiles of new tokens x query heads) and an mma.sync prefill kernel for
+short pieces.  All take head sizes 64 and 128 and pages of 64 positions; ``supported`` says so, and the
 caller uses the any-size kernel otherwise."""
 from __future__ import annotations
 

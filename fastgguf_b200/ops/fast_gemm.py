@@ -4,8 +4,9 @@
 None when the sizes are outside what the fast kernel takes (a reduction length that is no
 multiple of 8, unaligned rows), in which case the caller uses the plain kernel.
 
-With few rows (decode) and few weight tiles the kernel splits the reduction over a thread-block
-cluster and sums the partial tiles through distributed shared memory; it needs no scratch memory.
+With few rows (decode) one kernel serves every projection; with few weight tiles it splits the reduction
+over a thread-block cluster, whose CTAs push their partial columns into the owner's shared memory; it
+needs no scratch memory.
 """
 from __future__ import annotations
 
