@@ -840,6 +840,17 @@ extern "C" int fg_gemm_tc_max_ss_tiles(int N) { return (N + BM - 1) / BM; }
 // EPI_SILU_MUL: W is [N = 2F, K] with gate and up interleaved in blocks of 64 rows; out is [M, F] bf16.
 // Returns FG_ERR_BAD_SIZE for shapes TMA cannot describe (K % 8, unaligned bases): the caller
 // then uses the plain kernel.
+// streaming multiprocessors of the current device (148 on a B200)
+static int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
 extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *out, int ldc, int epi,
                           int M, int N, int K, int force_splits, const float *ss_in, int ss_tiles, int ss_size,
                           float ss_eps, const float *norm_w, void *xw_out, float *ss_out, int *ss_tiles_out,
@@ -856,17 +867,18 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
         int tiles = (N + BM - 1) / BM;
         // too few tiles to fill 148 SMs: a cluster of 2, 4 or 8 CTAs shares each tile along K
         if (epi != EPI_SILU_MUL) {
-            while (splits < 8 && tiles * splits < 120 && total_kb >= 4 * splits) splits *= 2;
+            while (splits < 8 && tiles * splits < sm_count() * 4 / 5 && total_kb >= 4 * splits) splits *= 2;
             if (force_splits == 1 || force_splits == 2 || force_splits == 4 || force_splits == 8)
                 if (force_splits <= total_kb) splits = force_splits;
         }
         grid = dim3(tiles, 1, 1);
     } else {
-        // tile width: rounds of tiles over the 148 persistent CTAs times the width (a 128-wide tile costs a tenth
+        // tile width: rounds of tiles over the persistent CTAs (one an SM) times the width (a 128-wide tile costs a tenth
         // more per column); 192 is there for feature counts like 3072 that quantise badly at 128 and 256
         int pt = (M + BM - 1) / BM;
         long long t256 = (long long)pt * ((N + 255) / 256), t192 = (long long)pt * ((N + 191) / 192), t128 = (long long)pt * ((N + 127) / 128);
-        double c256 = (double)((t256 + 147) / 148), c192 = 0.75 * (double)((t192 + 147) / 148), c128 = 0.55 * (double)((t128 + 147) / 148);
+        const int sms = sm_count();
+        double c256 = (double)((t256 + sms - 1) / sms), c192 = 0.75 * (double)((t192 + sms - 1) / sms), c128 = 0.55 * (double)((t128 + sms - 1) / sms);
         bn = (N <= 128 || c128 < c256) ? 128 : 256;
         if (epi != EPI_SILU_MUL && N > 128 && c192 < (bn == 128 ? c128 : c256)) bn = 192;
         grid = dim3(pt, (N + bn - 1) / bn, 1);

@@ -24,7 +24,15 @@ register_signatures("attn", {
                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
 })
 
-N_SM = 148
+_n_sm = {}
+
+
+def n_sm(device=None) -> int:
+    """Streaming multiprocessors of the device (148 on a B200)."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    if idx not in _n_sm:
+        _n_sm[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _n_sm[idx]
 
 
 def supported(q: torch.Tensor, k_pool: torch.Tensor, head_dim: int) -> bool:
@@ -39,7 +47,7 @@ def decode_splits(n_seq: int, n_heads: int, n_kv_heads: int, table_width: int) -
     both 2 and 8.  Up to 8 splits (a power of two) are merged inside a thread-block cluster; only contexts
     beyond 16K positions take more splits and the scratch-memory path."""
     ctas = n_seq * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
-    want = max(1, min((3 * N_SM // 2 + ctas - 1) // ctas, table_width))
+    want = max(1, min((3 * n_sm() // 2 + ctas - 1) // ctas, table_width))
     if want > 8 and table_width > 256:
         return want
     s = 1
