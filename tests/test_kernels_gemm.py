@@ -93,3 +93,24 @@ def test_gemm_tc_refuses_unaligned():
     a, w = _operands(4, 32, 36, torch.bfloat16, 5)      # K % 8 != 0: TMA cannot describe the rows
     assert fast_gemm.gemm_tc(a, w) is None
     assert fast_gemm.plan_for_weight(w) is None
+
+
+@pytest.mark.parametrize("M,N,K", [(513, 3072, 256), (700, 3000, 136), (300, 1152, 2048), (129, 2048, 512)])
+def test_gemm_tc_prefill_tile_widths_and_started_norm(M, N, K):
+    """Prefill shapes that pick 192-wide tiles (3072, 3000 and 1152 features), whole and ragged, and 256-wide ones;
+    plain, residual add through the shared-memory tiles (N % 32 == 0) and row-wise (3000), with the next norm started."""
+    from fastgguf_b200.ops import fast_gemm
+    a, w = _operands(M, N, K, torch.bfloat16, 6)
+    want = a.double() @ w.double().T
+    _check(fast_gemm.gemm_tc(a, w, out_dtype=torch.float32), a, w, want, False)
+    _check(fast_gemm.gemm_tc(a, w), a, w, want, True)
+    res = torch.randn(M, N, device="cuda")
+    nw = (1 + 0.1 * torch.randn(N, device="cuda")).float()
+    acc = res.clone()
+    out, started = fast_gemm.gemm_tc(a, w, out=acc, accumulate=True, emit_norm_weight=nw, emit_eps=1e-5)
+    x = want + res.double()
+    _check(acc, a, w, x, False)
+    assert (started.xw.double() - x * nw.double()).abs().max().item() <= 2 ** -7 * (x * nw.double()).abs().max().item()
+    ss = started.ss[:started.tiles].double().sum(0)
+    assert ((ss - (x * x).sum(1)).abs() / (x * x).sum(1)).max().item() < 1e-4
+    assert fast_gemm.pipeline_error() == 0
