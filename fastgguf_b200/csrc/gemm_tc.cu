@@ -52,7 +52,7 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// bounded wait: false when the limit ran out (not inlined: it has many call sites, and code size counts)
+// bounded wait: false when the limit ran out
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     long long t0 = clock64();
     for (;;) {
