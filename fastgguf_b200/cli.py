@@ -93,15 +93,20 @@ def cmd_generate(model_dir: str, argv: List[str]) -> int:
         print(e)
         return 2
     cfg = engine.config
-    print(f"[Config] {type(cfg).architecture_names[0]}: layers={len(engine.spec.layers)} embd={engine.spec.hidden_size} "
-          f"ctx={engine.cache.max_seq_len} dtype={o['dtype']}")
-    print(f"[Model] {len(engine.model.expected_tensors())} tensors, vocab={engine.spec.vocab_size}")
+
+    def say(*args, **kw):
+        # with --json the standard output is one JSON document; the summary lines go to the standard error
+        print(*args, file=sys.stderr if o["json"] else sys.stdout, **kw)
+
+    say(f"[Config] {type(cfg).architecture_names[0]}: layers={len(engine.spec.layers)} embd={engine.spec.hidden_size} "
+        f"ctx={engine.cache.max_seq_len} dtype={o['dtype']}")
+    say(f"[Model] {len(engine.model.expected_tensors())} tensors, vocab={engine.spec.vocab_size}")
     if o["temp"] <= 0:
-        print("[Sampler] greedy", end="")
+        say("[Sampler] greedy", end="")
     else:
-        print(f"[Sampler] temp={o['temp']:.2f} top_k={o['top_k']} top_p={o['top_p']:.2f}", end="")
-    print(f" repeat_penalty={o['repeat_penalty']:.2f} (last {o['repeat_last_n']}) max_tokens={o['max_tokens']} "
-          f"seed={o['seed']}")
+        say(f"[Sampler] temp={o['temp']:.2f} top_k={o['top_k']} top_p={o['top_p']:.2f}", end="")
+    say(f" repeat_penalty={o['repeat_penalty']:.2f} (last {o['repeat_last_n']}) max_tokens={o['max_tokens']} "
+        f"seed={o['seed']}")
     import torch
     t0 = time.time()
     out = engine.generate(o["prompts"], temp=o["temp"], top_k=o["top_k"], top_p=o["top_p"],
@@ -115,7 +120,7 @@ def cmd_generate(model_dir: str, argv: List[str]) -> int:
     else:
         for i, c in enumerate(out):
             print(f"[{i}] {' '.join(str(t) for t in c.tokens)}  ({c.finish_reason})")
-    print(f"[gen: {n_gen} tok in {dt:.2f}s @ {n_gen / max(dt, 1e-9):.2f} tok/s, prompts included]")
+    say(f"[gen: {n_gen} tok in {dt:.2f}s @ {n_gen / max(dt, 1e-9):.2f} tok/s, prompts included]")
     return 0
 
 

@@ -40,9 +40,12 @@ def test_generate_command(tmp_path):
     p = run("generate", d, "256", "--temp", "0", "--max-tokens", "6", "--prompt", "5,17,3", "--prompt", "9", "--json",
             "--ignore-eos")
     assert p.returncode == 0, p.stdout + p.stderr
-    assert "[Sampler] greedy" in p.stdout and "[Config] LlamaForCausalLM: layers=2 embd=256 ctx=256" in p.stdout
-    out = json.loads([l for l in p.stdout.splitlines() if l.startswith("[{")][0])
+    # with --json the standard output is the JSON document alone; the summary lines are on the standard error
+    assert "[Sampler] greedy" in p.stderr and "[Config] LlamaForCausalLM: layers=2 embd=256 ctx=256" in p.stderr
+    out = json.loads(p.stdout)
     assert [len(o["tokens"]) for o in out] == [6, 6] and all(o["finish_reason"] == "length" for o in out)
+    t = run("generate", d, "256", "--temp", "0", "--max-tokens", "3", "--prompt", "5,17,3", "--ignore-eos")
+    assert t.returncode == 0 and "[Sampler] greedy" in t.stdout and "[0] " in t.stdout and "[gen: 3 tok" in t.stdout
     q = run("generate", d, "256", "--temp", "0", "--max-tokens", "6", "--prompt", "5,17,3", "--prompt", "9", "--json",
             "--ignore-eos", "--dtype", "float32")
     assert q.returncode == 0
