@@ -391,28 +391,32 @@ topk_stage2_kernel(const unsigned long long *__restrict__ cand_in, int n_cand, i
             __syncthreads();
         }
     }
+    // the weights exp((v - top) / temp) of the k best, one thread each; the sums below add them in index order,
+    // as the serial sampler does (the same floats in the same order: the same token)
+    __shared__ float wgt[TOPK_MAX_K];
+    if (tid < k) wgt[tid] = expf((key_float((uint32_t)(cand[tid] >> 32)) - key_float((uint32_t)(cand[0] >> 32))) / sp.temp);
+    __syncthreads();
     if (tid == 0) {
         int n = 0;
         while (n < k && cand[n] != 0ull) n++;
-        float top = key_float((uint32_t)(cand[0] >> 32));
         float sum = 0.f;
-        for (int i = 0; i < n; i++) sum += expf((key_float((uint32_t)(cand[i] >> 32)) - top) / sp.temp);
+        for (int i = 0; i < n; i++) sum += wgt[i];
         int keep = n;
         if (sp.top_p > 0.f && sp.top_p < 1.0f) {
             float cum = 0.f, lim = sp.top_p * sum;
             for (int i = 0; i < n; i++) {
-                cum += expf((key_float((uint32_t)(cand[i] >> 32)) - top) / sp.temp);
+                cum += wgt[i];
                 if (cum >= lim) { keep = i + 1; break; }
             }
         }
         float tot = 0.f;
-        for (int i = 0; i < keep; i++) tot += expf((key_float((uint32_t)(cand[i] >> 32)) - top) / sp.temp);
+        for (int i = 0; i < keep; i++) tot += wgt[i];
         uint64_t st = rng[slot];
         float r = (float)(xorshift64star(&st) >> 40) / 16777216.0f * tot;
         rng[slot] = st;
         int pick = keep - 1;
         for (int i = 0; i < keep; i++) {
-            r -= expf((key_float((uint32_t)(cand[i] >> 32)) - top) / sp.temp);
+            r -= wgt[i];
             if (r < 0.f) { pick = i; break; }
         }
         int chosen = (int)(~(uint32_t)(cand[pick] & 0xffffffffull));
