@@ -41,7 +41,15 @@ def ptr(t) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream() -> c_void_p:
+    """The current CUDA stream of the current device, as a handle for the launchers.  Asked through the
+    raw-stream call when this torch has it: ``torch.cuda.current_stream()`` builds a Stream object on every
+    call (7 us), a third of the host time of a step launched kernel by kernel."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
