@@ -40,14 +40,20 @@ def supported(q: torch.Tensor, k_pool: torch.Tensor, head_dim: int) -> bool:
             and k_pool.shape[2] == 64 and q.stride(1) == 1 and q.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0)
 
 
-def decode_splits(n_seq: int, n_heads: int, n_kv_heads: int, table_width: int) -> int:
-    """How many CTAs share one sequence's pages: about one and a half CTAs per SM in all.  More than fit on
-    the GPU at once (three per SM, fewer beside the contraction kernels that are already resident) run as a
-    second wave whose page loads start late; measured at batch 8 with 8 KV heads, 4 splits (256 CTAs) beat
-    both 2 and 8.  Up to 8 splits (a power of two) are merged inside a thread-block cluster; only contexts
-    beyond 16K positions take more splits and the scratch-memory path."""
+def decode_splits(n_seq: int, n_heads: int, n_kv_heads: int, table_width: int, head_dim: int = 64) -> int:
+    """How many CTAs share one sequence's pages: about one and a half CTAs per SM in all, and never more than fit
+    on the GPU at once - three per SM at head size 64, one at 128 (each warp holds a K and a V page in shared
+    memory), fewer beside the contraction kernels that are already resident.  What does not fit runs as a second
+    wave whose page loads start late; measured at batch 8 with 8 KV heads and head size 64, 4 splits (256 CTAs)
+    beat both 2 and 8, and at head size 128 two splits (128 CTAs) beat four.  Up to 8 splits (a power of two) are
+    merged inside a thread-block cluster; only contexts beyond 16K positions take more splits and the
+    scratch-memory path."""
     ctas = n_seq * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
-    want = max(1, min((3 * n_sm() // 2 + ctas - 1) // ctas, table_width))
+    if head_dim <= 64:
+        want = (3 * n_sm() // 2 + ctas - 1) // ctas
+    else:
+        want = n_sm() // ctas
+    want = max(1, min(want, table_width))
     if want > 8 and table_width > 256:
         return want
     s = 1
@@ -61,7 +67,7 @@ def attention_decode(q, positions, block_table, k_pool, v_pool, n_heads, n_kv_he
     """q: [B, >= H*hd] bf16, one new token per sequence at ``positions[b]`` (already in the cache)."""
     B = q.shape[0]
     if n_splits is None:
-        n_splits = decode_splits(B, n_heads, n_kv_heads, block_table.shape[1])
+        n_splits = decode_splits(B, n_heads, n_kv_heads, block_table.shape[1], head_dim)
     if out is None:
         out = torch.empty((B, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
     part_o = part_ml = None
@@ -113,7 +119,7 @@ def attention_decode_fused(qkv, positions, block_table, k_pool, v_pool, cos, sin
     (very long contexts): the caller then runs RoPE + append and attention separately."""
     B = qkv.shape[0]
     if n_splits is None:
-        n_splits = decode_splits(B, n_heads, n_kv_heads, block_table.shape[1])
+        n_splits = decode_splits(B, n_heads, n_kv_heads, block_table.shape[1], head_dim)
     if n_splits not in (1, 2, 4, 8):
         return None
     if out is None:
