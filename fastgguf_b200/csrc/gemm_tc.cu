@@ -393,7 +393,9 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     const int warp = warp_index(), lane = threadIdx.x & 31;      // uniform: the role branches below are not divergent
     const int stages = a.stages, epi = a.epi, S = gridDim.z;
     const bool split = S > 1;
-    const int p0 = blockIdx.x * BM;               // first weight row (feature) of the tile; tokens are columns 0 .. BN
+    // grid (token block, weight tile, K split): the CTAs next to each other share a weight tile, which the second
+    // one finds in L2
+    const int p0 = blockIdx.y * BM, q0 = blockIdx.x * BN;      // first weight row (feature) and first token of the tile
     const int total_kb = (a.K + BK - 1) / BK;
     const int kb0 = blockIdx.z * a.kb_per_split;
     const int nkb = min(a.kb_per_split, total_kb - kb0);
@@ -436,7 +438,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             }
             pdl_wait();                                    // activations come from the kernel before
             for (int kb = 0; kb < pre; kb++)
-                tma_load_2d(smem0 + kb * STAGE_BYTES + W_BYTES, &tmX, (kb0 + kb) * BK, 0, full0 + 8 * kb);
+                tma_load_2d(smem0 + kb * STAGE_BYTES + W_BYTES, &tmX, (kb0 + kb) * BK, q0, full0 + 8 * kb);
             int s = 0, ph = 1;                             // ring position of K-block `kb`, parity of its empty barrier
             bool ok = true;
             for (int kb = pre; kb < nkb && ok; kb++) {
@@ -444,7 +446,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
                 const uint32_t dst = smem0 + s * STAGE_BYTES, bar = full0 + 8 * s;
                 mbar_expect_tx(bar, STAGE_BYTES);
                 tma_load_2d_hint(dst, &tmW, (kb0 + kb) * BK, p0, bar, stream_once);
-                tma_load_2d(dst + W_BYTES, &tmX, (kb0 + kb) * BK, 0, bar);
+                tma_load_2d(dst + W_BYTES, &tmX, (kb0 + kb) * BK, q0, bar);
                 if (++s == stages) { s = 0; ph ^= 1; }
             }
             // copies still in flight must land before the CTA may exit: the last pass over the ring
@@ -489,7 +491,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         }
         pdl_wait();
         // 1/rms of the token columns of this tile, while the main loop runs
-        for (int c = prow; c < BN; c += 128) inv_s[c] = (a.ss_in && c < a.M) ? inv_rms(a, c) : 1.0f;
+        for (int c = prow; c < BN; c += 128) inv_s[c] = (a.ss_in && q0 + c < a.M) ? inv_rms(a, q0 + c) : 1.0f;
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (split && epi == EPI_ADD_F32) {
             // the residual values this thread adds to after the main loop: columns w and w + 4 of this CTA's share
@@ -498,7 +500,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             for (int j = 0; j < 2; j++)
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    const int cl = w + 4 * j, m = c_begin + cl, nn = p0 + lane + 32 * i;
+                    const int cl = w + 4 * j, m = q0 + c_begin + cl, nn = p0 + lane + 32 * i;
                     res_pre[4 * j + i] = (cl < per && nn < a.N && m < a.M) ? __ldcg((const float *)a.out + (size_t)m * a.ldc + nn) : 0.f;
                 }
         }
@@ -515,7 +517,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             // shared memory as [token][feature], then all 128 threads share the activations
             float *exg = (float *)smem;           // [BN][64]; the stages are idle once tfull has fired
             float *exu = exg + BN * 64;
-            const int ncol = min(BN, a.M);
+            const int ncol = min(BN, a.M - q0);
             if (ok) {
                 float *ex = prow < 64 ? exg : exu;
 #pragma unroll 1
@@ -532,7 +534,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
 #pragma unroll 1
                 for (int c = prow >> 6; c < ncol; c += 2) {         // the halves take alternate tokens
                     const float iv = inv_s[c];
-                    ((bf16 *)a.out)[(size_t)c * a.ldc + f] =
+                    ((bf16 *)a.out)[(size_t)(q0 + c) * a.ldc + f] =
                         __float2bfloat16_rn(silu_mul(exg[c * 64 + fl] * iv, exu[c * 64 + fl] * iv));
                 }
             }
@@ -573,7 +575,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             const float *part = split ? recv : (const float *)smem;
 #pragma unroll 1
             for (int cl = w; cl < per; cl += 4) {
-                const int m = c_begin + cl;
+                const int m = q0 + c_begin + cl;
                 if (m >= a.M) break;                                               // tokens fill the columns from 0
                 float v[4];
 #pragma unroll
@@ -585,7 +587,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
 #pragma unroll
                     for (int z = 0; z < 8; z++) v[i] += pz[z];                     // rank order; absent ranks add 0
                 }
-                const float iv = inv_s[m];
+                const float iv = inv_s[c_begin + cl];
                 float sq = 0.f;
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
@@ -608,7 +610,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
                         if (emit) a.xw_out[(size_t)m * a.N + n] = __float2bfloat16_rn(v[i] * nw_pre[i]);
                     }
                 }
-                if (emit && lane == 0) a.ss_out[(size_t)blockIdx.x * a.M + m] = sq;
+                if (emit && lane == 0) a.ss_out[(size_t)blockIdx.y * a.M + m] = sq;
             }
         }
     }
@@ -858,20 +860,23 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return FG_ERR_BAD_SIZE;
     if (epi == EPI_SILU_MUL && N % 128) return FG_ERR_BAD_SIZE;
-    const bool swap = M <= 64;
+    // Up to 128 rows the weights stream through the decode kernel, in blocks of 64 tokens whose CTAs run side by side
+    // and share each weight tile through L2; beyond that the prefill kernel is faster (measured: 56.6 against 45.5 k tok/s
+    // at 96 rows, 65.8 against 74.0 k at 200).
+    const bool swap = M <= 128;
     const int total_kb = (K + BK - 1) / BK;
     int bn, splits = 1;
     dim3 grid;
     if (swap) {
         bn = M <= 16 ? 16 : M <= 32 ? 32 : 64;
-        int tiles = (N + BM - 1) / BM;
-        // too few tiles to fill 148 SMs: a cluster of 2, 4 or 8 CTAs shares each tile along K
+        int tiles = (N + BM - 1) / BM, blocks = (M + bn - 1) / bn;
+        // too few tiles to fill the SMs: a cluster of 2, 4 or 8 CTAs shares each tile along K
         if (epi != EPI_SILU_MUL) {
-            while (splits < 8 && tiles * splits < sm_count() * 4 / 5 && total_kb >= 4 * splits) splits *= 2;
+            while (splits < 8 && tiles * blocks * splits < sm_count() * 4 / 5 && total_kb >= 4 * splits) splits *= 2;
             if (force_splits == 1 || force_splits == 2 || force_splits == 4 || force_splits == 8)
                 if (force_splits <= total_kb) splits = force_splits;
         }
-        grid = dim3(tiles, 1, 1);
+        grid = dim3(blocks, tiles, 1);
     } else {
         // tile width: rounds of tiles over the persistent CTAs (one an SM) times the width (a 128-wide tile costs a tenth
         // more per column); 192 is there for feature counts like 3072 that quantise badly at 128 and 256
@@ -893,7 +898,7 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
     int esz = (epi == EPI_F32 || epi == EPI_ADD_F32) ? 4 : 2;
     int vec_ok = ((uintptr_t)out % 16 == 0) && ((size_t)ldc * esz % 16 == 0);
     if (norm_w && (epi != EPI_ADD_F32 || !xw_out || !ss_out)) return FG_ERR_BAD_DTYPE;
-    if (ss_tiles_out) *ss_tiles_out = swap ? (int)grid.x : (int)grid.y;
+    if (ss_tiles_out) *ss_tiles_out = (int)grid.y;
     GemmArgs a{out, M, N, K, ldc, kb_per_split, vec_ok, ss_in, ss_tiles, ss_size, ss_eps, norm_w, (bf16 *)xw_out, ss_out, epi, 0};
     switch (epi) {
     case EPI_BF16: return dispatch<EPI_BF16>(swap, bn, tmP, tmQ, a, grid, stream);
