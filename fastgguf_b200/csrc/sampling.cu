@@ -333,10 +333,21 @@ topk_stage1_kernel(const float *__restrict__ logits, int V, int ldl, int k, int 
         for (int i = tid; i < n; i += blockDim.x)
             if ((keys[i] & mask) == prefix) atomicAdd(&hist[(keys[i] >> shift) & 255], 1);
         __syncthreads();
-        if (tid == 0) {
-            int cum = 0, bin = 255;
-            for (; bin > 0; bin--) { if (cum + hist[bin] >= need) break; cum += hist[bin]; }
-            misc[0] = bin; misc[1] = need - cum;
+        // the bin that holds the `need`-th largest matching key, by a suffix sum over the 256 bins with 256 threads
+        // (thread t takes bin 255 - t): the one whose running count reaches `need`.  One thread walking the bins took
+        // as long as the counting itself.
+        {
+            const int x = hist[255 - tid], lane = tid & 31, w = tid >> 5;
+            int incl = x;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { int y = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += y; }
+            if (lane == 31) wsum[w] = incl;
+            if (tid == 0) { misc[0] = 0; misc[1] = need; }       // never kept: the matching keys are at least `need`
+            __syncthreads();
+            int before = 0;
+            for (int j = 0; j < w; j++) before += wsum[j];
+            incl += before;
+            if (incl >= need && incl - x < need) { misc[0] = 255 - tid; misc[1] = need - (incl - x); }
         }
         __syncthreads();
         prefix |= (uint32_t)misc[0] << shift;
