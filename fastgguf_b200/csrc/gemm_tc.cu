@@ -551,6 +551,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
                 for (int j = 0; j < 16; j++) {
                     const int c = c0 + j, r = c >> per_log, cl = c & (per - 1);
                     const float val = have ? v[j] : 0.f;
+                    if (q0 + c >= a.M) continue;                    // a column without a token is never read
                     if (split) st_dsmem_f32(smem_u32(&recv[((int)blockIdx.z * per + cl) * BM + prow]), r, val);
                     else ((float *)smem)[c * BM + prow] = val;
                 }
