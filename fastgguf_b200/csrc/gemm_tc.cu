@@ -53,15 +53,21 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 // bounded wait: false when the limit ran out
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// The clock is read only once the first try has failed: the waiting thread is often the single lane that issues
+// the MMAs or the copies, where every instruction of the loop is on the critical path.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    long long t0 = clock64();
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
     for (;;) {
-        uint32_t ok;
-        asm volatile("{\n\t.reg .pred p;\n\t"
-                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                     "selp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
+        if (mbar_try(bar, parity)) return true;
         if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
     }
 }
@@ -460,12 +466,16 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = make_idesc(BM, BN);
+            // One lane issues everything, one instruction after the other: the loop is kept lean.  The descriptor of
+            // a stage is the first stage's plus the stage's offset (the address field counts 16-byte units and
+            // shared memory is far below its 14 bits).
+            const uint64_t wdesc0 = make_smem_desc(smem0), xdesc0 = make_smem_desc(smem0 + W_BYTES);
             int s = 0, ph = 0;
             for (int kb = 0; kb < nkb; kb++) {
                 if (!mbar_wait(full0 + 8 * s, ph)) { raise_error(2); break; }
                 tc_fence_after();
-                const uint32_t sa = smem0 + s * STAGE_BYTES;
-                const uint64_t wdesc = make_smem_desc(sa), xdesc = make_smem_desc(sa + W_BYTES);
+                const uint64_t soff = (uint64_t)(s * (STAGE_BYTES >> 4));
+                const uint64_t wdesc = wdesc0 + soff, xdesc = xdesc0 + soff;
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; k++) {
                     const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);     // advance inside the swizzle row
