@@ -143,6 +143,7 @@ def main():
 
     import numpy as np
     import torch
+    from fastgguf_b200 import ops
     from fastgguf_b200.engine.api import Engine
     from fastgguf_b200.engine.runner import DecodeSession
     from fastgguf_b200.registry import config_from_dict
@@ -189,6 +190,7 @@ def main():
                 session.advance(live)
             t1.record()
             torch.cuda.synchronize()
+            ops.raise_on_device_error("timed decode")      # a number from a broken pipeline is no number
             ms = t0.elapsed_time(t1) / steps
             mean_ctx = ctx0 + batch * (steps + 1) / 2.0
         finally:
@@ -257,6 +259,7 @@ def main():
             engine.step([StepEntry(slot, toks, [PREFILL_TOKENS - 1])])
             t1.record()
             torch.cuda.synchronize()
+            ops.raise_on_device_error("timed prefill")
             engine.release(slot)
             if i >= 3:
                 times.append(t0.elapsed_time(t1))

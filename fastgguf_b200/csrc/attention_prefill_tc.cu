@@ -32,6 +32,7 @@
 #define ROWS 128
 #define ATT_THREADS 192
 #define WAIT_LIMIT_CYCLES 2000000000ll
+#define WAIT_SHORT_CYCLES 1000000ll
 #define LOG2E 1.4426950408889634f
 
 __device__ int g_attn_error = 0;
@@ -55,7 +56,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
                      "selp.u32 %0, 1, 0, p;\n\t}"
                      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+        const long long waited = clock64() - t0;
+        if (waited > WAIT_LIMIT_CYCLES) return false;
+        // once a wait has run out somewhere, every later wait gives up after a short time: a broken pipeline
+        // costs milliseconds for the kernels that follow, not a second per wait
+        if (waited > WAIT_SHORT_CYCLES && *(volatile int *)&g_attn_error != 0) return false;
     }
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
@@ -198,57 +203,69 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            int k_issued = 0, v_issued = 0;
-            for (int j = 0; j < n_iter; j++) {
-                int y[NPG];
-                for (int h = 0; h < NPG; h++)
-                    y[h] = (bt[min(p_begin + NPG * j + h, p_end - 1)] * KV + kvh) * PAGE;   // a page past the end is masked anyway
-                if (!mbar_wait(k_empty, (j & 1) ^ 1)) { raise_error(1); break; }
+        // the whole warp walks the pages and waits; one elected lane issues the copies
+        int k_issued = 0, v_issued = 0;
+        for (int j = 0; j < n_iter; j++) {
+            int y[NPG];
+            for (int h = 0; h < NPG; h++)
+                y[h] = (bt[min(p_begin + NPG * j + h, p_end - 1)] * KV + kvh) * PAGE;   // a page past the end is masked anyway
+            if (!__all_sync(0xffffffffu, mbar_wait(k_empty, (j & 1) ^ 1))) { raise_error(1); break; }
+            if (elect_one()) {
                 mbar_expect_tx(k_full, KV_TILE);
                 for (int h = 0; h < NPG; h++)
                     for (int c = 0; c < CH; c++) tma_load_2d(kt + c * (KEYS * 128) + h * (PAGE * 128), &tmK, c * 64, y[h], k_full);
-                k_issued = j + 1;
-                if (!mbar_wait(v_empty, (j & 1) ^ 1)) { raise_error(1); break; }
+            }
+            __syncwarp();
+            k_issued = j + 1;
+            if (!__all_sync(0xffffffffu, mbar_wait(v_empty, (j & 1) ^ 1))) { raise_error(1); break; }
+            if (elect_one()) {
                 mbar_expect_tx(v_full, KV_TILE);
                 for (int h = 0; h < NPG; h++)
                     for (int c = 0; c < CH; c++) tma_load_2d(vt + c * (KEYS * 128) + h * (PAGE * 128), &tmV, c * 64, y[h], v_full);
-                v_issued = j + 1;
             }
-            if (k_issued) mbar_wait(k_full, (k_issued - 1) & 1);      // copies in flight land before the CTA exits
-            if (v_issued) mbar_wait(v_full, (v_issued - 1) & 1);
+            __syncwarp();
+            v_issued = j + 1;
         }
+        if (k_issued) mbar_wait(k_full, (k_issued - 1) & 1);      // copies in flight land before the CTA exits
+        if (v_issued) mbar_wait(v_full, (v_issued - 1) & 1);
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0 && n_iter > 0) {
+        // the whole warp walks the iterations and waits; one elected lane issues
+        if (n_iter > 0) {
             const uint32_t idesc_s = make_idesc(ROWS, KEYS, 0), idesc_o = make_idesc(ROWS, HD, 1);
             auto issue_s = [&](int j) {
-                if (!mbar_wait(k_full, j & 1)) { raise_error(2); return false; }
+                if (!__all_sync(0xffffffffu, mbar_wait(k_full, j & 1))) { raise_error(2); return false; }
                 tc_fence_after();
+                if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ks++) {
-                    // 64-wide chunk ks / 4 of the head dimension (ROWS rows of Q, KEYS rows of K), 32 B inside its swizzle row
-                    const uint32_t qoff = (ks >> 2) * (ROWS * 128) + (ks & 3) * 32, koff = (ks >> 2) * (KEYS * 128) + (ks & 3) * 32;
-                    tc_mma_bf16(tmem_base, desc_k_major(qs + qoff), desc_k_major(kt + koff), idesc_s, ks != 0);
+                    for (int ks = 0; ks < HD / 16; ks++) {
+                        // 64-wide chunk ks / 4 of the head dimension (ROWS rows of Q, KEYS rows of K), 32 B inside its swizzle row
+                        const uint32_t qoff = (ks >> 2) * (ROWS * 128) + (ks & 3) * 32, koff = (ks >> 2) * (KEYS * 128) + (ks & 3) * 32;
+                        tc_mma_bf16(tmem_base, desc_k_major(qs + qoff), desc_k_major(kt + koff), idesc_s, ks != 0);
+                    }
+                    tc_commit(s_full);
+                    tc_commit(k_empty);              // the K tile is free once S is complete
                 }
-                tc_commit(s_full);
-                tc_commit(k_empty);                  // the K tile is free once S is complete
+                __syncwarp();
                 return true;
             };
             bool ok = issue_s(0);
             for (int j = 0; j < n_iter && ok; j++) {
-                if (!mbar_wait(p_full, j & 1)) { raise_error(3); break; }
-                if (!mbar_wait(v_full, j & 1)) { raise_error(2); break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(p_full, j & 1))) { raise_error(3); break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(v_full, j & 1))) { raise_error(2); break; }
                 tc_fence_after();
+                if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < KEYS / 16; ks++) {
-                    // A = P: 64-key chunk ks / 4, 32 B inside its swizzle row; B = V: 16 keys = two 8-key groups
-                    uint64_t adesc = desc_k_major(ps + (ks >> 2) * (ROWS * 128) + (ks & 3) * 32);
-                    uint64_t bdesc = desc_mn_major(vt + ks * 2048, KEYS * 128);
-                    tc_mma_bf16(tmem_base + KEYS, adesc, bdesc, idesc_o, (j | ks) != 0);     // O accumulates over the iterations
+                    for (int ks = 0; ks < KEYS / 16; ks++) {
+                        // A = P: 64-key chunk ks / 4, 32 B inside its swizzle row; B = V: 16 keys = two 8-key groups
+                        uint64_t adesc = desc_k_major(ps + (ks >> 2) * (ROWS * 128) + (ks & 3) * 32);
+                        uint64_t bdesc = desc_mn_major(vt + ks * 2048, KEYS * 128);
+                        tc_mma_bf16(tmem_base + KEYS, adesc, bdesc, idesc_o, (j | ks) != 0);     // O accumulates over the iterations
+                    }
+                    tc_commit(o_full);
+                    tc_commit(v_empty);
                 }
-                tc_commit(o_full);
-                tc_commit(v_empty);
+                __syncwarp();
                 if (j + 1 < n_iter) ok = issue_s(j + 1);
             }
         }

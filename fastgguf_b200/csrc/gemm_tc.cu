@@ -38,6 +38,7 @@
 #define UMMA_K 16
 #define GEMM_THREADS 192
 #define WAIT_LIMIT_CYCLES 2000000000ll
+#define WAIT_SHORT_CYCLES 1000000ll
 
 enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_ADD_F32 = 2, EPI_SILU_MUL = 3 };
 
@@ -68,7 +69,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     const long long t0 = clock64();
     for (;;) {
         if (mbar_try(bar, parity)) return true;
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+        const long long waited = clock64() - t0;
+        if (waited > WAIT_LIMIT_CYCLES) return false;
+        // once a wait has run out somewhere, every later wait gives up after a short time: a broken pipeline
+        // costs milliseconds for the kernels that follow, not a second per wait
+        if (waited > WAIT_SHORT_CYCLES && *(volatile int *)&g_gemm_error != 0) return false;
     }
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
@@ -435,57 +440,68 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            const int pre = min(stages, nkb);
-            const uint64_t stream_once = l2_evict_first_policy();
-            for (int kb = 0; kb < pre; kb++) {             // weights of the first stages: no dependency
+        // The whole warp walks the ring and waits; one elected lane issues the copies.
+        const int pre = min(stages, nkb);
+        const uint64_t stream_once = l2_evict_first_policy();
+        if (elect_one()) {
+            for (int kb = 0; kb < pre; kb++) {                 // weights of the first stages: no dependency
                 mbar_expect_tx(full0 + 8 * kb, STAGE_BYTES);
                 tma_load_2d_hint(smem0 + kb * STAGE_BYTES, &tmW, (kb0 + kb) * BK, p0, full0 + 8 * kb, stream_once);
             }
-            pdl_wait();                                    // activations come from the kernel before
+        }
+        __syncwarp();
+        pdl_wait();                                            // activations come from the kernel before
+        if (elect_one()) {
             for (int kb = 0; kb < pre; kb++)
                 tma_load_2d(smem0 + kb * STAGE_BYTES + W_BYTES, &tmX, (kb0 + kb) * BK, q0, full0 + 8 * kb);
-            int s = 0, ph = 1;                             // ring position of K-block `kb`, parity of its empty barrier
-            bool ok = true;
-            for (int kb = pre; kb < nkb && ok; kb++) {
-                if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { raise_error(1); ok = false; break; }
+        }
+        __syncwarp();
+        int s = 0, ph = 1;                                     // ring position of K-block `kb`, parity of its empty barrier
+        bool ok = true;
+        for (int kb = pre; kb < nkb; kb++) {
+            ok = __all_sync(0xffffffffu, mbar_wait(empty0 + 8 * s, ph ^ 1));
+            if (!ok) { raise_error(1); break; }
+            if (elect_one()) {
                 const uint32_t dst = smem0 + s * STAGE_BYTES, bar = full0 + 8 * s;
                 mbar_expect_tx(bar, STAGE_BYTES);
                 tma_load_2d_hint(dst, &tmW, (kb0 + kb) * BK, p0, bar, stream_once);
                 tma_load_2d(dst + W_BYTES, &tmX, (kb0 + kb) * BK, q0, bar);
-                if (++s == stages) { s = 0; ph ^= 1; }
             }
-            // copies still in flight must land before the CTA may exit: the last pass over the ring
-            if (!ok || nkb <= stages) { for (int j = 0; j < min(stages, nkb); j++) mbar_wait(full0 + 8 * j, 0); }
-            else {
-                // K-block kb sits in stage kb % stages with parity (kb / stages) & 1; wait for the last `stages` of them
-                for (int kb = nkb - stages; kb < nkb; kb++) mbar_wait(full0 + 8 * (kb % stages), (kb / stages) & 1);
-            }
+            __syncwarp();
+            if (++s == stages) { s = 0; ph ^= 1; }
+        }
+        // copies still in flight must land before the CTA may exit: the last pass over the ring
+        if (!ok || nkb <= stages) { for (int j = 0; j < min(stages, nkb); j++) mbar_wait(full0 + 8 * j, 0); }
+        else {
+            // K-block kb sits in stage kb % stages with parity (kb / stages) & 1; wait for the last `stages` of them
+            for (int kb = nkb - stages; kb < nkb; kb++) mbar_wait(full0 + 8 * (kb % stages), (kb / stages) & 1);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc(BM, BN);
-            // One lane issues everything, one instruction after the other: the loop is kept lean.  The descriptor of
-            // a stage is the first stage's plus the stage's offset (the address field counts 16-byte units and
-            // shared memory is far below its 14 bits).
-            const uint64_t wdesc0 = make_smem_desc(smem0), xdesc0 = make_smem_desc(smem0 + W_BYTES);
-            int s = 0, ph = 0;
-            for (int kb = 0; kb < nkb; kb++) {
-                if (!mbar_wait(full0 + 8 * s, ph)) { raise_error(2); break; }
-                tc_fence_after();
-                const uint64_t soff = (uint64_t)(s * (STAGE_BYTES >> 4));
-                const uint64_t wdesc = wdesc0 + soff, xdesc = xdesc0 + soff;
+        // The whole warp walks the ring and waits; one elected lane issues.  The descriptor of a stage is the
+        // first stage's plus the stage's offset (the address field counts 16-byte units and shared memory is
+        // far below its 14 bits).
+        const uint32_t idesc = make_idesc(BM, BN);
+        const uint64_t wdesc0 = make_smem_desc(smem0), xdesc0 = make_smem_desc(smem0 + W_BYTES);
+        int s = 0, ph = 0;
+        for (int kb = 0; kb < nkb; kb++) {
+            if (!__all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, ph))) { raise_error(2); break; }
+            tc_fence_after();
+            const uint64_t soff = (uint64_t)(s * (STAGE_BYTES >> 4));
+            const uint64_t wdesc = wdesc0 + soff, xdesc = xdesc0 + soff;
+            if (elect_one()) {
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; k++) {
                     const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);     // advance inside the swizzle row
                     tc_mma_bf16(tmem_base, wdesc + koff, xdesc + koff, idesc, (kb | k) != 0);
                 }
                 tc_commit(empty0 + 8 * s);        // arrives when these MMAs have read the stage
-                if (++s == stages) { s = 0; ph ^= 1; }
             }
-            tc_commit(tfull);                     // arrives when every MMA above is complete
+            __syncwarp();
+            if (++s == stages) { s = 0; ph ^= 1; }
         }
+        if (elect_one()) tc_commit(tfull);        // arrives when every MMA above is complete
+        __syncwarp();
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
         const int lg = warp & 3;                  // the TMEM lane group this warp may read
@@ -678,51 +694,59 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_con
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            pdl_wait();
-            int it = 0, issued = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                const int p0 = (tile % n_pt) * BM, q0 = (tile / n_pt) * BN;
-                for (int kb = 0; kb < nkb; kb++, it++) {
-                    int s = it % STAGES;
-                    if (!mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) { raise_error(1); ok = false; break; }
-                    uint32_t dst = smem0 + s * STAGE_BYTES, bar = full0 + 8 * s;
+        // the whole warp walks the tiles and the ring and waits; one elected lane issues the copies
+        pdl_wait();
+        int s = 0, ph = 0, issued = 0;                 // ring position, pass over the ring (parity), stages filled so far
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            const int p0 = (tile % n_pt) * BM, q0 = (tile / n_pt) * BN;
+            for (int kb = 0; kb < nkb; kb++) {
+                ok = __all_sync(0xffffffffu, mbar_wait(empty0 + 8 * s, ph ^ 1));
+                if (!ok) { raise_error(1); break; }
+                if (elect_one()) {
+                    const uint32_t dst = smem0 + s * STAGE_BYTES, bar = full0 + 8 * s;
                     mbar_expect_tx(bar, STAGE_BYTES);
                     tma_load_2d(dst, &tmP, kb * BK, p0, bar);
                     tma_load_2d(dst + P_BYTES, &tmQ, kb * BK, q0, bar);
-                    issued = it + 1;
                 }
+                __syncwarp();
+                issued++;
+                if (++s == STAGES) { s = 0; ph ^= 1; }
             }
-            for (int j = max(0, issued - STAGES); j < issued; j++)      // copies in flight land before the CTA exits
-                mbar_wait(full0 + 8 * (j % STAGES), (j / STAGES) & 1);
         }
+        for (int j = max(0, issued - STAGES); j < issued; j++)      // copies in flight land before the CTA exits
+            mbar_wait(full0 + 8 * (j % STAGES), (j / STAGES) & 1);
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc(BM, BN);
-            int it = 0, i = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, i++) {
-                const int acc = i & 1;
-                // the epilogue must have emptied this accumulator (its use before the last one)
-                if (!mbar_wait(tempty0 + 8 * acc, ((i >> 1) & 1) ^ 1)) { raise_error(4); break; }
+        // the whole warp walks the tiles and the ring and waits; one elected lane issues
+        const uint32_t idesc = make_idesc(BM, BN);
+        const uint64_t pdesc0 = make_smem_desc(smem0), qdesc0 = make_smem_desc(smem0 + P_BYTES);
+        int s = 0, ph = 0, i = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, i++) {
+            const int acc = i & 1;
+            // the epilogue must have emptied this accumulator (its use before the last one)
+            if (!__all_sync(0xffffffffu, mbar_wait(tempty0 + 8 * acc, ((i >> 1) & 1) ^ 1))) { raise_error(4); break; }
+            tc_fence_after();
+            for (int kb = 0; kb < nkb; kb++) {
+                ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, ph));
+                if (!ok) { raise_error(2); break; }
                 tc_fence_after();
-                for (int kb = 0; kb < nkb; kb++, it++) {
-                    int s = it % STAGES;
-                    if (!mbar_wait(full0 + 8 * s, (it / STAGES) & 1)) { raise_error(2); ok = false; break; }
-                    tc_fence_after();
-                    uint32_t sa = smem0 + s * STAGE_BYTES;
-                    uint64_t pdesc = make_smem_desc(sa), qdesc = make_smem_desc(sa + P_BYTES);
+                const uint64_t soff = (uint64_t)(s * (STAGE_BYTES >> 4));      // the address field counts 16-byte units
+                const uint64_t pdesc = pdesc0 + soff, qdesc = qdesc0 + soff;
+                if (elect_one()) {
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; k++) {
-                        uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
+                        const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
                         tc_mma_bf16(tmem_base + acc * BN, pdesc + koff, qdesc + koff, idesc, (kb | k) != 0);
                     }
                     tc_commit(empty0 + 8 * s);
                 }
-                tc_commit(tfull0 + 8 * acc);
+                __syncwarp();
+                if (++s == STAGES) { s = 0; ph ^= 1; }
             }
+            if (elect_one()) tc_commit(tfull0 + 8 * acc);      // also after an error: the epilogue is not left waiting
+            __syncwarp();
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)

@@ -128,7 +128,9 @@ class EngineBackend:
         rows = torch.tensor(list(slots), dtype=torch.int32, device=self.engine.device)
         toks = self.sampler.sample(logits, rows)
         self.stats["d2h_bytes"] += 4 * len(slots)
-        return toks.cpu().tolist()
+        host = toks.cpu().tolist()
+        ops.raise_on_device_error("decode step")
+        return host
 
     # ------------------------------------------------------------------ batches
     def run_batch(self, prompts, first_index: int, max_tokens: int, stop_ids: Sequence[int]) -> List[Completion]:
@@ -184,6 +186,7 @@ class EngineBackend:
                 host, ev = session.advance(live)
                 pending.append((live, host, ev))
             settle(block=True)
+            ops.raise_on_device_error("batch")
         finally:
             session.close()
         return done
@@ -215,6 +218,7 @@ class DecodeSession:
             g.active[:n] = 1
             self.widths = [0] * n                      # page-table entries of each row already uploaded
             self.first_tokens = first.cpu().tolist()
+            ops.raise_on_device_error("prompt step")
             backend.stats["d2h_bytes"] += 4 * n
         except BaseException:
             self.close()

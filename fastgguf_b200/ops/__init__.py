@@ -6,10 +6,10 @@ from typing import Optional
 
 import torch
 
-from .lib import KernelError, check, dtype_code, lib, ptr, require_cuda, stream
+from .lib import KernelError, check, dtype_code, lib, ptr, raise_on_device_error, require_cuda, stream
 
 __all__ = [
-    "KernelError", "embed_gather", "embed_gather_norm", "rmsnorm", "rope_append", "silu_mul", "gemm_generic",
+    "KernelError", "raise_on_device_error", "embed_gather", "embed_gather_norm", "rmsnorm", "rope_append", "silu_mul", "gemm_generic",
     "attention_generic", "attention", "rope_attention", "sample", "argmax", "decode_advance",
 ]
 

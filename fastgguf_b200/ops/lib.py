@@ -105,6 +105,25 @@ def register_signatures(module: str, signatures: dict) -> None:
     _SIGNATURES.setdefault(module, {}).update(signatures)
 
 
+#: (library, reader of its device-side error flag): a bounded wait that ran out leaves wrong output behind
+_ERROR_FLAGS = (("tc", "fg_gemm_tc_error"), ("attn", "fg_attention_prefill_tc_error"))
+
+
+def raise_on_device_error(where: str = "") -> None:
+    """Raise if a bounded wait inside a kernel ran out since the last call (the flags are cleared).
+
+    Reads only the libraries that were loaded; the read synchronises, so callers use it where they
+    wait for the device anyway (after a prompt step, at the end of a batch, before logits are written)."""
+    for module, reader in _ERROR_FLAGS:
+        l = _libs.get(module)
+        if l is None:
+            continue
+        code = int(getattr(l, reader)())
+        if code != 0:
+            raise KernelError(f"{where or 'kernel'}: a device-side wait ran out in library '{module}' "
+                              f"(code {code >> 8}, role {code & 255}); its output is not valid")
+
+
 def lib(module: str = "core") -> ctypes.CDLL:
     l = _libs.get(module)
     if l is None:
