@@ -109,3 +109,27 @@ def test_request_seeds_and_sampling_params():
     with pytest.raises(ValueError):
         SamplingParams(top_k=5000).validate()
     assert SamplingParams(temp=0).greedy and not SamplingParams().penalizes and SamplingParams(repeat_penalty=1.2).penalizes
+
+
+def test_device_error_flags_are_raised_and_only_loaded_libraries_are_asked(monkeypatch):
+    """A bounded wait that ran out inside a kernel leaves a flag behind; the host turns it into an exception."""
+    import importlib
+    oplib = importlib.import_module("fastgguf_b200.ops.lib")
+
+    class FakeLib:
+        def __init__(self, code):
+            self.code, self.reads = code, 0
+
+        def fg_gemm_tc_error(self):
+            self.reads += 1
+            code, self.code = self.code, 0           # reading clears the flag, as the library does
+            return code
+
+    monkeypatch.setattr(oplib, "_libs", {})
+    oplib.raise_on_device_error("nothing loaded")     # no library loaded: nothing is built or asked
+    fake = FakeLib((10003 << 8) | 2)
+    monkeypatch.setattr(oplib, "_libs", {"tc": fake})
+    with pytest.raises(oplib.KernelError, match="role 2"):
+        oplib.raise_on_device_error("prompt step")
+    oplib.raise_on_device_error("prompt step")        # cleared by the read
+    assert fake.reads == 2
