@@ -10,9 +10,10 @@
 // walks the sequence's pages, two at a time (128 keys) at head size 64 and one at a time at head size 128, so
 // that two CTAs fit on an SM at either size and the softmax of one runs under the MMAs of the other:
 //
-//   warp 0 (one lane)  TMA: the K tile and the V tile of an iteration (128B swizzle); the next K tile is
-//                      fetched as soon as S has consumed the current one, the next V tile after P V
-//   warp 1 (one lane)  MMA: S = Q K^T (128 x KEYS x HD), then, once P is in shared memory,
+//   warp 0             TMA (one elected lane issues): the K tile and the V tile of an iteration (128B
+//                      swizzle); the next K tile is fetched as soon as S has consumed the current one,
+//                      the next V tile after P V
+//   warp 1             MMA (one elected lane issues): S = Q K^T (128 x KEYS x HD), then, once P is in shared memory,
 //                      O += P V (128 x HD x KEYS) into the same tensor-memory accumulator, iteration after
 //                      iteration; V is the MN-major operand (its rows are keys)
 //   warps 2-5          thread = row: read S from tensor memory, scale, mask, running max and sum in

@@ -14,10 +14,11 @@
 //   gemm_tc_prefill_kernel: 128 token rows x BN = 128/192/256 weight rows per tile, persistent CTAs, two
 //     accumulators in tensor memory.
 //
-//   warp 0      TMA producer (one lane): K-blocks of 64 into a ring of smem stages, 128B swizzle.
+//   warp 0      TMA producer (the warp walks the ring, one elected lane issues): K-blocks of 64 into a ring
+//               of smem stages, 128B swizzle.
 //               The weight tiles of the first stages are fetched BEFORE the wait on the preceding
 //               kernel (weights are never written), so weight traffic overlaps that kernel's tail.
-//   warp 1      MMA issuer (one lane): tcgen05.mma 128 x BN x 16; its commit frees the stage.
+//   warp 1      MMA issuer (the same way): tcgen05.mma 128 x BN x 16; its commit frees the stage.
 //   warps 2-5   epilogue: tcgen05.ld of the f32 tile, then one of
 //               store bf16 | store f32 | add into f32 (residual) | silu(gate) * up -> bf16
 //
@@ -62,8 +63,8 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// The clock is read only once the first try has failed: the waiting thread is often the single lane that issues
-// the MMAs or the copies, where every instruction of the loop is on the critical path.
+// The clock is read only once the first try has failed: the waiting warp is often the one that issues the MMAs
+// or the copies, where every instruction of the loop is on the critical path.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
