@@ -13,6 +13,8 @@
 //     no scratch in global memory, no remote loads.
 //   gemm_tc_prefill_kernel: 128 token rows x BN = 128/192/256 weight rows per tile, persistent CTAs, two
 //     accumulators in tensor memory.
+//   gemm_tc_prefill_pair_kernel: the same for 256 token rows x 256 weight rows on a pair of CTAs
+//     (tcgen05.mma.cta_group::2): each SM loads half of the weight rows of a tile.
 //
 //   warp 0      TMA producer (the warp walks the ring, one elected lane issues): K-blocks of 64 into a ring
 //               of smem stages, 128B swizzle.
@@ -776,6 +778,170 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_con
     }
 }
 
+// ---------------------------------------------------------------------------- prefill: pairs of CTAs on 256-row tiles
+// Two CTAs of a cluster (a pair of SMs) share a tile of 256 token rows x BN weight rows: each loads its own 128
+// token rows and HALF of the weight rows, and the pair's leader issues tcgen05.mma.cta_group::2, which reads both
+// CTAs' shared memory and writes each CTA's 128 accumulator rows into that CTA's tensor memory.  Per K-block an
+// SM then receives 16 + BN/4 KB instead of 16 + BN/2 KB for the same MMA time: the main loop of the 128-row kernel
+// is bound by the L2-to-SM path, not by the tensor pipe.
+//   every copy of both CTAs completes on the LEADER's full barrier (cp.async.bulk.tensor .cta_group::2); the
+//   leader's commit frees the stage in both CTAs and hands the accumulator to both epilogues
+//   (tcgen05.commit .multicast::cluster); both epilogues release the accumulator on the leader's barrier.
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local_addr, int rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    return remote;
+}
+// a copy whose completion is counted on a barrier given by its cluster address (the pair leader's)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t cluster_bar) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate) {
+    const uint32_t acc = accumulate ? 1u : 0u, z = 0u;
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc), "r"(z) : "memory");
+}
+// arrives on the barrier at this address in BOTH CTAs of the pair once the MMAs issued so far are complete
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(both) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_prefill_pair_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, GemmArgs a,
+                            int n_pt, int n_tiles) {
+    constexpr int P_BYTES = BM * BK * 2, Q_BYTES = (BN / 2) * BK * 2;      // this CTA's share of a stage
+    constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
+    constexpr int TMEM_COLS = BN <= 128 ? 256 : 512;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+    __shared__ uint32_t tmem_base_s;
+
+    const int warp = warp_index(), lane = threadIdx.x & 31;
+    const int rank = (int)(blockIdx.x & 1);            // 0: the pair's leader (issues the MMAs), 1: its peer
+    const int pair = (int)(blockIdx.x >> 1), n_pairs = (int)(gridDim.x >> 1);
+    const int nkb = (a.K + BK - 1) / BK;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+    const uint32_t tfull0 = smem_u32(&bars[2 * STAGES]), tempty0 = smem_u32(&bars[2 * STAGES + 2]);
+    const uint32_t smem0 = smem_u32(smem);
+    const uint32_t lead_full0 = mapa_u32(full0, 0), lead_tempty0 = mapa_u32(tempty0, 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int i = 0; i < 2; i++) { mbar_init(tfull0 + 8 * i, 1); mbar_init(tempty0 + 8 * i, 8); }   // 4 epilogue warps x 2 CTAs
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();                                    // the partner's barriers exist before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+    pdl_launch_dependents();
+    if (threadIdx.x == 32) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmP) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmQ) : "memory");
+    }
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (both CTAs)
+        pdl_wait();
+        int s = 0, ph = 0;
+        bool ok = true;
+        for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+            const int p0 = (tile % n_pt) * (2 * BM) + rank * BM, q0 = (tile / n_pt) * BN + rank * (BN / 2);
+            for (int kb = 0; kb < nkb; kb++) {
+                ok = __all_sync(0xffffffffu, mbar_wait(empty0 + 8 * s, ph ^ 1));
+                if (!ok) { raise_error(1); break; }
+                if (elect_one()) {
+                    const uint32_t dst = smem0 + s * STAGE_BYTES, bar = lead_full0 + 8 * s;
+                    if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);     // both CTAs' copies of the stage
+                    tma_load_2d_pair(dst, &tmP, kb * BK, p0, bar);
+                    tma_load_2d_pair(dst + P_BYTES, &tmQ, kb * BK, q0, bar);
+                }
+                __syncwarp();
+                if (++s == STAGES) { s = 0; ph ^= 1; }
+            }
+        }
+        // the copies of both CTAs have landed once the leader has seen every stage full; the cluster barrier at the
+        // end of the kernel comes after that
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (the leader only)
+        if (rank == 0) {
+            const uint32_t idesc = make_idesc(2 * BM, BN);
+            const uint64_t pdesc0 = make_smem_desc(smem0), qdesc0 = make_smem_desc(smem0 + P_BYTES);
+            int s = 0, ph = 0, i = 0;
+            bool ok = true;
+            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, i++) {
+                const int acc = i & 1;
+                if (!__all_sync(0xffffffffu, mbar_wait(tempty0 + 8 * acc, ((i >> 1) & 1) ^ 1))) { raise_error(4); break; }
+                tc_fence_after();
+                for (int kb = 0; kb < nkb; kb++) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, ph));
+                    if (!ok) { raise_error(2); break; }
+                    tc_fence_after();
+                    const uint64_t soff = (uint64_t)(s * (STAGE_BYTES >> 4));
+                    const uint64_t pdesc = pdesc0 + soff, qdesc = qdesc0 + soff;
+                    if (elect_one()) {
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; k++) {
+                            const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
+                            tc_mma_bf16_pair(tmem_base + acc * BN, pdesc + koff, qdesc + koff, idesc, (kb | k) != 0);
+                        }
+                        tc_commit_pair(empty0 + 8 * s);              // frees the stage in both CTAs
+                    }
+                    __syncwarp();
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+                if (elect_one()) tc_commit_pair(tfull0 + 8 * acc);   // both epilogues; also after an error
+                __syncwarp();
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs): this CTA's 128 rows
+        pdl_wait();
+        const int lg = warp & 3, prow = lg * 32 + lane;
+        int i = 0;
+        for (int tile = pair; tile < n_tiles; tile += n_pairs, i++) {
+            const int acc = i & 1;
+            const int pt = tile % n_pt, qt = tile / n_pt;
+            const int p0 = pt * (2 * BM) + rank * BM;
+            if (!mbar_wait(tfull0 + 8 * acc, (i >> 1) & 1)) { raise_error(3); break; }
+            tc_fence_after();
+            const uint32_t trow = tmem_base + ((uint32_t)(lg * 32) << 16) + acc * BN;
+            if (EPI == EPI_ADD_F32 && a.vec_ok && (a.N & 31) == 0)
+                epilogue_add_coalesced<BN>(a, trow, p0, qt * BN, qt, lg, lane, smem + STAGES * STAGE_BYTES + lg * EPI_STAGE_BYTES);
+            else
+                epilogue_token_major<BN, EPI>(a, trow, p0, qt * BN, qt, prow);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8 * acc);      // the leader's barrier counts both CTAs' warps
+        }
+    }
+    // Neither CTA leaves, or frees tensor memory, while the other may still read its shared memory (the leader's
+    // MMAs), wait for its copies (they complete on the leader's barriers) or arrive on its barriers.
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+
 // ---------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -847,6 +1013,38 @@ static int launch_prefill(const CUtensorMap &tmP, const CUtensorMap &tmQ, const 
                      n_pt, n_tiles);
 }
 
+static int sm_count();
+template <int BN, int STAGES, int EPI>
+static int launch_prefill_pair(const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs &a, cudaStream_t stream) {
+    constexpr int smem = STAGES * (BM + BN / 2) * BK * 2 + 1024 + (EPI == EPI_ADD_F32 ? 4 * EPI_STAGE_BYTES : 0);
+    static bool configured = false;
+    static int n_sm = 0;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_prefill_pair_kernel<BN, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        n_sm = sm_count();
+        configured = true;
+    }
+    int n_pt = (a.M + 2 * BM - 1) / (2 * BM), n_tiles = n_pt * ((a.N + BN - 1) / BN);
+    int pairs = n_sm / 2;
+    // the CTAs of a pair are neighbours along x
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (n_tiles < pairs ? n_tiles : pairs), 1, 1); cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (fg_pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 2; attr[n].val.clusterDim.y = 1; attr[n].val.clusterDim.z = 1;
+    n++;
+    cfg.attrs = attr; cfg.numAttrs = n;
+    return (int)cudaLaunchKernelEx(&cfg, gemm_tc_prefill_pair_kernel<BN, STAGES, EPI>, tmP, tmQ, a, n_pt, n_tiles);
+}
+
 template <int EPI>
 static int dispatch(bool swap, int bn, const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs &a, dim3 grid, cudaStream_t st) {
     if (swap) {
@@ -859,6 +1057,7 @@ static int dispatch(bool swap, int bn, const CUtensorMap &tmP, const CUtensorMap
         }
     } else {
         switch (bn) {
+        case -256: return launch_prefill_pair<256, 6, EPI>(tmP, tmQ, a, st);
         case 128: return launch_prefill<128, 6, EPI>(tmP, tmQ, a, st);
         case 192: if (EPI != EPI_SILU_MUL) return launch_prefill<192, 5, EPI == EPI_SILU_MUL ? EPI_BF16 : EPI>(tmP, tmQ, a, st); break;
         case 256: return launch_prefill<256, 4, EPI>(tmP, tmQ, a, st);
@@ -923,13 +1122,25 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
         bn = (N <= 128 || c128 < c256) ? 128 : 256;
         if (epi != EPI_SILU_MUL && N > 128 && c192 < (bn == 128 ? c128 : c256)) bn = 192;
         grid = dim3(pt, (N + bn - 1) / bn, 1);
+        // 256-wide tiles: a pair of CTAs on 256 x 256 (half the weight rows per SM and K-block) where that takes no more
+        // rounds than single CTAs on 128 x 256.  FASTGGUF_PAIR=0 keeps the single-CTA kernel.
+        static int pair_on = -1;
+        if (pair_on < 0) { const char *e = getenv("FASTGGUF_PAIR"); pair_on = !(e && e[0] == '0'); }
+        bool pair = false;
+        if (pair_on && bn == 256 && M > 128 && sms >= 2) {
+            const long long tp = (long long)((M + 255) / 256) * ((N + 255) / 256);
+            const long long rounds_pair = (tp + sms / 2 - 1) / (sms / 2), rounds_one = (t256 + sms - 1) / sms;
+            pair = rounds_pair <= rounds_one;
+        }
+        if (force_splits == -2 && sms >= 2) pair = true;               // tests: the pair kernel at any size
+        if (pair) { bn = -256; grid = dim3((M + 255) / 256, (N + 255) / 256, 1); }
     }
     int kb_per_split = (total_kb + splits - 1) / splits;       // a split may be empty: it adds zeros
     grid.z = splits;
     CUtensorMap tmP, tmQ;
     int e = swap ? make_map(&tmP, W, N, K, ldw, BM) : make_map(&tmP, X, M, K, ldx, BM);
     if (e) return e;
-    e = swap ? make_map(&tmQ, X, M, K, ldx, bn) : make_map(&tmQ, W, N, K, ldw, bn);
+    e = swap ? make_map(&tmQ, X, M, K, ldx, bn) : make_map(&tmQ, W, N, K, ldw, bn < 0 ? 128 : bn);
     if (e) return e;
     int esz = (epi == EPI_F32 || epi == EPI_ADD_F32) ? 4 : 2;
     int vec_ok = ((uintptr_t)out % 16 == 0) && ((size_t)ldc * esz % 16 == 0);
