@@ -28,6 +28,7 @@ CHAT_OPTIONS_HELP = (
     "                  --repeat-penalty 1.0 (1 = off)  --repeat-last-n 64\n"
     "                  --max-tokens 512 (0 = until stop)  --seed N\n"
     "                  --prompt ID,ID,...  (repeat for a batch)  --prompts-file FILE (one prompt a line)\n"
+    "                  --stop-id ID (repeat; added to the model's own stop tokens)\n"
     "                  --dtype bfloat16|float32  --batch N  --ignore-eos  --json\n")
 
 
@@ -38,7 +39,7 @@ class UsageError(Exception):
 def parse_generate_args(argv: List[str]) -> dict:
     """Positional [ctx], then --option value pairs (fastgguf.c:6957-6974)."""
     o = dict(ctx=2048, temp=1.0, top_k=64, top_p=0.95, repeat_penalty=1.0, repeat_last_n=64, max_tokens=512,
-             seed=0, prompts=[], dtype="bfloat16", batch=None, ignore_eos=False, json=False)
+             seed=0, prompts=[], stop_ids=[], dtype="bfloat16", batch=None, ignore_eos=False, json=False)
     flags = {"--ignore-eos": "ignore_eos", "--json": "json"}
     valued = {"--temp": ("temp", float), "--top-k": ("top_k", int), "--top-p": ("top_p", float),
               "--repeat-penalty": ("repeat_penalty", float), "--repeat-last-n": ("repeat_last_n", int),
@@ -68,6 +69,8 @@ def parse_generate_args(argv: List[str]) -> dict:
                 o[key] = typ(v)
             elif a == "--prompt":
                 o["prompts"].append([int(t) for t in v.replace(",", " ").split()])
+            elif a == "--stop-id":
+                o["stop_ids"].append(int(v))
             elif a == "--prompts-file":
                 with open(v) as f:
                     o["prompts"].extend([int(t) for t in line.replace(",", " ").split()] for line in f if line.strip())
@@ -111,7 +114,8 @@ def cmd_generate(model_dir: str, argv: List[str]) -> int:
     t0 = time.time()
     out = engine.generate(o["prompts"], temp=o["temp"], top_k=o["top_k"], top_p=o["top_p"],
                           repeat_penalty=o["repeat_penalty"], repeat_last_n=o["repeat_last_n"],
-                          max_tokens=o["max_tokens"], seed=o["seed"], ignore_eos=o["ignore_eos"], batch_size=batch)
+                          max_tokens=o["max_tokens"], seed=o["seed"], ignore_eos=o["ignore_eos"], batch_size=batch,
+                          stop_ids=(list(engine.spec.stop_token_ids) + o["stop_ids"]) if o["stop_ids"] else None)
     torch.cuda.synchronize()
     dt = time.time() - t0
     n_gen = sum(len(c.tokens) for c in out)

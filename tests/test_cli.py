@@ -34,6 +34,20 @@ def test_inspect_dump_random_and_usage(tmp_path):
     assert run("frobnicate").returncode == 1
 
 
+def test_generate_options_have_the_reference_names_and_defaults():
+    from fastgguf_b200.cli import UsageError, parse_generate_args
+    o = parse_generate_args([])
+    assert (o["ctx"], o["temp"], o["top_k"], o["top_p"], o["repeat_penalty"], o["repeat_last_n"], o["max_tokens"]) == \
+        (2048, 1.0, 64, 0.95, 1.0, 64, 512)
+    o = parse_generate_args(["32", "--temp", "0", "--top-k", "0", "--seed", "9", "--prompt", "1,2 3", "--stop-id", "7",
+                             "--stop-id", "11", "--ignore-eos"])
+    assert o["ctx"] == 64                                   # at least 64, as the reference
+    assert o["prompts"] == [[1, 2, 3]] and o["stop_ids"] == [7, 11] and o["ignore_eos"] and o["seed"] == 9
+    for bad in (["--temp"], ["--top-k", "x"], ["--stop-id", "eos"], ["--nope", "1"], ["abc"]):
+        with pytest.raises(UsageError):
+            parse_generate_args(bad)
+
+
 @pytest.mark.gpu
 def test_generate_command(tmp_path):
     d = make_model_dir(tmp_path, TINY_C, 2, torch.bfloat16)
