@@ -84,6 +84,36 @@ def read_config_json(model_dir: str) -> dict:
     return d
 
 
+def merge_generation_config(model_dir: str, d: dict) -> dict:
+    """Stop tokens that a model folder names beside config.json: ``generation_config.json`` may list further
+    ``eos_token_id`` values (instruction-tuned checkpoints end a turn with tokens that config.json does not name).
+    The union, config.json's first, replaces ``d["eos_token_id"]``; a folder without the file is left as it is.
+    (The reference takes its stop set from the model file's metadata plus named control tokens,
+    fastgguf.c:3644-3652.)"""
+    path = os.path.join(model_dir, "generation_config.json")
+    if not os.path.exists(path):
+        return d
+    try:
+        with open(path, "r", encoding="utf-8") as f:
+            g = json.load(f)
+    except json.JSONDecodeError as e:
+        raise ConfigError(f"{path}: not valid JSON ({e})") from None
+    more = g.get("eos_token_id") if isinstance(g, dict) else None
+    if more is None:
+        return d
+    more = [more] if isinstance(more, int) and not isinstance(more, bool) else more
+    if not isinstance(more, list) or not all(isinstance(t, int) and not isinstance(t, bool) for t in more):
+        raise ConfigError(f"{path}: 'eos_token_id' must be an integer or a list of integers, got {more!r}")
+    have = d.get("eos_token_id")
+    have = [] if have is None else [have] if isinstance(have, int) and not isinstance(have, bool) else have
+    if not isinstance(have, list):
+        return d                                     # config.json's own value is wrong: its reader says so
+    merged = list(have) + [t for t in more if t not in have]
+    out = dict(d)
+    out["eos_token_id"] = merged[0] if len(merged) == 1 else merged
+    return out
+
+
 def architecture_name(d: dict) -> str:
     archs = d.get("architectures")
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):

@@ -15,7 +15,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Callable, Dict
 
-from .config.base import ConfigError, ModelConfig, architecture_name, read_config_json
+from .config.base import ConfigError, ModelConfig, architecture_name, merge_generation_config, read_config_json
 
 
 @dataclass(frozen=True)
@@ -53,7 +53,7 @@ def config_from_dict(d: dict) -> ModelConfig:
 
 
 def config_from_dir(model_dir: str) -> ModelConfig:
-    return config_from_dict(read_config_json(model_dir))
+    return config_from_dict(merge_generation_config(model_dir, read_config_json(model_dir)))
 
 
 def spec_from_config(config: ModelConfig):

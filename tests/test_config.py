@@ -127,3 +127,28 @@ def test_cli_option_parsing_follows_the_reference():
         parse_generate_args(["--bogus", "1"])
     with pytest.raises(UsageError, match="missing value"):
         parse_generate_args(["--temp"])
+
+
+def test_stop_tokens_of_generation_config_are_added(tmp_path):
+    """A folder's generation_config.json may name further end-of-turn tokens; the union is the stop set."""
+    from fastgguf_b200.config.base import ConfigError
+    from fastgguf_b200.registry import config_from_dir
+    d = tmp_path / "m"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(TINY_A))                     # eos_token_id 2
+    assert config_from_dir(str(d)).eos_token_ids == (2,)                   # no second file: unchanged
+    (d / "generation_config.json").write_text(json.dumps({"eos_token_id": [2, 7, 9], "temperature": 0.6}))
+    assert config_from_dir(str(d)).eos_token_ids == (2, 7, 9)
+    (d / "generation_config.json").write_text(json.dumps({"eos_token_id": 11}))
+    assert config_from_dir(str(d)).eos_token_ids == (2, 11)
+    (d / "generation_config.json").write_text(json.dumps({"do_sample": True}))
+    assert config_from_dir(str(d)).eos_token_ids == (2,)
+    (d / "generation_config.json").write_text(json.dumps({"eos_token_id": 100000}))
+    with pytest.raises(ConfigError, match="outside the vocabulary"):
+        config_from_dir(str(d))
+    (d / "generation_config.json").write_text(json.dumps({"eos_token_id": "</s>"}))
+    with pytest.raises(ConfigError, match="generation_config.json"):
+        config_from_dir(str(d))
+    (d / "generation_config.json").write_text("{not json")
+    with pytest.raises(ConfigError, match="not valid JSON"):
+        config_from_dir(str(d))
