@@ -98,12 +98,14 @@ class Engine:
     # ------------------------------------------------------------------ generation
     def generate(self, prompts: Sequence[Sequence[int]], *, temp: float = 1.0, top_k: int = 64, top_p: float = 0.95,
                  repeat_penalty: float = 1.0, repeat_last_n: int = 64, max_tokens: int = 512, seed: int = 0,
-                 stop_ids: Optional[Sequence[int]] = None, ignore_eos: bool = False, batch_size: Optional[int] = None):
-        """Generate for every prompt (lists of token ids); returns one ``Completion`` per prompt."""
+                 stop_ids: Optional[Sequence[int]] = None, ignore_eos: bool = False, batch_size: Optional[int] = None,
+                 on_token=None):
+        """Generate for every prompt (lists of token ids); returns one ``Completion`` per prompt.
+        ``on_token(request_index, token)``, if given, is called for each generated token as the host sees it."""
         from ..sampling import SamplingParams
         from .generate import generate
         params = SamplingParams(temp=temp, top_k=top_k, top_p=top_p, repeat_penalty=repeat_penalty,
                                 repeat_last_n=repeat_last_n, seed=seed)
         stops = tuple(self.spec.stop_token_ids if stop_ids is None else stop_ids)
         return generate(self, prompts, params, max_tokens=max_tokens, stop_ids=() if ignore_eos else stops,
-                        batch_size=batch_size or self.max_batch)
+                        batch_size=batch_size or self.max_batch, on_token=on_token)

@@ -35,8 +35,10 @@ def plan_batches(n_requests: int, batch_size: int) -> List[range]:
 
 
 def run_batch(backend, prompts: Sequence[Sequence[int]], first_index: int, max_tokens: int,
-              stop_ids: Sequence[int]) -> List[Completion]:
-    """Generate for one batch of prompts that start together.
+              stop_ids: Sequence[int], on_token=None) -> List[Completion]:
+    """Generate for one batch of prompts that start together.  ``on_token(request_index, token)`` is called
+    for every token as the host learns of it (the reference prints each token as it is made,
+    fastgguf.c:5297-5298); stop tokens are not reported, as they are not emitted.
 
     backend.acquire(request_index, prompt) -> slot      backend.release(slot)
     backend.step(entries) -> logits handle              backend.sample(logits, slots) -> list of tokens
@@ -60,6 +62,8 @@ def run_batch(backend, prompts: Sequence[Sequence[int]], first_index: int, max_t
                     c.finish_reason = "stop"
                     continue
                 c.tokens.append(int(tok))
+                if on_token is not None:
+                    on_token(first_index + i, int(tok))
                 if 0 < max_tokens <= len(c.tokens) or backend.room(slots[i]) <= 0:
                     c.finish_reason = "length"
                     continue
@@ -74,9 +78,9 @@ def run_batch(backend, prompts: Sequence[Sequence[int]], first_index: int, max_t
 
 
 def generate(engine, prompts: Sequence[Sequence[int]], params, *, max_tokens: int, stop_ids: Sequence[int],
-             batch_size: int) -> List[Completion]:
+             batch_size: int, on_token=None) -> List[Completion]:
     backend = engine.backend(params, stop_ids)
     out: List[Completion] = []
     for rng in plan_batches(len(prompts), batch_size):
-        out.extend(backend.run_batch([prompts[i] for i in rng], rng.start, max_tokens, stop_ids))
+        out.extend(backend.run_batch([prompts[i] for i in rng], rng.start, max_tokens, stop_ids, on_token))
     return out

@@ -133,10 +133,11 @@ class EngineBackend:
         return host
 
     # ------------------------------------------------------------------ batches
-    def run_batch(self, prompts, first_index: int, max_tokens: int, stop_ids: Sequence[int]) -> List[Completion]:
+    def run_batch(self, prompts, first_index: int, max_tokens: int, stop_ids: Sequence[int],
+                  on_token=None) -> List[Completion]:
         if self.use_graphs and len(prompts) <= BUCKETS[-1]:
-            return self._run_batch_graphs(prompts, first_index, max_tokens, stop_ids)
-        return run_batch(self, prompts, first_index, max_tokens, stop_ids)
+            return self._run_batch_graphs(prompts, first_index, max_tokens, stop_ids, on_token)
+        return run_batch(self, prompts, first_index, max_tokens, stop_ids, on_token)
 
     def _graph(self, width: int) -> DecodeGraph:
         g = self._graphs.get(width)
@@ -144,7 +145,7 @@ class EngineBackend:
             g = self._graphs[width] = DecodeGraph(self.engine, self.sampler, width)
         return g
 
-    def _run_batch_graphs(self, prompts, first_index, max_tokens, stop_ids) -> List[Completion]:
+    def _run_batch_graphs(self, prompts, first_index, max_tokens, stop_ids, on_token=None) -> List[Completion]:
         cache = self.engine.cache
         stop = set(stop_ids)
         n = len(prompts)
@@ -169,6 +170,8 @@ class EngineBackend:
                             c.finish_reason, known_done[i] = "stop", True
                             continue
                         c.tokens.append(int(tok))
+                        if on_token is not None:
+                            on_token(first_index + i, int(tok))
                         if 0 < max_tokens <= len(c.tokens) or len(prompts[i]) + len(c.tokens) - 1 >= cache.max_seq_len:
                             c.finish_reason, known_done[i] = "length", True
 

@@ -133,3 +133,77 @@ def test_device_error_flags_are_raised_and_only_loaded_libraries_are_asked(monke
         oplib.raise_on_device_error("prompt step")
     oplib.raise_on_device_error("prompt step")        # cleared by the read
     assert fake.reads == 2
+
+
+class _FakeEvent:
+    def synchronize(self):
+        pass
+
+
+class _HostTokens(list):
+    def tolist(self):
+        return list(self)
+
+
+def _graph_path(monkeypatch, scripts, prompts, first_index, max_tokens, stop_ids, capacity=1000, on_token=None):
+    """The graph path's host loop (tokens are seen one step late) with the device replaced by scripts."""
+    from types import SimpleNamespace
+    from fastgguf_b200.engine import runner
+    log = SimpleNamespace(advanced=[], closed=0)
+
+    class FakeSession:
+        def __init__(self, backend, prompts, first_index=0):
+            self.n = len(prompts)
+            self.idx = [first_index + i for i in range(self.n)]
+            self.cursor = [1] * self.n
+            self.first_tokens = [scripts[j][0] for j in self.idx]
+
+        def advance(self, live):
+            log.advanced.append(list(live))
+            toks = [0] * self.n
+            for i in live:
+                s = scripts[self.idx[i]]
+                toks[i] = s[self.cursor[i]] if self.cursor[i] < len(s) else 0      # the device goes on past a stop token
+                self.cursor[i] += 1
+            return _HostTokens(toks), _FakeEvent()
+
+        def close(self):
+            log.closed += 1
+
+    monkeypatch.setattr(runner, "DecodeSession", FakeSession)
+    monkeypatch.setattr(runner.ops, "raise_on_device_error", lambda *a, **k: None)
+    backend = object.__new__(runner.EngineBackend)
+    backend.engine = SimpleNamespace(cache=SimpleNamespace(max_seq_len=capacity))
+    out = backend._run_batch_graphs(prompts, first_index, max_tokens, stop_ids, on_token)
+    return out, log
+
+
+@pytest.mark.parametrize("scripts,prompts,max_tokens,stop,capacity", [
+    ({0: [10, 11, 12], 1: [20, 21, 22]}, [[1, 2, 3], [4]], 3, (), 1000),
+    ({0: [10, 99, 12, 13, 14], 1: [20, 21, 22, 23, 24]}, [[1], [2]], 4, (99,), 1000),
+    ({0: [99], 1: [99]}, [[1, 2], [3]], 8, (99,), 1000),
+    ({0: [5, 6, 7, 8, 9, 10, 11], 1: [99, 1, 1, 1, 1, 1, 1], 2: [7, 7, 99, 3, 3, 3, 3]}, [[1] * 4, [2] * 2, [3]], 6, (99,), 1000),
+    ({0: [1, 2, 3, 4, 5, 6, 7, 8], 1: [9, 9, 9, 9, 9, 9, 9, 9]}, [[1, 2, 3, 4, 5], [6]], 0, (), 8),     # the cache fills up
+])
+def test_graph_path_decides_as_the_plain_loop_does(monkeypatch, scripts, prompts, max_tokens, stop, capacity):
+    plain = run_batch(FakeBackend({k: list(v) + [0] * 8 for k, v in scripts.items()}, capacity=capacity), prompts, 0,
+                      max_tokens=max_tokens, stop_ids=stop)
+    seen = []
+    out, log = _graph_path(monkeypatch, scripts, prompts, 0, max_tokens, stop, capacity,
+                           on_token=lambda r, t: seen.append((r, t)))
+    assert [(c.tokens, c.finish_reason) for c in out] == [(c.tokens, c.finish_reason) for c in plain]
+    assert log.closed == 1
+    # every token is reported once, in order, and stop tokens are not
+    for i, c in enumerate(out):
+        assert [t for r, t in seen if r == i] == c.tokens
+    # a request is never stepped after the host knows that it ended, and at most once after it ended
+    for i, c in enumerate(out):
+        steps_taken = sum(1 for live in log.advanced if i in live)
+        assert steps_taken <= len(c.tokens) + 1
+
+
+def test_plain_loop_reports_tokens_with_request_indices():
+    seen = []
+    b = FakeBackend({4: [10, 99], 5: [20, 21]})
+    run_batch(b, [[1], [2]], 4, max_tokens=2, stop_ids=(99,), on_token=lambda r, t: seen.append((r, t)))
+    assert seen == [(4, 10), (5, 20), (5, 21)]
