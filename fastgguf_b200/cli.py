@@ -29,7 +29,8 @@ CHAT_OPTIONS_HELP = (
     "                  --max-tokens 512 (0 = until stop)  --seed N\n"
     "                  --prompt ID,ID,...  (repeat for a batch)  --prompts-file FILE (one prompt a line)\n"
     "                  --stop-id ID (repeat; added to the model's own stop tokens)\n"
-    "                  --dtype bfloat16|float32  --batch N  --ignore-eos  --json\n")
+    "                  --dtype bfloat16|float32  --batch N  --ignore-eos  --json\n"
+    "                  --stream  (print \"request token\" lines to the standard error as tokens are made)\n")
 
 
 class UsageError(Exception):
@@ -39,8 +40,8 @@ class UsageError(Exception):
 def parse_generate_args(argv: List[str]) -> dict:
     """Positional [ctx], then --option value pairs (fastgguf.c:6957-6974)."""
     o = dict(ctx=2048, temp=1.0, top_k=64, top_p=0.95, repeat_penalty=1.0, repeat_last_n=64, max_tokens=512,
-             seed=0, prompts=[], stop_ids=[], dtype="bfloat16", batch=None, ignore_eos=False, json=False)
-    flags = {"--ignore-eos": "ignore_eos", "--json": "json"}
+             seed=0, prompts=[], stop_ids=[], dtype="bfloat16", batch=None, ignore_eos=False, json=False, stream=False)
+    flags = {"--ignore-eos": "ignore_eos", "--json": "json", "--stream": "stream"}
     valued = {"--temp": ("temp", float), "--top-k": ("top_k", int), "--top-p": ("top_p", float),
               "--repeat-penalty": ("repeat_penalty", float), "--repeat-last-n": ("repeat_last_n", int),
               "--max-tokens": ("max_tokens", int), "--seed": ("seed", int), "--dtype": ("dtype", str),
@@ -115,7 +116,8 @@ def cmd_generate(model_dir: str, argv: List[str]) -> int:
     out = engine.generate(o["prompts"], temp=o["temp"], top_k=o["top_k"], top_p=o["top_p"],
                           repeat_penalty=o["repeat_penalty"], repeat_last_n=o["repeat_last_n"],
                           max_tokens=o["max_tokens"], seed=o["seed"], ignore_eos=o["ignore_eos"], batch_size=batch,
-                          stop_ids=(list(engine.spec.stop_token_ids) + o["stop_ids"]) if o["stop_ids"] else None)
+                          stop_ids=(list(engine.spec.stop_token_ids) + o["stop_ids"]) if o["stop_ids"] else None,
+                          on_token=(lambda r, t: print(r, t, file=sys.stderr, flush=True)) if o["stream"] else None)
     torch.cuda.synchronize()
     dt = time.time() - t0
     n_gen = sum(len(c.tokens) for c in out)

@@ -43,6 +43,7 @@ def test_generate_options_have_the_reference_names_and_defaults():
                              "--stop-id", "11", "--ignore-eos"])
     assert o["ctx"] == 64                                   # at least 64, as the reference
     assert o["prompts"] == [[1, 2, 3]] and o["stop_ids"] == [7, 11] and o["ignore_eos"] and o["seed"] == 9
+    assert not o["stream"] and parse_generate_args(["--stream"])["stream"]
     for bad in (["--temp"], ["--top-k", "x"], ["--stop-id", "eos"], ["--nope", "1"], ["abc"]):
         with pytest.raises(UsageError):
             parse_generate_args(bad)
