@@ -62,7 +62,10 @@ attn_decode_kernel(const bf16 *__restrict__ q, int ldq, const int *__restrict__ 
     if (CLUSTER && n_splits > 1) cluster_arrive_relaxed();       // matched before the first push: every CTA runs
     pdl_launch_dependents();
     if (!FUSE) pdl_wait();
-    // positions and page tables are written between steps, never by the kernel just before this one
+    // Read before the wait (fused form): positions, the page table and this entry's own pages.  Allowed only
+    // because nothing launched since the stream's last full barrier writes them (see common.cuh): positions
+    // and tables change by the step's opening copy or by decode_advance, the last kernel of a step, and this
+    // pool is appended to by this kernel alone.  A caller that reorders that must launch without the overlap.
     const int pos = positions[b];
     const int lo_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int first_page = lo_key / PAGE, n_pages = pos / PAGE - first_page + 1;
@@ -325,11 +328,16 @@ static int launch_decode_kernel(dim3 grid, int cluster_x, cudaStream_t stream, c
     constexpr int smem_max = DEC_WARPS * 2 * PAGE * HD * 2 + (CLUSTER ? DEC_WARPS * 16 * HD * 4 + DEC_WARPS * 8 * 16 * 2 * 4 : 0);
     const int rows_cap = G < 16 ? G : 16;
     const int smem = DEC_WARPS * 2 * PAGE * HD * 2 + (CLUSTER ? DEC_WARPS * rows_cap * HD * 4 + DEC_WARPS * n_splits * 16 * 2 * 4 : 0);
-    static bool configured = false;
-    if (!configured) {
+    // the attribute belongs to the function on ONE device: set it once on every device that launches
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaError_t ed = cudaGetDevice(&dev);
+    if (ed != cudaSuccess) return (int)ed;
+    if (dev < 0 || dev >= 64) return FG_ERR_BAD_SIZE;
+    if (!configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, CLUSTER, FUSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = dim3(DEC_WARPS * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
@@ -379,6 +387,7 @@ extern "C" int fg_attention_decode(const void *q, int ldq, void *out, int ldo, c
                                    int B, int H, int KV, int hd, int page_size, float scale, int window,
                                    int n_splits, float *part_o, float *part_ml, cudaStream_t stream) {
     if (B <= 0) return 0;
+    if (KV <= 0 || H <= 0) return FG_ERR_BAD_SIZE;
     if (page_size != PAGE || H % KV || n_splits < 1 || B > 65535 || ldq % 2 || ((uintptr_t)q & 3)) return FG_ERR_BAD_SIZE;
     if ((part_o == nullptr) != (part_ml == nullptr)) return FG_ERR_BAD_SIZE;
     if (!part_o && n_splits != 1 && n_splits != 2 && n_splits != 4 && n_splits != 8) return FG_ERR_BAD_SIZE;
@@ -395,6 +404,7 @@ extern "C" int fg_attention_decode_fused(const void *qkv, int ldq, void *out, in
                                          const float *cos_t, const float *sin_t, int B, int H, int KV, int hd,
                                          int page_size, float scale, int window, int n_splits, cudaStream_t stream) {
     if (B <= 0) return 0;
+    if (KV <= 0 || H <= 0) return FG_ERR_BAD_SIZE;
     if (page_size != PAGE || H % KV || B > 65535 || ldq % 8 || ((uintptr_t)qkv & 15) || ((uintptr_t)k_pool & 15) ||
         ((uintptr_t)v_pool & 15) || (n_splits != 1 && n_splits != 2 && n_splits != 4 && n_splits != 8))
         return FG_ERR_BAD_SIZE;
@@ -442,9 +452,10 @@ extern "C" int fg_attention_decode_noalloc(const void *q, int ldq, void *out, in
                                            const void *v_pool, int B, int H, int KV, int hd, int page_size, float scale,
                                            int window, int n_splits, cudaStream_t stream) {
     if (B <= 0) return 0;
-    if (n_splits < 1 || H <= 0 || hd <= 0) return FG_ERR_BAD_SIZE;
+    if (n_splits < 1 || H <= 0 || KV <= 0 || hd <= 0) return FG_ERR_BAD_SIZE;
     long long rows = (long long)B * H * n_splits;
-    if (rows * (hd + 2) > FG_NOALLOC_SCRATCH_FLOATS) return FG_ERR_NOALLOC_TOO_LARGE;
+    // with one split the kernel writes the output itself and never touches the array
+    if (n_splits > 1 && rows * (hd + 2) > FG_NOALLOC_SCRATCH_FLOATS) return FG_ERR_NOALLOC_TOO_LARGE;
     float *scratch = nullptr;
     int e = noalloc_scratch_address(&scratch);
     if (e) return e;

@@ -94,6 +94,14 @@ __device__ __forceinline__ bool elect_one() {
 // pdl_launch_dependents() at its start (its successor may be scheduled) and pdl_wait() before
 // it first touches memory that an earlier kernel writes or reads; what it does before that
 // wait (barrier set-up, fetching weights, which no kernel writes) overlaps the predecessor.
+// The wait returns when every earlier kernel of the stream has finished (each of them waits too, so
+// completion is transitive); BEFORE it, not only the predecessor but kernels further back may still
+// run, because a kernel releases its successor at its start.  So a kernel may read before its wait
+// only memory that nothing launched since the last full barrier of the stream writes - a full barrier
+// being a memory copy, or the boundary of a graph launch.  Weights qualify always.  Positions, page
+// tables and an entry's own cache pool qualify for the fused decode attention because the engine writes
+// positions and tables only by the copy that opens a step or by `decode_advance_kernel`, the LAST
+// node of the decode graph, and because an entry's pool is appended to by that entry's kernel alone.
 // FASTGGUF_PDL=0 turns the attribute off; the two instructions are then no-ops.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

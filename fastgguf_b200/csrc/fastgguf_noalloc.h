@@ -12,9 +12,11 @@
  * the caller allocates.  The caller still passes every input and the output.
  *
  * Limits and rules
- *   - B * H * n_splits * (head_dim + 2) must not exceed FG_NOALLOC_SCRATCH_FLOATS (1 Mi floats,
- *     4 MiB); larger requests return FG_ERR_NOALLOC_TOO_LARGE and launch nothing.  Every GPU
- *     that loads the library holds these 4 MiB until the process exits.
+ *   - With n_splits > 1, B * H * n_splits * (head_dim + 2) must not exceed
+ *     FG_NOALLOC_SCRATCH_FLOATS (1 Mi floats, 4 MiB); larger requests return
+ *     FG_ERR_NOALLOC_TOO_LARGE and launch nothing.  A call with n_splits == 1 writes its output
+ *     directly, uses none of the array and has no such limit.  Every GPU that loads the library
+ *     holds these 4 MiB until the process exits.
  *   - The first call on a device looks up the array's device address (once per device, with
  *     that device current).  Make that first call outside any stream capture.
  *   - All calls share the one array, which keeps the last call's contents.  Every element a

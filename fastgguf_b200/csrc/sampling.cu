@@ -444,8 +444,12 @@ topk_stage2_kernel(const unsigned long long *__restrict__ cand_in, int n_cand, i
 
 // ---- greedy without a repeat penalty: the vocabulary of each row is split over GREEDY_BLOCKS blocks;
 // each folds its best (value, lowest index) into one 64-bit word per row with atomicMax, and the
-// block that arrives last writes the token and clears the word for the next call.  The words
-// live in device memory of this library; calls on one stream follow one another.
+// block that arrives last writes the token and clears the word for the next call.  The words (best,
+// arrivals) are the first two of the caller's scratch row when `scratch` is given - a sampler that
+// owns its scratch shares nothing with other samplers and can clear it when a batch starts - and
+// otherwise live in device memory of this library, which every caller without scratch shares: such
+// calls must follow one another on ONE stream, and a launch that never finished leaves its row's
+// count behind.
 #define GREEDY_BLOCKS 32
 #define GREEDY_MAX_ROWS 1024
 __device__ unsigned long long g_greedy_best[GREEDY_MAX_ROWS];
@@ -453,11 +457,14 @@ __device__ int g_greedy_count[GREEDY_MAX_ROWS];
 
 __global__ void __launch_bounds__(256)
 greedy_kernel(const float *__restrict__ logits, int V, int ldl, const int *__restrict__ seq_slot,
-              int *__restrict__ hist, int hist_cap, int *__restrict__ hist_count, int *__restrict__ out_tokens) {
+              int *__restrict__ hist, int hist_cap, int *__restrict__ hist_count, int *__restrict__ out_tokens,
+              unsigned long long *__restrict__ scratch, int scratch_stride) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ unsigned long long s_best[8];
     const int b = blockIdx.y;
+    unsigned long long *word = scratch ? scratch + (size_t)b * scratch_stride : &g_greedy_best[b];
+    int *count = scratch ? (int *)(scratch + (size_t)b * scratch_stride + 1) : &g_greedy_count[b];
     const float *row = logits + (size_t)b * ldl;
     const int per = (V + GREEDY_BLOCKS - 1) / GREEDY_BLOCKS;
     const int i0 = blockIdx.x * per, i1 = min(V, i0 + per);
@@ -475,15 +482,15 @@ greedy_kernel(const float *__restrict__ logits, int V, int ldl, const int *__res
     __syncthreads();
     if (threadIdx.x == 0) {
         for (int w = 1; w < (int)(blockDim.x >> 5); w++) best = s_best[w] > best ? s_best[w] : best;
-        atomicMax(&g_greedy_best[b], best);
+        atomicMax(word, best);
         __threadfence();
-        if (atomicAdd(&g_greedy_count[b], 1) == GREEDY_BLOCKS - 1) {
+        if (atomicAdd(count, 1) == GREEDY_BLOCKS - 1) {
             __threadfence();
-            unsigned long long win = atomicMax(&g_greedy_best[b], 0ull);
+            unsigned long long win = atomicMax(word, 0ull);
             int tok = (int)(~(uint32_t)(win & 0xffffffffull));
             out_tokens[b] = tok;
-            g_greedy_best[b] = 0ull;
-            g_greedy_count[b] = 0;
+            *word = 0ull;
+            *count = 0;
             if (hist) {
                 int slot = seq_slot[b];
                 int *h = hist + (size_t)slot * hist_cap;
@@ -504,9 +511,9 @@ extern "C" int fg_sample(float *logits, int B, int V, int ldl, float temp, int t
     if (B <= 0) return 0;
     if (top_k > MAX_TOP_K) return FG_ERR_BAD_SIZE;
     bool penalizes = hist && repeat_penalty > 0.f && repeat_penalty != 1.0f && repeat_last_n > 0;
-    if (temp <= 0.f && !penalizes && B <= GREEDY_MAX_ROWS)
+    if (temp <= 0.f && !penalizes && (scratch ? B <= 65535 : B <= GREEDY_MAX_ROWS))
         return fg_launch(greedy_kernel, dim3(GREEDY_BLOCKS, B), dim3(256), 0, stream, (const float *)logits, V, ldl,
-                         seq_slot, hist, hist_cap, hist_count, out_tokens);
+                         seq_slot, hist, hist_cap, hist_count, out_tokens, scratch, TOPK_CAND);
     SampleParams sp{temp, top_p, repeat_penalty, top_k, repeat_last_n};
     if (temp > 0.f && top_k > 0 && top_k <= TOPK_MAX_K && scratch && B <= 65535) {
         // two stages; `scratch` holds B * 2048 words

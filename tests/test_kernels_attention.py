@@ -88,7 +88,8 @@ def test_attention_generic(H, KV, hd, window, dtype, tol):
 
 @pytest.mark.parametrize("n_splits", [None, 1, 2, 3, 8, 16])
 @pytest.mark.parametrize("H,KV,hd,window", [(8, 2, 64, 0), (3, 1, 128, 0), (24, 8, 128, 0), (20, 1, 64, 0),
-                                            (4, 4, 64, 100)])
+                                            (4, 4, 64, 100), (4, 2, 64, 64), (4, 2, 64, 128), (8, 2, 64, 65),
+                                            (6, 2, 128, 128), (3, 1, 128, 65)])
 def test_attention_decode(H, KV, hd, window, n_splits):
     from fastgguf_b200.ops import fast_attention
     case = make_case([0, 63, 64, 700, 2047, 129], [1] * 6, H, KV, hd, torch.bfloat16, 12)
@@ -105,7 +106,8 @@ def test_attention_decode(H, KV, hd, window, n_splits):
 
 
 @pytest.mark.parametrize("H,KV,hd,window", [(8, 2, 64, 0), (3, 1, 128, 0), (24, 8, 128, 0), (20, 1, 64, 0),
-                                            (4, 4, 64, 100)])
+                                            (4, 4, 64, 100), (4, 2, 64, 64), (4, 2, 64, 128), (8, 2, 64, 65),
+                                            (6, 2, 128, 128), (3, 1, 128, 65)])
 def test_attention_prefill(H, KV, hd, window):
     from fastgguf_b200.ops import fast_attention
     new = [200, 1, 67, 5]
@@ -117,7 +119,8 @@ def test_attention_prefill(H, KV, hd, window):
 
 
 @pytest.mark.parametrize("H,KV,hd,window", [(8, 2, 64, 0), (3, 1, 128, 0), (24, 8, 128, 0), (20, 1, 64, 0),
-                                            (4, 4, 64, 100)])
+                                            (4, 4, 64, 100), (4, 2, 64, 64), (4, 2, 64, 128), (8, 2, 64, 65),
+                                            (6, 2, 128, 128), (3, 1, 128, 65)])
 def test_attention_prefill_tcgen05(H, KV, hd, window):
     from fastgguf_b200.ops import fast_attention
     new = [200, 1, 67, 5, 300]
@@ -130,7 +133,8 @@ def test_attention_prefill_tcgen05(H, KV, hd, window):
 
 
 @pytest.mark.parametrize("n_splits", [None, 1, 4, 8])
-@pytest.mark.parametrize("H,KV,hd,window", [(8, 2, 64, 0), (6, 2, 128, 0), (20, 1, 64, 0), (4, 4, 64, 100)])
+@pytest.mark.parametrize("H,KV,hd,window", [(8, 2, 64, 0), (6, 2, 128, 0), (20, 1, 64, 0), (4, 4, 64, 100),
+                                            (4, 2, 64, 64), (4, 2, 64, 128), (6, 2, 128, 65), (6, 2, 128, 128)])
 def test_attention_decode_fused_with_rope_and_append(H, KV, hd, window, n_splits):
     """One kernel for RoPE, cache append and attention of a decode step, against the separate kernels."""
     from fastgguf_b200 import ops

@@ -58,7 +58,9 @@ def test_noalloc_rejects_requests_beyond_its_array():
     fn = _noalloc_symbol()
     H, KV, hd = 32, 8, 128
     case = make_case([10] * 4, [1] * 4, H, KV, hd, torch.bfloat16, 24)
-    case["q"] = case["q"].repeat(600, 1)                 # B * H * n_splits * (hd + 2) > 1 Mi floats
-    rc, _ = _call(fn, dict(case), H, KV, hd, 0.1, 1)
+    case["q"] = case["q"].repeat(300, 1)                 # B * H * n_splits * (hd + 2) > 1 Mi floats
+    rc, _ = _call(fn, dict(case), H, KV, hd, 0.1, 2)
     assert rc == 10005                                   # refused before anything is launched
+    rc, _ = _call(fn, dict(case), H, 0, hd, 0.1, 2)
+    assert rc == 10002                                   # no KV heads: a size error, not a division by zero
     torch.cuda.synchronize()
