@@ -1,4 +1,4 @@
-"""Paged key/value cache with per-sequence slots and fixed-size per-sequence state."""
-from .paged import CacheError, CacheFull, CacheGroup, PagedKVCache, StatePool
+"""Paged key/value cache with per-sequence slots (bookkeeping view of the host's cache)."""
+from .paged import CacheError, CacheFull, CacheRequest, PagedKVCache, cache_bytes
 
-__all__ = ["CacheError", "CacheFull", "CacheGroup", "PagedKVCache", "StatePool"]
+__all__ = ["CacheError", "CacheFull", "CacheRequest", "PagedKVCache", "cache_bytes"]

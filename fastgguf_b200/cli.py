@@ -87,38 +87,44 @@ def cmd_generate(model_dir: str, argv: List[str]) -> int:
     o = parse_generate_args(argv)
     if not o["prompts"]:
         raise UsageError("generate needs at least one --prompt ID,ID,... (token ids) or --prompts-file FILE")
+    from .capi import EngineError
     from .engine.api import Engine
     n = len(o["prompts"])
     batch = o["batch"] or min(n, 64)
-    try:
-        engine = Engine.from_dir(model_dir, dtype=o["dtype"], max_tokens=batch * ((o["ctx"] + 63) // 64 * 64),
-                                 max_batch=batch, max_seq_len=o["ctx"])
-    except (ValueError, OSError) as e:
-        print(e)
-        return 2
-    cfg = engine.config
 
     def say(*args, **kw):
         # with --json the standard output is one JSON document; the summary lines go to the standard error
         print(*args, file=sys.stderr if o["json"] else sys.stdout, **kw)
 
-    say(f"[Config] {type(cfg).architecture_names[0]}: layers={len(engine.spec.layers)} embd={engine.spec.hidden_size} "
-        f"ctx={engine.cache.max_seq_len} dtype={o['dtype']}")
-    say(f"[Model] {len(engine.model.expected_tensors())} tensors, vocab={engine.spec.vocab_size}")
+    try:
+        engine = Engine.from_dir(model_dir, dtype=o["dtype"], max_tokens=batch * ((o["ctx"] + 63) // 64 * 64),
+                                 max_batch=batch, max_seq_len=o["ctx"])
+    except (EngineError, ValueError, OSError) as e:
+        print(e)
+        return 2
+    info = engine.info()
+    # the reference's load-time summary (fastgguf.c:4561-4565), with the cache's size
+    say(f"[Config] {engine.config.architecture}: layers={info['layers']} embd={info['hidden_size']} "
+        f"ctx={info['max_seq_len']} dtype={o['dtype']}")
+    say(f"[Model] {info['tensors']} tensors, {info['weight_bytes'] / 2 ** 20:.1f} MiB, vocab={info['vocab_size']}")
+    say(f"[cache] slots={info['slots']} pages={info['pages']} page={info['page_size']} "
+        f"bytes/token={info['bytes_per_token']} bytes={info['cache_bytes']} ({info['cache_bytes'] / 2 ** 20:.1f} MiB)")
     if o["temp"] <= 0:
         say("[Sampler] greedy", end="")
     else:
         say(f"[Sampler] temp={o['temp']:.2f} top_k={o['top_k']} top_p={o['top_p']:.2f}", end="")
     say(f" repeat_penalty={o['repeat_penalty']:.2f} (last {o['repeat_last_n']}) max_tokens={o['max_tokens']} "
         f"seed={o['seed']}")
-    import torch
     t0 = time.time()
-    out = engine.generate(o["prompts"], temp=o["temp"], top_k=o["top_k"], top_p=o["top_p"],
-                          repeat_penalty=o["repeat_penalty"], repeat_last_n=o["repeat_last_n"],
-                          max_tokens=o["max_tokens"], seed=o["seed"], ignore_eos=o["ignore_eos"], batch_size=batch,
-                          stop_ids=(list(engine.spec.stop_token_ids) + o["stop_ids"]) if o["stop_ids"] else None,
-                          on_token=(lambda r, t: print(r, t, file=sys.stderr, flush=True)) if o["stream"] else None)
-    torch.cuda.synchronize()
+    try:
+        out = engine.generate(o["prompts"], temp=o["temp"], top_k=o["top_k"], top_p=o["top_p"],
+                              repeat_penalty=o["repeat_penalty"], repeat_last_n=o["repeat_last_n"],
+                              max_tokens=o["max_tokens"], seed=o["seed"], ignore_eos=o["ignore_eos"], batch_size=batch,
+                              stop_ids=(list(info["stop_token_ids"]) + o["stop_ids"]) if o["stop_ids"] else None,
+                              on_token=(lambda r, t: print(r, t, file=sys.stderr, flush=True)) if o["stream"] else None)
+    except (EngineError, ValueError) as e:
+        print(e)
+        return 1
     dt = time.time() - t0
     n_gen = sum(len(c.tokens) for c in out)
     if o["json"]:
@@ -131,34 +137,39 @@ def cmd_generate(model_dir: str, argv: List[str]) -> int:
 
 
 def cmd_inspect(model_dir: str, as_json: bool = False) -> int:
-    """What ``fastgguf inspect`` prints for a GGUF file (fastgguf.c:5319-5360), for a model folder:
-    the architecture, every configuration field and derived size, a dtype histogram and the tensors."""
-    from .config.base import ConfigError
+    """What ``fastgguf inspect`` prints for a GGUF file (fastgguf.c:5319-5360), for a model folder: the
+    architecture, every configuration field (marked where the file did not give it) and derived size, memory
+    per token and for the parameters, a dtype histogram and the tensors."""
+    from .capi import EngineError
     from .registry import config_from_dir
-    from .weights.loader import FolderSource
-    from .weights.safetensors_io import SafetensorsError
+    from .weights import folder_tensors
     try:
         cfg = config_from_dir(model_dir)
-        src = FolderSource(model_dir)
-    except (ConfigError, SafetensorsError, OSError) as e:
+        tensors = folder_tensors(model_dir)
+    except (EngineError, OSError) as e:
         print(e)
         return 2
     desc = cfg.describe()
-    tensors = [(n, *src.shape_dtype(n)) for n in sorted(src.names())]
     if as_json:
-        print(json.dumps({"architecture": type(cfg).architecture_names[0], "config": desc,
-                          "tensors": [{"name": n, "shape": list(s), "dtype": str(d)} for n, s, d in tensors]},
-                         default=str))
+        print(json.dumps({"architecture": cfg.architecture, "config": desc, "tensors": tensors}))
         return 0
-    print(f"architecture: {type(cfg).architecture_names[0]}")
+    defaulted = set(desc.get("defaulted", []))
+    print(f"architecture: {cfg.architecture}")
     for k, v in desc.items():
-        print(f"  {k} = {v}")
-    hist = {}
-    for _, s, d in tensors:
-        hist[str(d)] = hist.get(str(d), 0) + 1
-    print(f"tensors: {len(tensors)}  (" + ", ".join(f"{k}: {v}" for k, v in sorted(hist.items())) + ")")
-    for n, s, d in tensors[:15]:
-        print(f"  {n:<48} {str(d).replace('torch.', ''):<9} {list(s)}")
+        if k in ("architecture", "defaulted"):
+            continue
+        print(f"  {k} = {v}" + ("   (default)" if k in defaulted else ""))
+    hist, nbytes = {}, {}
+    sizes = {"float32": 4, "bfloat16": 2, "float16": 2, "int32": 4, "int64": 8}
+    for t in tensors:
+        n = 1
+        for s in t["shape"]:
+            n *= s
+        hist[t["dtype"]] = hist.get(t["dtype"], 0) + 1
+        nbytes[t["dtype"]] = nbytes.get(t["dtype"], 0) + n * sizes.get(t["dtype"], 0)
+    print(f"tensors: {len(tensors)}  (" + ", ".join(f"{k}: {v} ({nbytes[k] / 2 ** 20:.1f} MiB)" for k, v in sorted(hist.items())) + ")")
+    for t in tensors[:15]:
+        print(f"  {t['name']:<48} {t['dtype']:<9} {t['shape']}")
     if len(tensors) > 15:
         print(f"  ... {len(tensors) - 15} more")
     return 0
@@ -192,12 +203,16 @@ def cmd_random(argv: List[str]) -> int:
         else:
             raise UsageError(f"unknown option {argv[i]}")
         i += 2
-    from .engine.api import parse_dtype
+    from .capi import EngineError
     from .registry import config_from_dict
-    from .weights.random_init import write_random_model
-    with open(argv[0]) as f:
-        cfg = config_from_dict(json.load(f))
-    out = write_random_model(cfg, seed, argv[1], parse_dtype(dtype))
+    from .weights import write_random_model
+    try:
+        with open(argv[0]) as f:
+            cfg = config_from_dict(json.load(f))
+        out = write_random_model(cfg, seed, argv[1], dtype)
+    except (EngineError, ValueError, OSError) as e:
+        print(e)
+        return 2
     print(f"wrote {out}/config.json and {out}/model.safetensors (seed {seed}, {dtype})")
     return 0
 

@@ -1,5 +1,5 @@
-"""Typed configurations, one class per architecture, chosen by ``architectures[0]``."""
+"""Typed configurations, chosen by ``architectures[0]`` of config.json (read and checked by the C++ host)."""
 from .base import ConfigError, ModelConfig, architecture_name, read_config_json
-from .llama import LlamaConfig, RopeScaling
+from .llama import LlamaConfig
 
-__all__ = ["ConfigError", "ModelConfig", "LlamaConfig", "RopeScaling", "architecture_name", "read_config_json"]
+__all__ = ["ConfigError", "ModelConfig", "LlamaConfig", "architecture_name", "read_config_json"]

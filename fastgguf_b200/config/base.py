@@ -1,76 +1,97 @@
-"""Typed model configuration: the shared base and the error type.
+"""Typed model configuration as Python sees it: a view of the C++ host's configuration object.
 
-A configuration is read from the architecture's own ``config.json`` keys.  Every size and
-every constant that ``config.json`` gives lives in the typed object and nowhere else; code
-that needs a size takes it from there (or from a part's parameters, which were filled from
-there).
-
-The reference engine reads the same numbers from GGUF metadata through ``kv_num(g, key,
-default)`` (fastgguf.c:448-454) with an architecture prefix (fastgguf.c:4189) and fails with
-"bad config" on nonsense (fastgguf.c:4215-4218).
+The configuration is read, defaulted and validated by the host (``csrc/host/config.cpp``: the
+architecture's own config.json keys, the reference's defaults for absent ones - fastgguf.c:4224,
+:4228, :4281-4283 - and "bad config" errors, :4215-4218).  A ``ModelConfig`` here holds the host's
+handle and shows its fields as attributes; no size or constant of config.json is kept anywhere else.
 """
 from __future__ import annotations
 
 import json
 import os
-from dataclasses import dataclass, fields, asdict
-from typing import ClassVar
+from ctypes import byref, c_void_p
+from types import SimpleNamespace
+
+from .. import capi
+from ..capi import ConfigError
+
+__all__ = ["ConfigError", "ModelConfig", "architecture_name", "read_config_json"]
 
 
-class ConfigError(ValueError):
-    """A config.json that is missing a key, has a wrong type, or describes an impossible model."""
-
-
-_MISSING = object()
-
-
-def take(d: dict, key: str, typ, default=_MISSING, *, where: str = "config.json"):
-    """Fetch ``d[key]`` with a type check; ``default`` stands for an absent or null key."""
-    v = d.get(key, None)
-    if v is None:
-        if default is _MISSING:
-            raise ConfigError(f"{where}: required key '{key}' is missing")
-        return default
-    if typ is float and isinstance(v, int) and not isinstance(v, bool):
-        v = float(v)
-    if typ is int and isinstance(v, bool):
-        raise ConfigError(f"{where}: key '{key}' must be an integer, got {v!r}")
-    if typ is int and isinstance(v, float) and v == int(v):
-        v = int(v)
-    if not isinstance(v, typ):
-        raise ConfigError(f"{where}: key '{key}' must be {typ.__name__}, got {type(v).__name__} ({v!r})")
-    return v
-
-
-@dataclass
 class ModelConfig:
-    """Base of every architecture's typed configuration."""
+    """A configuration of a registered architecture (a handle of the host plus its description)."""
 
-    #: names under which ``architectures[0]`` of config.json selects this class
-    architecture_names: ClassVar[tuple] = ()
+    def __init__(self, handle: c_void_p):
+        self._handle = handle
+        self._desc = capi.take_json(capi.lib().fg_config_describe, handle)
+
+    def __del__(self):
+        h, self._handle = getattr(self, "_handle", None), None
+        if h:
+            try:
+                capi.lib().fg_config_destroy(h)
+            except Exception:
+                pass
+
+    # -- construction ------------------------------------------------------------------
+    @classmethod
+    def from_dict(cls, d: dict) -> "ModelConfig":
+        out = c_void_p()
+        capi.check(capi.lib().fg_config_from_json(json.dumps(d).encode("utf-8"), byref(out)))
+        return cls(out)
 
     @classmethod
-    def from_dict(cls, d: dict) -> "ModelConfig":  # pragma: no cover - abstract
-        raise NotImplementedError
+    def from_dir(cls, model_dir: str) -> "ModelConfig":
+        out = c_void_p()
+        capi.check(capi.lib().fg_config_from_dir(os.fspath(model_dir).encode("utf-8"), byref(out)))
+        return cls(out)
+
+    # -- views ---------------------------------------------------------------------------
+    @property
+    def architecture(self) -> str:
+        return self._desc["architecture"]
+
+    @property
+    def architecture_names(self) -> tuple:
+        return (self._desc["architecture"],)
 
     def to_dict(self) -> dict:
         """The config.json form of this configuration (what ``from_dict`` reads back)."""
-        raise NotImplementedError
+        return capi.take_json(capi.lib().fg_config_to_json, self._handle)
 
-    def validate(self) -> None:
-        raise NotImplementedError
-
-    # -- shared helpers ---------------------------------------------------------------
     def describe(self) -> dict:
-        """Every field, plus derived sizes; the ``inspect`` dump prints this."""
-        out = {}
-        for f in fields(self):
-            v = getattr(self, f.name)
-            out[f.name] = asdict(v) if hasattr(v, "__dataclass_fields__") else v
-        return out
+        """Every field, plus derived sizes, memory per token and the keys that were defaulted."""
+        return dict(self._desc)
+
+    def spec_json(self) -> dict:
+        """The model as data: parts, layers, execution order, checkpoint tensor names."""
+        return capi.take_json(capi.lib().fg_config_spec, self._handle)
+
+    def parameter_count(self) -> int:
+        return int(self._desc["parameters"])
+
+    def __getattr__(self, name):
+        desc = self.__dict__.get("_desc")
+        if desc is None or name not in desc:
+            raise AttributeError(name)
+        v = desc[name]
+        if name == "eos_token_ids":
+            return tuple(v)
+        if isinstance(v, dict):
+            return SimpleNamespace(**v)
+        return v
+
+    def __eq__(self, other):
+        return isinstance(other, ModelConfig) and self.to_dict() == other.to_dict()
+
+    __hash__ = None
+
+    def __repr__(self):
+        return f"{type(self).__name__}({self.to_dict()})"
 
 
 def read_config_json(model_dir: str) -> dict:
+    """config.json of a folder as it stands (for ``dump``); the typed reading is the host's."""
     path = os.path.join(model_dir, "config.json")
     try:
         with open(path, "r", encoding="utf-8") as f:
@@ -82,36 +103,6 @@ def read_config_json(model_dir: str) -> dict:
     if not isinstance(d, dict):
         raise ConfigError(f"{path}: top level must be an object")
     return d
-
-
-def merge_generation_config(model_dir: str, d: dict) -> dict:
-    """Stop tokens that a model folder names beside config.json: ``generation_config.json`` may list further
-    ``eos_token_id`` values (instruction-tuned checkpoints end a turn with tokens that config.json does not name).
-    The union, config.json's first, replaces ``d["eos_token_id"]``; a folder without the file is left as it is.
-    (The reference takes its stop set from the model file's metadata plus named control tokens,
-    fastgguf.c:3644-3652.)"""
-    path = os.path.join(model_dir, "generation_config.json")
-    if not os.path.exists(path):
-        return d
-    try:
-        with open(path, "r", encoding="utf-8") as f:
-            g = json.load(f)
-    except json.JSONDecodeError as e:
-        raise ConfigError(f"{path}: not valid JSON ({e})") from None
-    more = g.get("eos_token_id") if isinstance(g, dict) else None
-    if more is None:
-        return d
-    more = [more] if isinstance(more, int) and not isinstance(more, bool) else more
-    if not isinstance(more, list) or not all(isinstance(t, int) and not isinstance(t, bool) for t in more):
-        raise ConfigError(f"{path}: 'eos_token_id' must be an integer or a list of integers, got {more!r}")
-    have = d.get("eos_token_id")
-    have = [] if have is None else [have] if isinstance(have, int) and not isinstance(have, bool) else have
-    if not isinstance(have, list):
-        return d                                     # config.json's own value is wrong: its reader says so
-    merged = list(have) + [t for t in more if t not in have]
-    out = dict(d)
-    out["eos_token_id"] = merged[0] if len(merged) == 1 else merged
-    return out
 
 
 def architecture_name(d: dict) -> str:

@@ -31,7 +31,12 @@ MODULES = {
     "core": ["elementwise.cu", "gemm_generic.cu", "attention_generic.cu", "sampling.cu"],
     "tc": ["gemm_tc.cu"],
     "attn": ["attention_decode.cu", "attention_prefill.cu", "attention_prefill_tc.cu"],
+    # the C++ host: configuration, weights, cache, step function, generation loop, C interface; it opens the
+    # kernel libraries above by name when a model first needs them
+    "engine": ["host/api.cpp", "host/cache.cpp", "host/config.cpp", "host/device.cpp", "host/model.cpp", "host/parts.cpp",
+               "host/runner.cpp", "host/safetensors.cpp", "host/host_kernels.cu"],
 }
+LINK_FLAGS = {"engine": ["-ldl"]}
 HEADERS = ["common.cuh"]
 
 NVCC_FLAGS = [
@@ -84,7 +89,11 @@ def _module_hash(module: str) -> str:
 
 
 def _extra_headers(module: str) -> list:
-    return [f for f in os.listdir(CSRC_DIR) if f.endswith((".cuh", ".h")) and f not in HEADERS]
+    top = [f for f in os.listdir(CSRC_DIR) if f.endswith((".cuh", ".h")) and f not in HEADERS]
+    if module != "engine":
+        return top
+    host = os.path.join(CSRC_DIR, "host")
+    return top + ["host/" + f for f in os.listdir(host) if f.endswith(".hpp")]
 
 
 def _say(msg: str) -> None:
@@ -134,11 +143,11 @@ def build_module(module: str, verbose_ptxas: bool = False) -> str:
         th.start()
         try:
             extra = ["-Xptxas", "-v"] if verbose_ptxas else []
-            objs = [os.path.join(out_dir, f"{module}-{os.path.splitext(s)[0]}.{os.getpid()}.o") for s in srcs]
+            objs = [os.path.join(out_dir, f"{module}-{os.path.splitext(s)[0].replace('/', '_')}.{os.getpid()}.o") for s in srcs]
             with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 2)) as ex:
                 list(ex.map(lambda a: _compile_one(nvcc, a[0], a[1], extra), zip(srcs, objs)))
             tmp = lib + f".{os.getpid()}.tmp"
-            p = subprocess.run([nvcc, "-shared", "-o", tmp, *objs], capture_output=True, text=True)
+            p = subprocess.run([nvcc, "-shared", "-o", tmp, *objs, *LINK_FLAGS.get(module, [])], capture_output=True, text=True)
             if p.returncode != 0:
                 raise BuildError(f"linking {lib} failed:\n{p.stdout}\n{p.stderr}")
             os.replace(tmp, lib)

@@ -1,0 +1,100 @@
+// What the host needs from the device: checked CUDA calls, tensors as (pointer, dtype, shape, row stride),
+// a bump allocator for a step's activations, and the kernel libraries' launchers looked up on first use.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "../fastgguf_b200.h"
+#include "../fastgguf_parts.h"
+#include "errors.hpp"
+
+namespace fg {
+
+#define FG_CUDA(call)                                                                                        \
+    do {                                                                                                     \
+        cudaError_t e_ = (call);                                                                             \
+        if (e_ != cudaSuccess)                                                                               \
+            ::fg::fail(FG_E_DEVICE, ::fg::format("%s failed: %s", #call, cudaGetErrorString(e_)));           \
+    } while (0)
+
+// A launcher's return code -> exception (0 passes).
+void check_kernel(int code, const char *what);
+
+// A launcher of libfg_<module>.so, opened on first use from the folder of this library (or
+// $FASTGGUF_LIB_DIR).  A missing library is an error: there is no other implementation to fall back to.
+void *kernel_symbol(const char *module, const char *name);
+#define FG_KERNEL(module, fn) (reinterpret_cast<decltype(&::fn)>(::fg::kernel_symbol(module, #fn)))
+// every launcher call made so far (each launches at least one kernel)
+long long launch_count();
+void count_launch();
+#define FG_LAUNCH(module, fn, ...)                                                                           \
+    do {                                                                                                     \
+        ::fg::count_launch();                                                                                \
+        ::fg::check_kernel(FG_KERNEL(module, fn)(__VA_ARGS__), #fn);                                         \
+    } while (0)
+// Reads and clears the error flags of the kernel libraries that are loaded; throws FG_E_KERNEL if one is set.
+void raise_on_device_error(const char *where);
+
+struct Tensor {
+    void *data = nullptr;
+    int dtype = FG_F32;
+    int64_t rows = 0, cols = 0;      // a matrix [rows, cols]; vectors have rows == 1
+    int64_t ld = 0;                  // elements between rows
+    bool defined() const { return data != nullptr; }
+    int64_t numel() const { return rows * cols; }
+    template <typename T> T *ptr() const { return (T *)data; }
+    Tensor row_range(int64_t begin, int64_t end) const;
+    fg_dev_tensor view() const;
+};
+int elem_size(int dtype);
+
+// Device memory for the activations of one step: allocation bumps a cursor through a list of blocks;
+// `reset` starts over.  The sequence of allocations of a step is deterministic, so a step that is run
+// once to warm up and then recorded into a CUDA graph gets the same addresses both times; blocks are only
+// added outside a recording.
+class Arena {
+public:
+    explicit Arena(size_t block_bytes = (size_t)64 << 20) : block_bytes_(block_bytes) {}
+    ~Arena();
+    Arena(const Arena &) = delete;
+    void *alloc(size_t bytes);
+    Tensor matrix(int64_t rows, int64_t cols, int dtype);
+    void reset() { block_ = 0; offset_ = 0; }
+    void forbid_growth(bool v) { frozen_ = v; }
+    size_t bytes_reserved() const;
+
+private:
+    struct Block { void *p; size_t size; };
+    std::vector<Block> blocks_;
+    size_t block_bytes_, block_ = 0, offset_ = 0;
+    bool frozen_ = false;
+};
+
+// Device memory that lives as long as its owner.
+class DeviceBuffer {
+public:
+    DeviceBuffer() = default;
+    explicit DeviceBuffer(size_t bytes, const char *what = "device memory");
+    ~DeviceBuffer();
+    DeviceBuffer(DeviceBuffer &&o) noexcept : p_(o.p_), bytes_(o.bytes_) { o.p_ = nullptr; o.bytes_ = 0; }
+    DeviceBuffer &operator=(DeviceBuffer &&o) noexcept;
+    DeviceBuffer(const DeviceBuffer &) = delete;
+    void *get() const { return p_; }
+    size_t bytes() const { return bytes_; }
+
+private:
+    void *p_ = nullptr;
+    size_t bytes_ = 0;
+};
+
+// ---- small kernels of the host library (host_kernels.cu)
+void dev_convert(const void *src, int src_dtype, void *dst, int dst_dtype, int64_t n, cudaStream_t s);
+// dst[r, :] = src[rows[r], :] (rows on the host, uploaded by the call); cols elements of `dtype`
+void dev_gather_rows(const void *src, void *dst, const std::vector<int64_t> &rows, int64_t cols, int dtype, cudaStream_t s);
+void dev_fill_random(void *dst, int dtype, int64_t n, uint64_t seed, uint64_t name_hash, int init, float std, cudaStream_t s);
+void dev_scale_f32(float *x, int64_t n, float scale, cudaStream_t s);
+
+}  // namespace fg

@@ -1,4 +1,4 @@
-"""Model assembly, the step function, generation and the entry points."""
+"""The entry points: a loaded model with its cache (``Engine``), steps, generation."""
 from .batch import StepEntry
 from .spec import LayerSpec, ModelSpec, PartSpec, RunSpec
 

@@ -38,7 +38,7 @@ TINY = {"a": (TINY_A, 0), "b": (TINY_B, 1), "c": (TINY_C, 2), "d": (TINY_D, 3), 
 def make_model_dir(tmp_path, cfg_dict, seed, dtype=torch.bfloat16):
     """Write a random model folder under tmp_path; returns its path."""
     from fastgguf_b200.registry import config_from_dict
-    from fastgguf_b200.weights.random_init import write_random_model
+    from fastgguf_b200.weights import write_random_model
     return write_random_model(config_from_dict(cfg_dict), seed, str(tmp_path), dtype)
 
 

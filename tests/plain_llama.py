@@ -4,7 +4,7 @@ cache, one function for each part, CPU only.  It shares no code with ``fastgguf_
 parses config.json and reads the safetensors file with its own few lines.
 
 Compared once with the reference's own C code on a tiny random model: see
-``tests/golden/make_golden.py`` and ``tests/test_plain_vs_reference.py``.
+``tests/golden/make_golden.py`` and ``tests/test_plain.py``.
 
 Precision: ``dtype=torch.float64`` (default) makes it an oracle whose own rounding is
 negligible; ``torch.float32`` follows the reference's mix (float everywhere, double for the
@@ -23,11 +23,9 @@ _ST_DTYPES = {"F32": torch.float32, "BF16": torch.bfloat16, "F16": torch.float16
 
 
 # ------------------------------------------------------------------------------ reading
-def read_model_folder(model_dir):
-    """(config dict, {tensor name: float32 CPU tensor}) of a model folder."""
-    with open(os.path.join(model_dir, "config.json")) as f:
-        cfg = json.load(f)
-    with open(os.path.join(model_dir, "model.safetensors"), "rb") as f:
+def read_safetensors(path):
+    """{tensor name: CPU tensor in its stored dtype} of one safetensors file."""
+    with open(path, "rb") as f:
         (hlen,) = struct.unpack("<Q", f.read(8))
         header = json.loads(f.read(hlen))
         data = f.read()
@@ -36,8 +34,38 @@ def read_model_folder(model_dir):
         if name == "__metadata__":
             continue
         b, e = info["data_offsets"]
-        t = torch.frombuffer(bytearray(data[b:e]), dtype=_ST_DTYPES[info["dtype"]]).reshape(info["shape"])
-        tensors[name] = t.to(torch.float32) if t.dtype.is_floating_point else t
+        if e == b:
+            tensors[name] = torch.empty(info["shape"], dtype=_ST_DTYPES[info["dtype"]])
+            continue
+        tensors[name] = torch.frombuffer(bytearray(data[b:e]), dtype=_ST_DTYPES[info["dtype"]]).reshape(info["shape"])
+    return tensors
+
+
+def write_safetensors(path, tensors):
+    """The tests' own writer (for files with faults the engine's reader must name)."""
+    names = {v: k for k, v in _ST_DTYPES.items()}
+    header, off = {}, 0
+    for name in sorted(tensors):
+        t = tensors[name]
+        n = t.numel() * t.element_size()
+        header[name] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + n]}
+        off += n
+    blob = json.dumps(header, separators=(",", ":")).encode()
+    blob += b" " * ((8 - len(blob) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(blob)) + blob)
+        for name in sorted(tensors):
+            t = tensors[name].detach().contiguous()
+            if t.numel():
+                f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes())
+
+
+def read_model_folder(model_dir):
+    """(config dict, {tensor name: float32 CPU tensor}) of a model folder."""
+    with open(os.path.join(model_dir, "config.json")) as f:
+        cfg = json.load(f)
+    tensors = {k: (t.to(torch.float32) if t.dtype.is_floating_point else t)
+               for k, t in read_safetensors(os.path.join(model_dir, "model.safetensors")).items()}
     return cfg, tensors
 
 

@@ -2,26 +2,34 @@
 import random
 
 import pytest
-import torch
 
-from fastgguf_b200.cache import CacheError, CacheFull, PagedKVCache, StatePool
-from fastgguf_b200.parts.base import CacheRequest, StateRequest
+from fastgguf_b200.cache import CacheError, CacheFull, CacheRequest, PagedKVCache, cache_bytes
 
 
 def make(requests=None, **kw):
     requests = requests or {0: CacheRequest(2, 16), 1: CacheRequest(2, 16)}
-    args = dict(max_tokens=640, max_seq_len=512, n_slots=4, allocate=False)
+    args = dict(max_tokens=640, max_seq_len=512, n_slots=4)
     args.update(kw)
     return PagedKVCache(requests, **args)
 
 
 def test_groups_share_requests_and_have_storage_of_their_own():
-    c = PagedKVCache({0: CacheRequest(2, 16), 1: CacheRequest(2, 16, window=100), 2: CacheRequest(2, 16),
-                      3: CacheRequest(1, 32)}, max_tokens=256, max_seq_len=256, n_slots=2,
-                     dtype=torch.float32, device=torch.device("cpu"))
-    assert len(c.groups) == 3 and c.groups[0].entries == [0, 2] and c.group_of_entry == {0: 0, 1: 1, 2: 0, 3: 2}
-    assert c.groups[0].k_pools[0].shape == (5, 2, 64, 16) and c.groups[2].v_pools[3].shape == (5, 1, 64, 32)
-    assert c.groups[0].k_pools[0].data_ptr() != c.groups[0].k_pools[2].data_ptr()
+    req = {0: CacheRequest(2, 16), 1: CacheRequest(2, 16, window=100), 2: CacheRequest(2, 16), 3: CacheRequest(1, 32)}
+    c = PagedKVCache(req, max_tokens=256, max_seq_len=256, n_slots=2)
+    assert len(c.groups) == 3 and c.groups[0]["entries"] == [0, 2] and c.group_of_entry == {0: 0, 1: 1, 2: 0, 3: 2}
+    assert [g["pages"] for g in c.groups] == [4, 4, 4] and c.groups[1]["window"] == 100 and c.groups[0]["window"] is None
+    # a pool per entry: [pages + the reserved page 0, KV heads, 64, head size], keys and values, 4 bytes each
+    b = cache_bytes(req, 256, dtype="float32")
+    assert b["bytes"] == 2 * 4 * 5 * 64 * (3 * 2 * 16 + 1 * 32) and b["pages"] == 4
+    assert b["bytes_per_token"] == 2 * 4 * (3 * 2 * 16 + 1 * 32)
+
+
+def test_cache_memory_of_the_benchmark_models():
+    """Keys and values of one token over all layers, in bfloat16: 32 / 112 / 128 KiB for the 1B / 3B / 8B sizes."""
+    for layers, kv, hd, kib in ((16, 8, 64, 32), (28, 8, 128, 112), (32, 8, 128, 128)):
+        b = cache_bytes({i: CacheRequest(kv, hd) for i in range(layers)}, 4096)
+        assert b["bytes_per_token"] == kib * 1024
+        assert b["bytes"] == (4096 // 64 + 1) * 64 * kib * 1024
 
 
 def test_pages_follow_lengths_and_come_back():
@@ -90,7 +98,7 @@ def test_longest_sequence_limit():
 
 def test_windowed_group_gives_pages_back():
     c = PagedKVCache({0: CacheRequest(1, 16), 1: CacheRequest(1, 16, window=70)}, max_tokens=2048, max_seq_len=2048,
-                     n_slots=2, allocate=False)
+                     n_slots=2)
     s = c.acquire()
     c.reserve([(s, 300)])
     assert c.free_pages(0) == 32 - 5 and c.free_pages(1) == 32 - 5     # a long prompt needs all its pages for the step
@@ -144,12 +152,3 @@ def test_random_traffic_keeps_the_invariants():
         c.release(s)
     c.check()
     assert c.free_pages() == 12
-
-
-def test_state_pool_rows_are_zeroed_on_reset():
-    p = StatePool({2: StateRequest((3, 4)), 5: StateRequest((2,), torch.int32)}, n_slots=3, device=torch.device("cpu"))
-    assert p.of(2).shape == (3, 3, 4) and p.of(5).dtype == torch.int32 and p.of(0) is None
-    p.of(2)[1] += 7.0
-    p.of(5)[1] += 3
-    p.reset(1)
-    assert p.of(2)[1].abs().sum() == 0 and p.of(5)[1].sum() == 0

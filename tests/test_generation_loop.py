@@ -1,7 +1,8 @@
-"""The generation loop's decisions, driven by a fake backend on the CPU."""
+"""The generation loop's decisions - the host's ``run_batch`` and ``run_batch_late`` - driven by a fake backend on
+the CPU through the C interface's callbacks."""
 import pytest
 
-from fastgguf_b200.engine.generate import plan_batches, run_batch
+from fastgguf_b200.engine.generate import plan_batches, run_batch, run_batch_late
 
 
 class FakeBackend:
@@ -46,6 +47,29 @@ def test_plan_batches():
     assert plan_batches(0, 4) == []
     with pytest.raises(ValueError):
         plan_batches(3, 0)
+
+
+def test_status_codes_of_the_c_interface():
+    """Every exported function returns a status; the message of the last failure is kept for the caller."""
+    import ctypes
+    from fastgguf_b200 import capi
+    l = capi.lib()
+    out = ctypes.c_void_p()
+    assert l.fg_config_from_json(None, ctypes.byref(out)) == capi.E_USAGE and b"null" in l.fg_last_error()
+    assert l.fg_config_from_json(b"{nope", ctypes.byref(out)) == capi.E_CONFIG and b"not valid JSON" in l.fg_last_error()
+    assert l.fg_config_from_json(b'{"architectures": ["Nope"]}', ctypes.byref(out)) == capi.E_CONFIG
+    assert l.fg_cache_create(b"[]", 0, 64, 1, 64, ctypes.byref(out)) == capi.E_USAGE
+    assert l.fg_cache_create(b'[{"entry": 0, "n_kv_heads": 1, "head_dim": 16}]', 64, 64, 1, 64, ctypes.byref(out)) == capi.OK
+    slot, n = ctypes.c_int(), ctypes.c_int()
+    assert l.fg_cache_acquire(out, ctypes.byref(slot)) == capi.OK and slot.value == 0
+    assert l.fg_cache_acquire(out, ctypes.byref(slot)) == capi.E_CAPACITY and b"slots" in l.fg_last_error()
+    assert l.fg_cache_length(out, 7, ctypes.byref(n)) == capi.E_CACHE
+    one, many = (ctypes.c_int * 1)(0), (ctypes.c_int * 1)(500)
+    assert l.fg_cache_reserve(out, 1, one, many) == capi.E_CAPACITY          # beyond the longest sequence
+    assert l.fg_cache_check(out) == capi.OK
+    l.fg_cache_destroy(out)
+    assert l.fg_spec_tensors(b'{"hidden_size": 8}', ctypes.byref(out)) == capi.E_CONFIG
+    assert l.fg_register_part(2, b"x", None) == capi.E_USAGE
 
 
 def test_prompts_in_one_step_then_one_token_each():
@@ -111,71 +135,34 @@ def test_request_seeds_and_sampling_params():
     assert SamplingParams(temp=0).greedy and not SamplingParams().penalizes and SamplingParams(repeat_penalty=1.2).penalizes
 
 
-def test_device_error_flags_are_raised_and_only_loaded_libraries_are_asked(monkeypatch):
-    """A bounded wait that ran out inside a kernel leaves a flag behind; the host turns it into an exception."""
-    import importlib
-    oplib = importlib.import_module("fastgguf_b200.ops.lib")
+class FakeSession:
+    """The device of the graph path replaced by scripts: it goes on past a stop token, as the device does."""
 
-    class FakeLib:
-        def __init__(self, code):
-            self.code, self.reads = code, 0
+    def __init__(self, scripts, prompts, first_index=0):
+        self.scripts, self.n = scripts, len(prompts)
+        self.idx = [first_index + i for i in range(self.n)]
+        self.cursor = [1] * self.n
+        self.first_tokens = [scripts[j][0] for j in self.idx]
+        self.advanced, self.closed = [], 0
 
-        def fg_gemm_tc_error(self):
-            self.reads += 1
-            code, self.code = self.code, 0           # reading clears the flag, as the library does
-            return code
+    def advance(self, live):
+        self.advanced.append(list(live))
+        toks = [0] * self.n
+        for i in live:
+            s = self.scripts[self.idx[i]]
+            toks[i] = s[self.cursor[i]] if self.cursor[i] < len(s) else 0
+            self.cursor[i] += 1
+        return toks
 
-    monkeypatch.setattr(oplib, "_libs", {})
-    oplib.raise_on_device_error("nothing loaded")     # no library loaded: nothing is built or asked
-    fake = FakeLib((10003 << 8) | 2)
-    monkeypatch.setattr(oplib, "_libs", {"tc": fake})
-    with pytest.raises(oplib.KernelError, match="role 2"):
-        oplib.raise_on_device_error("prompt step")
-    oplib.raise_on_device_error("prompt step")        # cleared by the read
-    assert fake.reads == 2
-
-
-class _FakeEvent:
-    def synchronize(self):
-        pass
+    def close(self):
+        self.closed += 1
 
 
-class _HostTokens(list):
-    def tolist(self):
-        return list(self)
-
-
-def _graph_path(monkeypatch, scripts, prompts, first_index, max_tokens, stop_ids, capacity=1000, on_token=None):
+def _graph_path(scripts, prompts, first_index, max_tokens, stop_ids, capacity=1000, on_token=None):
     """The graph path's host loop (tokens are seen one step late) with the device replaced by scripts."""
-    from types import SimpleNamespace
-    from fastgguf_b200.engine import runner
-    log = SimpleNamespace(advanced=[], closed=0)
-
-    class FakeSession:
-        def __init__(self, backend, prompts, first_index=0):
-            self.n = len(prompts)
-            self.idx = [first_index + i for i in range(self.n)]
-            self.cursor = [1] * self.n
-            self.first_tokens = [scripts[j][0] for j in self.idx]
-
-        def advance(self, live):
-            log.advanced.append(list(live))
-            toks = [0] * self.n
-            for i in live:
-                s = scripts[self.idx[i]]
-                toks[i] = s[self.cursor[i]] if self.cursor[i] < len(s) else 0      # the device goes on past a stop token
-                self.cursor[i] += 1
-            return _HostTokens(toks), _FakeEvent()
-
-        def close(self):
-            log.closed += 1
-
-    monkeypatch.setattr(runner, "DecodeSession", FakeSession)
-    monkeypatch.setattr(runner.ops, "raise_on_device_error", lambda *a, **k: None)
-    backend = object.__new__(runner.EngineBackend)
-    backend.engine = SimpleNamespace(cache=SimpleNamespace(max_seq_len=capacity))
-    out = backend._run_batch_graphs(prompts, first_index, max_tokens, stop_ids, on_token)
-    return out, log
+    session = FakeSession(scripts, prompts, first_index)
+    out = run_batch_late(session, prompts, first_index, max_tokens, stop_ids, capacity, on_token)
+    return out, session
 
 
 @pytest.mark.parametrize("scripts,prompts,max_tokens,stop,capacity", [
@@ -185,12 +172,11 @@ def _graph_path(monkeypatch, scripts, prompts, first_index, max_tokens, stop_ids
     ({0: [5, 6, 7, 8, 9, 10, 11], 1: [99, 1, 1, 1, 1, 1, 1], 2: [7, 7, 99, 3, 3, 3, 3]}, [[1] * 4, [2] * 2, [3]], 6, (99,), 1000),
     ({0: [1, 2, 3, 4, 5, 6, 7, 8], 1: [9, 9, 9, 9, 9, 9, 9, 9]}, [[1, 2, 3, 4, 5], [6]], 0, (), 8),     # the cache fills up
 ])
-def test_graph_path_decides_as_the_plain_loop_does(monkeypatch, scripts, prompts, max_tokens, stop, capacity):
+def test_graph_path_decides_as_the_plain_loop_does(scripts, prompts, max_tokens, stop, capacity):
     plain = run_batch(FakeBackend({k: list(v) + [0] * 8 for k, v in scripts.items()}, capacity=capacity), prompts, 0,
                       max_tokens=max_tokens, stop_ids=stop)
     seen = []
-    out, log = _graph_path(monkeypatch, scripts, prompts, 0, max_tokens, stop, capacity,
-                           on_token=lambda r, t: seen.append((r, t)))
+    out, log = _graph_path(scripts, prompts, 0, max_tokens, stop, capacity, on_token=lambda r, t: seen.append((r, t)))
     assert [(c.tokens, c.finish_reason) for c in out] == [(c.tokens, c.finish_reason) for c in plain]
     assert log.closed == 1
     # every token is reported once, in order, and stop tokens are not

@@ -1,4 +1,6 @@
-"""Weights: the safetensors container, loading by name with one error, dtype policy, random folders."""
+"""Weights: the safetensors container, loading by name with one error, dtype policy, random folders.
+Everything here runs on the host (the C++ reader and checker behind ``fastgguf_b200.weights``); the files
+are written and read back by the test's own small safetensors code in ``plain_llama``."""
 import json
 import os
 import struct
@@ -6,140 +8,150 @@ import struct
 import pytest
 import torch
 
+import plain_llama
 from helpers import TINY_A, TINY_B, make_model_dir
 
 
-def _expected(cfg_dict, dtype=torch.bfloat16):
-    from fastgguf_b200.engine.model import DecoderModel
-    from fastgguf_b200.parts.base import Runtime
-    from fastgguf_b200.registry import config_from_dict, spec_from_config
-    model = DecoderModel(spec_from_config(config_from_dict(cfg_dict)), Runtime(torch.device("cpu"), dtype))
-    return model
+def _config(cfg_dict):
+    from fastgguf_b200.registry import config_from_dict
+    return config_from_dict(cfg_dict)
 
 
-def test_safetensors_round_trip(tmp_path):
-    from fastgguf_b200.weights import SafetensorsFile, write_safetensors
+def _random_tensors(tmp_path, cfg_dict, seed):
+    d = make_model_dir(tmp_path / f"src{seed}", cfg_dict, seed)
+    return plain_llama.read_safetensors(os.path.join(d, "model.safetensors"))
+
+
+def test_folder_tensors_reads_what_was_written(tmp_path):
+    from fastgguf_b200.weights import folder_tensors
     t = {"a": torch.randn(3, 5).to(torch.bfloat16), "b.c": torch.arange(7, dtype=torch.int32),
          "d": torch.randn(2, 2, 2), "e": torch.zeros(0, 4)}
-    path = str(tmp_path / "x.safetensors")
-    write_safetensors(path, t, {"k": "v"})
-    f = SafetensorsFile(path)
-    assert sorted(f.names()) == sorted(t) and f.metadata == {"k": "v"}
-    for k, v in t.items():
-        assert torch.equal(f.tensor(k), v) and f.tensor(k).dtype == v.dtype
+    plain_llama.write_safetensors(str(tmp_path / "model.safetensors"), t)
+    got = {e["name"]: e for e in folder_tensors(str(tmp_path))}
+    assert sorted(got) == sorted(t)
+    assert got["a"] == {"name": "a", "dtype": "bfloat16", "shape": [3, 5]}
+    assert got["b.c"]["dtype"] == "int32" and got["d"]["shape"] == [2, 2, 2] and got["e"]["shape"] == [0, 4]
 
 
 def test_container_errors(tmp_path):
-    from fastgguf_b200.weights import SafetensorsError, SafetensorsFile
-    p = str(tmp_path / "m.safetensors")
-    with pytest.raises(SafetensorsError, match="cannot open"):
-        SafetensorsFile(p)
+    from fastgguf_b200.weights import SafetensorsError, folder_tensors
+    p = str(tmp_path / "model.safetensors")
+    with pytest.raises(SafetensorsError, match="neither model.safetensors"):
+        folder_tensors(str(tmp_path))
     open(p, "wb").write(b"abc")
     with pytest.raises(SafetensorsError, match="too short"):
-        SafetensorsFile(p)
+        folder_tensors(str(tmp_path))
     open(p, "wb").write(struct.pack("<Q", 1000) + b"{}")
     with pytest.raises(SafetensorsError, match="header length"):
-        SafetensorsFile(p)
+        folder_tensors(str(tmp_path))
     open(p, "wb").write(struct.pack("<Q", 5) + b"{nope")
     with pytest.raises(SafetensorsError, match="not valid JSON"):
-        SafetensorsFile(p)
+        folder_tensors(str(tmp_path))
 
     def with_header(h, data=b"\0" * 8):
         blob = json.dumps(h).encode()
         open(p, "wb").write(struct.pack("<Q", len(blob)) + blob + data)
+
     with_header({"w": {"dtype": "F32", "shape": [4], "data_offsets": [0, 16]}})
     with pytest.raises(SafetensorsError, match="extends past the end"):
-        SafetensorsFile(p)
+        folder_tensors(str(tmp_path))
     with_header({"w": {"dtype": "Q4_K", "shape": [2], "data_offsets": [0, 8]}})
     with pytest.raises(SafetensorsError, match="unsupported type Q4_K"):
-        SafetensorsFile(p)
+        folder_tensors(str(tmp_path))
     with_header({"w": {"dtype": "F32", "shape": [3], "data_offsets": [0, 8]}})
     with pytest.raises(SafetensorsError, match="needs 12 bytes"):
-        SafetensorsFile(p)
+        folder_tensors(str(tmp_path))
     with_header({"w": {"dtype": "F32"}})
     with pytest.raises(SafetensorsError, match="malformed"):
-        SafetensorsFile(p)
+        folder_tensors(str(tmp_path))
+
+
+def test_shards_and_a_tensor_in_two_of_them(tmp_path):
+    from fastgguf_b200.weights import SafetensorsError, folder_tensors
+    plain_llama.write_safetensors(str(tmp_path / "s1.safetensors"), {"a": torch.zeros(2), "b": torch.zeros(3)})
+    plain_llama.write_safetensors(str(tmp_path / "s2.safetensors"), {"c": torch.zeros(4)})
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(
+        {"weight_map": {"a": "s1.safetensors", "b": "s1.safetensors", "c": "s2.safetensors"}}))
+    assert [e["name"] for e in folder_tensors(str(tmp_path))] == ["a", "b", "c"]
+    plain_llama.write_safetensors(str(tmp_path / "s2.safetensors"), {"c": torch.zeros(4), "a": torch.zeros(2)})
+    with pytest.raises(SafetensorsError, match="is also in"):
+        folder_tensors(str(tmp_path))
+    (tmp_path / "model.safetensors.index.json").write_text("{}")
+    with pytest.raises(SafetensorsError, match="not a shard index"):
+        folder_tensors(str(tmp_path))
 
 
 def test_one_error_lists_missing_unexpected_and_wrong(tmp_path):
-    from fastgguf_b200.weights import FolderSource, WeightError, load_tensors, random_tensors, write_safetensors
-    from fastgguf_b200.registry import config_from_dict
-    cfg = config_from_dict(TINY_B)
-    model = _expected(TINY_B)
-    t = random_tensors(cfg, 1)
+    from fastgguf_b200.weights import WeightError, check_weights
+    cfg = _config(TINY_B)
+    t = _random_tensors(tmp_path, TINY_B, 1)
     del t["model.layers.1.mlp.up_proj.weight"], t["model.norm.weight"]
     t["model.layers.0.self_attn.q_proj.bias"] = torch.zeros(144)
     t["model.layers.2.self_attn.k_proj.weight"] = torch.zeros(48, 144, dtype=torch.bfloat16)
     t["model.embed_tokens.weight"] = torch.zeros(509, 144, dtype=torch.int32)
-    write_safetensors(str(tmp_path / "model.safetensors"), t)
-    with pytest.raises(WeightError) as e:
-        load_tensors(FolderSource(str(tmp_path)), model.expected_tensors(), torch.bfloat16, torch.device("cpu"))
-    err = e.value
-    assert err.missing == ["model.layers.1.mlp.up_proj.weight", "model.norm.weight"]
-    assert err.unexpected == ["model.layers.0.self_attn.q_proj.bias"]
-    assert len(err.wrong) == 2 and "[48, 144]" in str(err) and "[24, 144]" in str(err)
-    for name in err.missing + err.unexpected:
-        assert name in str(err)
+    plain_llama.write_safetensors(str(tmp_path / "model.safetensors"), t)
+    for kwargs in (dict(model_dir=str(tmp_path)), dict(tensors=t)):           # a folder, and tensors in memory
+        with pytest.raises(WeightError) as e:
+            check_weights(cfg, **kwargs)
+        err = e.value
+        assert err.missing == ["model.layers.1.mlp.up_proj.weight", "model.norm.weight"]
+        assert err.unexpected == ["model.layers.0.self_attn.q_proj.bias"]
+        assert len(err.wrong) == 2 and "[48, 144]" in str(err) and "[24, 144]" in str(err)
+        for name in err.missing + err.unexpected:
+            assert name in str(err)
 
 
 def test_dtype_policy(tmp_path):
     """16-bit tensors become bfloat16, a tensor stored in 32 bits stays so; float32 engines widen all."""
-    from fastgguf_b200.weights import FolderSource, load_tensors, random_tensors, write_safetensors
-    from fastgguf_b200.registry import config_from_dict
-    t = random_tensors(config_from_dict(TINY_A), 0)
+    from fastgguf_b200.weights import check_weights
+    cfg = _config(TINY_A)
+    t = _random_tensors(tmp_path, TINY_A, 0)
     t["model.norm.weight"] = t["model.norm.weight"].float()
     t["model.layers.0.mlp.down_proj.weight"] = t["model.layers.0.mlp.down_proj.weight"].to(torch.float16)
-    write_safetensors(str(tmp_path / "model.safetensors"), t)
-    exp = _expected(TINY_A).expected_tensors()
-    got = load_tensors(FolderSource(str(tmp_path)), exp, torch.bfloat16, torch.device("cpu"))
-    assert got["model.norm.weight"].dtype == torch.float32
-    assert got["model.layers.0.mlp.down_proj.weight"].dtype == torch.bfloat16
-    assert got["model.embed_tokens.weight"].dtype == torch.bfloat16
-    wide = load_tensors(FolderSource(str(tmp_path)), exp, torch.float32, torch.device("cpu"))
-    assert all(v.dtype == torch.float32 for v in wide.values())
-    assert torch.equal(wide["model.embed_tokens.weight"], t["model.embed_tokens.weight"].float())
+    plain_llama.write_safetensors(str(tmp_path / "model.safetensors"), t)
+    got = check_weights(cfg, model_dir=str(tmp_path), dtype="bfloat16")
+    assert got["model.norm.weight"] == "float32"
+    assert got["model.layers.0.mlp.down_proj.weight"] == "bfloat16"
+    assert got["model.embed_tokens.weight"] == "bfloat16"
+    wide = check_weights(cfg, model_dir=str(tmp_path), dtype="float32")
+    assert set(wide.values()) == {"float32"}
 
 
 def test_tied_head_ignores_a_stored_lm_head_and_untied_needs_it(tmp_path):
-    from fastgguf_b200.weights import FolderSource, WeightError, load_tensors, random_tensors, write_safetensors
-    from fastgguf_b200.registry import config_from_dict, spec_from_config
-    cfg = config_from_dict(TINY_A)
-    t = random_tensors(cfg, 0)
-    assert "lm_head.weight" not in t
+    from fastgguf_b200.weights import WeightError, check_weights, expected_tensors
+    cfg = _config(TINY_A)
+    t = _random_tensors(tmp_path, TINY_A, 0)
+    assert "lm_head.weight" not in t and "lm_head.weight" not in expected_tensors(cfg)
     t["lm_head.weight"] = torch.zeros(256, 64, dtype=torch.bfloat16)
-    write_safetensors(str(tmp_path / "model.safetensors"), t)
-    spec = spec_from_config(cfg)
-    load_tensors(FolderSource(str(tmp_path)), _expected(TINY_A).expected_tensors(), torch.bfloat16,
-                 torch.device("cpu"), spec.ignored_tensors)
+    plain_llama.write_safetensors(str(tmp_path / "model.safetensors"), t)
+    check_weights(cfg, model_dir=str(tmp_path))
     # untied: the same file loads, and the head is the stored tensor
-    got = load_tensors(FolderSource(str(tmp_path)), _expected(dict(TINY_A, tie_word_embeddings=False)).expected_tensors(),
-                       torch.bfloat16, torch.device("cpu"))
-    assert "lm_head.weight" in got
+    untied = _config(dict(TINY_A, tie_word_embeddings=False))
+    assert "lm_head.weight" in check_weights(untied, model_dir=str(tmp_path))
     del t["lm_head.weight"]
-    write_safetensors(str(tmp_path / "model.safetensors"), t)
+    plain_llama.write_safetensors(str(tmp_path / "model.safetensors"), t)
     with pytest.raises(WeightError) as e:
-        load_tensors(FolderSource(str(tmp_path)), _expected(dict(TINY_A, tie_word_embeddings=False)).expected_tensors(),
-                     torch.bfloat16, torch.device("cpu"))
+        check_weights(untied, model_dir=str(tmp_path))
     assert e.value.missing == ["lm_head.weight"]
 
 
 def test_random_model_folder_is_deterministic(tmp_path):
-    from fastgguf_b200.weights import SafetensorsFile
     a = make_model_dir(tmp_path / "a", TINY_B, 5)
     b = make_model_dir(tmp_path / "b", TINY_B, 5)
     c = make_model_dir(tmp_path / "c", TINY_B, 6)
-    fa, fb, fc = (SafetensorsFile(os.path.join(d, "model.safetensors")) for d in (a, b, c))
-    assert sorted(fa.names()) == sorted(fb.names())
-    assert all(torch.equal(fa.tensor(n), fb.tensor(n)) for n in fa.names())
-    assert not torch.equal(fa.tensor("lm_head.weight"), fc.tensor("lm_head.weight"))
+    fa, fb, fc = (plain_llama.read_safetensors(os.path.join(d, "model.safetensors")) for d in (a, b, c))
+    assert sorted(fa) == sorted(fb)
+    assert all(torch.equal(fa[n], fb[n]) for n in fa)
+    assert not torch.equal(fa["lm_head.weight"], fc["lm_head.weight"])
+    # a tensor's values depend on (seed, its name) alone: two tensors of one folder differ
+    assert not torch.equal(fa["model.layers.0.mlp.up_proj.weight"], fa["model.layers.1.mlp.up_proj.weight"])
     cfg = json.load(open(os.path.join(a, "config.json")))
-    assert cfg["architectures"] == ["LlamaForCausalLM"] and cfg["hidden_size"] == 144
-    w = fa.tensor("model.layers.0.mlp.up_proj.weight").float()
-    n = fa.tensor("model.norm.weight").float()
-    assert abs(w.std().item() - 0.02) < 0.002 and abs(n.mean().item() - 1.0) < 0.01 and 0.005 < n.std().item() < 0.02
-
-
-def test_missing_weight_file(tmp_path):
-    from fastgguf_b200.weights import FolderSource, SafetensorsError
-    with pytest.raises(SafetensorsError, match="neither model.safetensors"):
-        FolderSource(str(tmp_path))
+    assert cfg["architectures"] == ["LlamaForCausalLM"] and cfg["hidden_size"] == 144 and cfg["torch_dtype"] == "bfloat16"
+    w = fa["model.layers.0.mlp.up_proj.weight"].float()
+    n = fa["model.norm.weight"].float()
+    assert abs(w.std().item() - 0.02) < 0.002 and abs(w.mean().item()) < 0.001
+    assert abs(n.mean().item() - 1.0) < 0.01 and 0.005 < n.std().item() < 0.02
+    # float32 folders hold the values the bfloat16 ones were rounded from
+    f32 = plain_llama.read_safetensors(os.path.join(make_model_dir(tmp_path / "f", TINY_B, 5, "float32"), "model.safetensors"))
+    assert f32["lm_head.weight"].dtype == torch.float32
+    assert torch.equal(f32["lm_head.weight"].to(torch.bfloat16), fa["lm_head.weight"])
