@@ -47,12 +47,12 @@ TOKENS = [(i * 37 + 11) % 67 for i in range(24)]
 def main():
     ref_dir = sys.argv[1]
     from fastgguf_b200.registry import config_from_dict
-    from fastgguf_b200.weights.random_init import write_random_model
+    from fastgguf_b200.weights import write_random_model
     import plain_llama
     from gguf import GGUFWriter
 
     model_dir = os.path.join(HERE, "tiny_model")
-    write_random_model(config_from_dict(CONFIG), seed=3, out_dir=model_dir, dtype=torch.float32)
+    write_random_model(config_from_dict(CONFIG), 3, model_dir, "float32")
     cfg, W = plain_llama.read_model_folder(model_dir)
     E, H, KV, hd = plain_llama.sizes(cfg)
 

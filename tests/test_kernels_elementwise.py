@@ -37,13 +37,13 @@ def test_rmsnorm(M, E, eps, out_dtype, tol):
 @pytest.mark.parametrize("H,KV,hd", [(3, 1, 8), (4, 2, 48), (2, 2, 128)])
 def test_rope_append(H, KV, hd, dtype, tol):
     """q rotated in place; k rotated and v copied into the right page, KV head and offset."""
+    from types import SimpleNamespace
     from fastgguf_b200 import ops
-    from fastgguf_b200.parts.base import Runtime
-    from fastgguf_b200.parts.rope import RotaryEncoding
+    from fastgguf_b200.parts import position_tables
     scaling = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                "original_max_position_embeddings": 64}
-    rope = RotaryEncoding(Runtime(torch.device("cuda"), dtype), hd, 500000.0, scaling)
-    rope.prepare(400)
+    cos, sin, _ = position_tables("rope", dict(head_dim=hd, theta=500000.0, scaling=scaling), 400)
+    rope = SimpleNamespace(cos=torch.from_numpy(cos).cuda(), sin=torch.from_numpy(sin).cuda())
     cfg = {"rope_theta": 500000.0, "rope_scaling": scaling}
     positions = [0, 1, 63, 64, 200, 399, 5]
     row_seq = [0, 0, 0, 0, 1, 1, 2]
