@@ -140,11 +140,10 @@ static int launch_prefill(const void *q, int ldq, void *out, int ldo, const int 
                           const int *block_table, int table_width, const void *k_pool, const void *v_pool,
                           int n_seq, int max_new, int H, int KV, float scale, int window, cudaStream_t stream) {
     constexpr int smem = 2 * 2 * PAGE * HD * 2;
-    static bool configured = false;
-    if (!configured) {
+    static FgPerDevice configured;
+    if (fg_needs_setup(configured)) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD, PF_WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     int G = H / KV, Gc = G < 16 ? G : 16, TQ = PF_WARPS * 16 / Gc;
     dim3 grid((max_new + TQ - 1) / TQ, KV * ((G + Gc - 1) / Gc), n_seq);

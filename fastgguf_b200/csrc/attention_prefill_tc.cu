@@ -37,6 +37,9 @@
 #define LOG2E 1.4426950408889634f
 
 __device__ int g_attn_error = 0;
+// how long a wait may last, in SM cycles; a variable so that a test can shorten it (fg_attention_prefill_tc_test_hook)
+__device__ long long g_attn_wait_limit = WAIT_LIMIT_CYCLES;
+static int g_test_skip_copy = 0;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -58,10 +61,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
                      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
         const long long waited = clock64() - t0;
-        if (waited > WAIT_LIMIT_CYCLES) return false;
-        // once a wait has run out somewhere, every later wait gives up after a short time: a broken pipeline
-        // costs milliseconds for the kernels that follow, not a second per wait
-        if (waited > WAIT_SHORT_CYCLES && *(volatile int *)&g_attn_error != 0) return false;
+        if (waited > WAIT_SHORT_CYCLES) {
+            // once a wait has run out somewhere, every later wait gives up after a short time: a broken pipeline
+            // costs milliseconds for the kernels that follow, not a second per wait
+            if (*(volatile int *)&g_attn_error != 0) return false;
+            if (waited > *(volatile long long *)&g_attn_wait_limit) return false;
+        }
     }
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
@@ -137,7 +142,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)                  // two CTAs s
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                        const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out, int ldo,
                        const int *__restrict__ cu_rows, const int *__restrict__ seq_start,
-                       const int *__restrict__ block_table, int table_width, int KV, int G, float scale_log2, int window) {
+                       const int *__restrict__ block_table, int table_width, int KV, int G, float scale_log2, int window,
+                       int test_skip_copy) {
     constexpr int CH = HD / 64;                        // 64-wide chunks of the head dimension
     constexpr int KEYS = HD > 64 ? 64 : 128, NPG = KEYS / PAGE;      // keys and pages per iteration
     constexpr int Q_BYTES = ROWS * HD * 2, KV_TILE = KEYS * HD * 2;
@@ -213,8 +219,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             if (!__all_sync(0xffffffffu, mbar_wait(k_empty, (j & 1) ^ 1))) { raise_error(1); break; }
             if (elect_one()) {
                 mbar_expect_tx(k_full, KV_TILE);
-                for (int h = 0; h < NPG; h++)
-                    for (int c = 0; c < CH; c++) tma_load_2d(kt + c * (KEYS * 128) + h * (PAGE * 128), &tmK, c * 64, y[h], k_full);
+                // (a test may ask for the first K tile to stay incomplete: its barrier never fires and every wait runs out)
+                if (!(test_skip_copy && j == 0))
+                    for (int h = 0; h < NPG; h++)
+                        for (int c = 0; c < CH; c++) tma_load_2d(kt + c * (KEYS * 128) + h * (PAGE * 128), &tmK, c * 64, y[h], k_full);
             }
             __syncwarp();
             k_issued = j + 1;
@@ -449,17 +457,20 @@ static int launch_tc(const CUtensorMap &tmK, const CUtensorMap &tmV, const void 
                      int max_new, int H, int KV, float scale, int window, cudaStream_t stream) {
     constexpr int KEYS = HD > 64 ? 64 : 128;
     constexpr int smem = ROWS * HD * 2 + 2 * KEYS * HD * 2 + ROWS * KEYS * 2 + 1024;
-    static bool configured = false;
-    if (!configured) {
+    // the attributes belong to the function on ONE device: set them once on every device that launches
+    static bool configured[64] = {false};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FG_ERR_BAD_SIZE;
+    if (!configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-        configured = true;
+        configured[dev] = true;
     }
     int G = H / KV, Gc = G < 16 ? G : 16, TQ = ROWS / Gc;
     dim3 grid(KV * ((G + Gc - 1) / Gc), (max_new + TQ - 1) / TQ, n_seq);
     return fg_launch(attn_prefill_tc_kernel<HD>, grid, dim3(ATT_THREADS), (size_t)smem, stream, tmK, tmV, (const bf16 *)q, ldq,
-                     (bf16 *)out, ldo, cu_rows, seq_start, block_table, table_width, KV, G, scale * LOG2E, window);
+                     (bf16 *)out, ldo, cu_rows, seq_start, block_table, table_width, KV, G, scale * LOG2E, window, g_test_skip_copy);
 }
 
 // Arguments as fg_attention_prefill, plus the number of pages in the pools.  Takes HD 64 and 128.
@@ -480,6 +491,16 @@ extern "C" int fg_attention_prefill_tc(const void *q, int ldq, void *out, int ld
     if (e) return e;
     if (hd == 64) return launch_tc<64>(tmK, tmV, q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, n_seq, max_new, H, KV, scale, window, stream);
     return launch_tc<128>(tmK, tmV, q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, n_seq, max_new, H, KV, scale, window, stream);
+}
+
+// For the test of the bounded waits: wait_limit_cycles > 0 sets how long a wait may last (0 restores the default of
+// about a second; values below half a millisecond act as half a millisecond), and skip_copy != 0 makes the producer
+// leave the first K tile of every CTA incomplete, so that the waits run out: the kernel then raises the error flag,
+// frees its tensor memory and returns.  Never set outside a test.
+extern "C" int fg_attention_prefill_tc_test_hook(long long wait_limit_cycles, int skip_copy) {
+    long long v = wait_limit_cycles > 0 ? wait_limit_cycles : WAIT_LIMIT_CYCLES;
+    g_test_skip_copy = skip_copy ? 1 : 0;
+    return (int)cudaMemcpyToSymbol(g_attn_wait_limit, &v, sizeof v);
 }
 
 extern "C" int fg_attention_prefill_tc_error(void) {

@@ -107,6 +107,17 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 #include <cstdlib>
+// Function attributes (the dynamic shared memory limit) belong to a kernel on ONE device: a launcher sets them the
+// first time it runs on each device.  True once per device for the call site that owns `s`.
+struct FgPerDevice { bool done[64]; };
+static inline bool fg_needs_setup(FgPerDevice &s) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (s.done[dev]) return false;
+    s.done[dev] = true;
+    return true;
+}
+
 static inline bool fg_pdl_enabled() {
     static int v = -1;
     if (v < 0) { const char *e = getenv("FASTGGUF_PDL"); v = !(e && e[0] == '0'); }

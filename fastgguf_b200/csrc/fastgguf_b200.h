@@ -49,6 +49,8 @@ int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *out, int ld
                void *xw_out, float *ss_out, int *ss_tiles_out /* host */, cudaStream_t stream);
 int fg_gemm_tc_max_ss_tiles(int N);
 int fg_gemm_tc_error(void);
+/* tests only: shorten the bounded waits and make the decode kernel's pipeline stall, see gemm_tc.cu */
+int fg_gemm_tc_test_hook(long long wait_limit_cycles, int skip_copy);
 
 /* ---- libfg_attn: bf16 tensor-core attention over the paged cache (head sizes 64 and 128, pages of 64) */
 int fg_attention_decode(const void *q, int ldq, void *out, int ldo, const int *positions, const int *block_table,
@@ -67,6 +69,7 @@ int fg_attention_prefill_tc(const void *q, int ldq, void *out, int ldo, const in
                             int n_pages, int n_seq, int max_new, int H, int KV, int hd, int page_size, float scale,
                             int window, cudaStream_t stream);
 int fg_attention_prefill_tc_error(void);
+int fg_attention_prefill_tc_test_hook(long long wait_limit_cycles, int skip_copy);   /* tests only */
 /* fg_attention_decode_noalloc: see fastgguf_noalloc.h */
 
 #ifdef __cplusplus

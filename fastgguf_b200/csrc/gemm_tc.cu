@@ -46,6 +46,9 @@
 enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_ADD_F32 = 2, EPI_SILU_MUL = 3 };
 
 __device__ int g_gemm_error = 0;      // 0, or (code << 8 | role) of the first wait that ran out
+// How long a wait may last, in SM cycles (about a second).  A variable, so that a test can make a wait run out within a
+// millisecond (fg_gemm_tc_test_hook); it is read only by waits that have already lasted WAIT_SHORT_CYCLES.
+__device__ long long g_gemm_wait_limit = WAIT_LIMIT_CYCLES;
 
 // ---------------------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -73,10 +76,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (;;) {
         if (mbar_try(bar, parity)) return true;
         const long long waited = clock64() - t0;
-        if (waited > WAIT_LIMIT_CYCLES) return false;
-        // once a wait has run out somewhere, every later wait gives up after a short time: a broken pipeline
-        // costs milliseconds for the kernels that follow, not a second per wait
-        if (waited > WAIT_SHORT_CYCLES && *(volatile int *)&g_gemm_error != 0) return false;
+        if (waited > WAIT_SHORT_CYCLES) {
+            // once a wait has run out somewhere, every later wait gives up after a short time: a broken pipeline
+            // costs milliseconds for the kernels that follow, not a second per wait
+            if (*(volatile int *)&g_gemm_error != 0) return false;
+            if (waited > *(volatile long long *)&g_gemm_wait_limit) return false;
+        }
     }
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
@@ -151,6 +156,8 @@ __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.w
 // (8 bits of mantissa) right after, and the precise forms made the epilogue of a 64-token tile several us long
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
+static int g_test_skip_copy = 0;      // host side of fg_gemm_tc_test_hook
+
 struct GemmArgs {
     void *out;            // [M, ldc] bf16 or f32 by epilogue
     int M, N, K;          // tokens, weight rows (2F for the silu epilogue), reduction
@@ -168,6 +175,7 @@ struct GemmArgs {
     bf16 *xw_out;         // [M, N]
     float *ss_out;        // [tiles, M]
     int epi, stages;      // decode kernel: epilogue and ring depth are run-time values
+    int test_skip_copy;   // tests only: the decode kernel's producer omits the activation copy of its first stage
 };
 
 __device__ __forceinline__ float inv_rms(const GemmArgs &a, int m) {
@@ -455,7 +463,8 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         __syncwarp();
         pdl_wait();                                            // activations come from the kernel before
         if (elect_one()) {
-            for (int kb = 0; kb < pre; kb++)
+            // (a test may ask for stage 0 to stay incomplete: its barrier then never fires and every wait runs out)
+            for (int kb = a.test_skip_copy ? 1 : 0; kb < pre; kb++)
                 tma_load_2d(smem0 + kb * STAGE_BYTES + W_BYTES, &tmX, (kb0 + kb) * BK, q0, full0 + 8 * kb);
         }
         __syncwarp();
@@ -985,11 +994,10 @@ static int launch_decode(const CUtensorMap &tmW, const CUtensorMap &tmX, GemmArg
     if (!split && ring < BN * BM * 4) ring = BN * BM * 4;
     const int smem = ring + 1024 + (split ? BN * BM * 4 : 0);
     constexpr int smem_max = MAX_STAGES * stage_bytes + 1024;
-    static bool configured = false;
-    if (!configured) {
+    static FgPerDevice configured;
+    if (fg_needs_setup(configured)) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_decode_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     return fg_launch_cluster(gemm_tc_decode_kernel<BN>, grid, dim3(GEMM_THREADS), (size_t)smem, stream, (int)grid.z, tmW, tmX, a);
 }
@@ -997,15 +1005,14 @@ static int launch_decode(const CUtensorMap &tmW, const CUtensorMap &tmX, GemmArg
 template <int BN, int STAGES, int EPI>
 static int launch_prefill(const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs &a, cudaStream_t stream) {
     constexpr int smem = STAGES * (BM + BN) * BK * 2 + 1024 + (EPI == EPI_ADD_F32 ? 4 * EPI_STAGE_BYTES : 0);
-    static bool configured = false;
+    static FgPerDevice configured;
     static int n_sm = 0;
-    if (!configured) {
+    if (fg_needs_setup(configured)) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_prefill_kernel<BN, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         int dev = 0;
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
-        configured = true;
     }
     int n_pt = (a.M + BM - 1) / BM, n_tiles = n_pt * ((a.N + BN - 1) / BN);
     dim3 grid(n_tiles < n_sm ? n_tiles : n_sm);
@@ -1017,13 +1024,12 @@ static int sm_count();
 template <int BN, int STAGES, int EPI>
 static int launch_prefill_pair(const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs &a, cudaStream_t stream) {
     constexpr int smem = STAGES * (BM + BN / 2) * BK * 2 + 1024 + (EPI == EPI_ADD_F32 ? 4 * EPI_STAGE_BYTES : 0);
-    static bool configured = false;
+    static FgPerDevice configured;
     static int n_sm = 0;
-    if (!configured) {
+    if (fg_needs_setup(configured)) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_prefill_pair_kernel<BN, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         n_sm = sm_count();
-        configured = true;
     }
     int n_pt = (a.M + 2 * BM - 1) / (2 * BM), n_tiles = n_pt * ((a.N + BN - 1) / BN);
     int pairs = n_sm / 2;
@@ -1146,7 +1152,8 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
     int vec_ok = ((uintptr_t)out % 16 == 0) && ((size_t)ldc * esz % 16 == 0);
     if (norm_w && (epi != EPI_ADD_F32 || !xw_out || !ss_out)) return FG_ERR_BAD_DTYPE;
     if (ss_tiles_out) *ss_tiles_out = (int)grid.y;
-    GemmArgs a{out, M, N, K, ldc, kb_per_split, vec_ok, ss_in, ss_tiles, ss_size, ss_eps, norm_w, (bf16 *)xw_out, ss_out, epi, 0};
+    GemmArgs a{out, M, N, K, ldc, kb_per_split, vec_ok, ss_in, ss_tiles, ss_size, ss_eps, norm_w, (bf16 *)xw_out, ss_out, epi, 0,
+               g_test_skip_copy};
     switch (epi) {
     case EPI_BF16: return dispatch<EPI_BF16>(swap, bn, tmP, tmQ, a, grid, stream);
     case EPI_F32: return dispatch<EPI_F32>(swap, bn, tmP, tmQ, a, grid, stream);
@@ -1154,6 +1161,16 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
     case EPI_SILU_MUL: return dispatch<EPI_SILU_MUL>(swap, bn, tmP, tmQ, a, grid, stream);
     }
     return FG_ERR_BAD_DTYPE;
+}
+
+// For the test of the bounded waits: wait_limit_cycles > 0 sets how long a wait may last (0 restores the default of
+// about a second; values below half a millisecond act as half a millisecond), and skip_copy != 0 makes the decode
+// kernel's producer leave the first stage of every launch incomplete, so that its waits run out: the kernel then
+// raises the error flag, frees its tensor memory and returns.  Never set outside a test.
+extern "C" int fg_gemm_tc_test_hook(long long wait_limit_cycles, int skip_copy) {
+    long long v = wait_limit_cycles > 0 ? wait_limit_cycles : WAIT_LIMIT_CYCLES;
+    g_test_skip_copy = skip_copy ? 1 : 0;
+    return (int)cudaMemcpyToSymbol(g_gemm_wait_limit, &v, sizeof v);
 }
 
 // The error flag of the pipelines: 0, or FG_ERR_PIPELINE << 8 | role.  Reading clears it.

@@ -124,9 +124,26 @@ Arena::~Arena() {
     for (auto &b : blocks_) cudaFree(b.p);
 }
 
+void Arena::reset() {
+    if (used_ > peak_) peak_ = used_;
+    used_ = 0;
+    block_ = 0;
+    offset_ = 0;
+    if (frozen_ || blocks_.size() <= 1) return;
+    // the last step spilled into further blocks: one block for the largest step so far (cudaFree waits for the device)
+    for (auto &b : blocks_) cudaFree(b.p);
+    blocks_.clear();
+    size_t size = peak_ + peak_ / 8;
+    if (size < block_bytes_) size = block_bytes_;
+    void *p = nullptr;
+    if (cudaMalloc(&p, size) == cudaSuccess) blocks_.push_back({p, size});
+    else cudaGetLastError();                 // alloc() asks again, block by block, and reports what fails
+}
+
 void *Arena::alloc(size_t bytes) {
     bytes = (bytes + 255) / 256 * 256;
     if (bytes == 0) bytes = 256;
+    used_ += bytes;
     while (true) {
         if (block_ < blocks_.size()) {
             Block &b = blocks_[block_];

@@ -54,7 +54,9 @@ int elem_size(int dtype);
 // Device memory for the activations of one step: allocation bumps a cursor through a list of blocks;
 // `reset` starts over.  The sequence of allocations of a step is deterministic, so a step that is run
 // once to warm up and then recorded into a CUDA graph gets the same addresses both times; blocks are only
-// added outside a recording.
+// added outside a recording.  A step that needed more than the first block got further blocks; the next
+// `reset` replaces them all by ONE block of the largest need seen so far, so that steps of changing shapes
+// (a long prompt, then single tokens, then another batch) do not pile up memory.
 class Arena {
 public:
     explicit Arena(size_t block_bytes = (size_t)64 << 20) : block_bytes_(block_bytes) {}
@@ -62,14 +64,14 @@ public:
     Arena(const Arena &) = delete;
     void *alloc(size_t bytes);
     Tensor matrix(int64_t rows, int64_t cols, int dtype);
-    void reset() { block_ = 0; offset_ = 0; }
+    void reset();
     void forbid_growth(bool v) { frozen_ = v; }
     size_t bytes_reserved() const;
 
 private:
     struct Block { void *p; size_t size; };
     std::vector<Block> blocks_;
-    size_t block_bytes_, block_ = 0, offset_ = 0;
+    size_t block_bytes_, block_ = 0, offset_ = 0, used_ = 0, peak_ = 0;
     bool frozen_ = false;
 };
 

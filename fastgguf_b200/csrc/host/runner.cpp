@@ -209,6 +209,7 @@ DecodeGraph::DecodeGraph(Engine &e, Sampler &sampler, int width_) : width(width_
     FG_CUDA(cudaStreamSynchronize(e.stream));
     FG_CUDA(cudaMemset(tokens, 0, (size_t)B * 4));
     FG_CUDA(cudaMemset(positions, 0, (size_t)B * 4));
+    arena_.reset();                                  // one block for what the warm-up needed
     arena_.forbid_growth(true);
     FG_CUDA(cudaStreamBeginCapture(e.capture_stream, cudaStreamCaptureModeRelaxed));
     try {

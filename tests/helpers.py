@@ -47,12 +47,21 @@ def random_tokens(n, vocab, seed):
     return [int(t) for t in rng.integers(0, vocab, size=n)]
 
 
+#: worst relative error seen per test (printed at the end of a run, so the margin under each tolerance is known)
+WORST = {}
+
+
 def rel_err(got, want):
     """max |got - want| / max |want| over whole arrays (numpy or torch)."""
+    import os
     got = np.asarray(got, dtype=np.float64)
     want = np.asarray(want, dtype=np.float64)
-    return float(np.abs(got - want).max() / max(np.abs(want).max(), 1e-30))
+    err = float(np.abs(got - want).max() / max(np.abs(want).max(), 1e-30))
+    test = os.environ.get("PYTEST_CURRENT_TEST", "").split(" ")[0]
+    WORST[test] = max(WORST.get(test, 0.0), err)
+    return err
 
 
 #: tolerances on max|dlogit| / max|logit| against the float64 plain implementation
-TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+#: about twice the worst error any engine test shows (float32 1.5e-6, bfloat16 4.8e-3; the run prints them at its end)
+TOL = {"float32": 4e-6, "bfloat16": 1e-2}

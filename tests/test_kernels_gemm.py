@@ -23,7 +23,9 @@ def _check(got, a, w, want, out_is_bf16):
 
 @pytest.mark.parametrize("adt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
                                      (torch.bfloat16, torch.float32)])
-@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 200, 72), (70, 130, 257), (129, 65, 64)])
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 200, 72), (70, 130, 257), (129, 65, 64),
+                                   (16, 333, 1100), (9, 1000, 4096), (2, 31, 516),        # few rows: the weight-streaming kernel
+                                   (300, 260, 1000), (65, 128, 36), (200, 129, 130)])    # many rows: 128 x 128 tiles
 def test_gemm_generic(M, N, K, adt, wdt):
     from fastgguf_b200 import ops
     a, _ = _operands(M, N, K, adt, 1)
@@ -37,6 +39,13 @@ def test_gemm_generic(M, N, K, adt, wdt):
     _check(acc, a, w, want + res.double(), False)
     if adt == torch.bfloat16:
         _check(ops.gemm_generic(a, w), a, w, want, True)
+    # a row's result does not depend on the other rows of the step: alone, it gives the same bits
+    if M > 1:
+        alone = ops.gemm_generic(a[M - 1:M].contiguous(), w, out_dtype=torch.float32)
+        if (M <= 16) == (1 <= 16):                       # the same kernel serves both row counts
+            assert torch.equal(alone[0], got[M - 1])
+        else:
+            assert (alone[0] - got[M - 1]).abs().max() <= 1e-5 * got.abs().max()
 
 
 @pytest.mark.parametrize("M", [1, 5, 16, 33, 64, 100, 300, 700])
