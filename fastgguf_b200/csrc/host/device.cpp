@@ -121,39 +121,53 @@ fg_dev_tensor Tensor::view() const {
 
 // ------------------------------------------------------------------------------------ memory
 Arena::~Arena() {
-    for (auto &b : blocks_) cudaFree(b.p);
+    for (auto &l : lanes_)
+        for (auto &b : l.blocks) cudaFree(b.p);
 }
 
 void Arena::reset() {
-    if (used_ > peak_) peak_ = used_;
-    used_ = 0;
-    block_ = 0;
-    offset_ = 0;
-    if (frozen_ || blocks_.size() <= 1) return;
-    // the last step spilled into further blocks: one block for the largest step so far (cudaFree waits for the device)
-    for (auto &b : blocks_) cudaFree(b.p);
-    blocks_.clear();
-    size_t size = peak_ + peak_ / 8;
-    if (size < block_bytes_) size = block_bytes_;
-    void *p = nullptr;
-    if (cudaMalloc(&p, size) == cudaSuccess) blocks_.push_back({p, size});
-    else cudaGetLastError();                 // alloc() asks again, block by block, and reports what fails
+    cur_ = 0;
+    for (auto &l : lanes_) {
+        if (l.used > l.peak) l.peak = l.used;
+        l.used = 0;
+        l.block = 0;
+        l.offset = 0;
+        if (frozen_ || l.blocks.size() <= 1) continue;
+        // the last step spilled into further blocks: one block for the largest step so far (cudaFree waits for the device)
+        for (auto &b : l.blocks) cudaFree(b.p);
+        l.blocks.clear();
+        size_t size = l.peak + l.peak / 8;
+        if (size < block_bytes_) size = block_bytes_;
+        void *p = nullptr;
+        if (cudaMalloc(&p, size) == cudaSuccess) l.blocks.push_back({p, size});
+        else cudaGetLastError();             // alloc() asks again, block by block, and reports what fails
+    }
+}
+
+void Arena::begin_layer(int i) {
+    cur_ = 1 + (i & 1);
+    Lane &l = lanes_[cur_];
+    if (l.used > l.peak) l.peak = l.used;
+    l.used = 0;
+    l.block = 0;
+    l.offset = 0;
 }
 
 void *Arena::alloc(size_t bytes) {
     bytes = (bytes + 255) / 256 * 256;
     if (bytes == 0) bytes = 256;
-    used_ += bytes;
+    Lane &l = lanes_[cur_];
+    l.used += bytes;
     while (true) {
-        if (block_ < blocks_.size()) {
-            Block &b = blocks_[block_];
-            if (offset_ + bytes <= b.size) {
-                void *p = (char *)b.p + offset_;
-                offset_ += bytes;
+        if (l.block < l.blocks.size()) {
+            Block &b = l.blocks[l.block];
+            if (l.offset + bytes <= b.size) {
+                void *p = (char *)b.p + l.offset;
+                l.offset += bytes;
                 return p;
             }
-            block_++;
-            offset_ = 0;
+            l.block++;
+            l.offset = 0;
             continue;
         }
         if (frozen_) fail(FG_E_INTERNAL, "a recorded step asked for more activation memory than its warm-up run");
@@ -165,7 +179,7 @@ void *Arena::alloc(size_t bytes) {
             fail(FG_E_DEVICE, format("out of device memory: the activations of this step need another %zu MiB (%s)",
                                      size >> 20, cudaGetErrorString(e)));
         }
-        blocks_.push_back({p, size});
+        l.blocks.push_back({p, size});
     }
 }
 
@@ -183,7 +197,8 @@ Tensor Arena::matrix(int64_t rows, int64_t cols, int dtype) {
 
 size_t Arena::bytes_reserved() const {
     size_t n = 0;
-    for (auto &b : blocks_) n += b.size;
+    for (auto &l : lanes_)
+        for (auto &b : l.blocks) n += b.size;
     return n;
 }
 

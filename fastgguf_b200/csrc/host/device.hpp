@@ -51,12 +51,15 @@ struct Tensor {
 };
 int elem_size(int dtype);
 
-// Device memory for the activations of one step: allocation bumps a cursor through a list of blocks;
-// `reset` starts over.  The sequence of allocations of a step is deterministic, so a step that is run
-// once to warm up and then recorded into a CUDA graph gets the same addresses both times; blocks are only
-// added outside a recording.  A step that needed more than the first block got further blocks; the next
-// `reset` replaces them all by ONE block of the largest need seen so far, so that steps of changing shapes
-// (a long prompt, then single tokens, then another batch) do not pile up memory.
+// Device memory for the activations of one step.  Allocation bumps a cursor through a list of blocks; `reset`
+// starts over.  The sequence of allocations of a step is deterministic, so a step that is run once to warm up and
+// then recorded into a CUDA graph gets the same addresses both times; blocks are only added outside a recording.
+// A step that needed more than a lane's first block got further blocks; the next `reset` replaces them by ONE block
+// of the largest need seen so far, so that steps of changing shapes do not pile up memory.
+// Three lanes keep a deep model's step small: what lives for the whole step (the residual stream, the step's
+// integers, the logits) goes to lane 0, and the temporaries of layer i to lane 1 + (i & 1), which starts over when
+// layer i begins - what layer i - 1 handed over (a started norm) lies in the other lane and stays until layer i + 1.
+// All work of a step is ordered on one stream, so memory of layer i - 2 is free when layer i writes it.
 class Arena {
 public:
     explicit Arena(size_t block_bytes = (size_t)64 << 20) : block_bytes_(block_bytes) {}
@@ -64,14 +67,21 @@ public:
     Arena(const Arena &) = delete;
     void *alloc(size_t bytes);
     Tensor matrix(int64_t rows, int64_t cols, int dtype);
-    void reset();
+    void reset();                       // a new step: every lane starts over
+    void begin_layer(int i);            // allocations now go to the lane of layer i, which starts over
+    void end_layers() { cur_ = 0; }     // back to the step's own lane
     void forbid_growth(bool v) { frozen_ = v; }
     size_t bytes_reserved() const;
 
 private:
     struct Block { void *p; size_t size; };
-    std::vector<Block> blocks_;
-    size_t block_bytes_, block_ = 0, offset_ = 0, used_ = 0, peak_ = 0;
+    struct Lane {
+        std::vector<Block> blocks;
+        size_t block = 0, offset = 0, used = 0, peak = 0;
+    };
+    Lane lanes_[3];
+    int cur_ = 0;
+    size_t block_bytes_;
     bool frozen_ = false;
 };
 

@@ -433,8 +433,10 @@ Tensor DecoderModel::forward(Runtime &rt, const Batch &batch) {
     DeferredNorm pending = embedding_->forward(rt, batch, x, first);
     for (size_t i = 0; i < n; i++) {
         Norm *next = i + 1 < n ? entry_norm(block_at(i + 1)) : head_norm;
+        rt.arena->begin_layer((int)i);                 // this entry's temporaries reuse the memory of entry i - 2
         pending = block_at(i)->forward(rt, x, batch, io[i], pending, next);
     }
+    rt.arena->end_layers();
     if (!batch.want_rows) return Tensor();
     if (head_norm && pending.defined() && n) return head_->forward(rt, Tensor(), &pending);
     return head_->forward(rt, final_norm_->forward(rt, x, batch.want_rows, batch.n_want), nullptr);
