@@ -10,8 +10,9 @@ sys.path.insert(0, ROOT)
 import bench  # noqa: E402
 
 
-def _run(*args):
-    return subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), *args], capture_output=True, text=True, timeout=120)
+def _run(*args, env=None):
+    return subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), *args], capture_output=True, text=True, timeout=120,
+                          env=dict(os.environ, **(env or {})))
 
 
 def test_more_than_one_gpu_is_refused_with_one_line_and_code_2():
@@ -21,7 +22,10 @@ def test_more_than_one_gpu_is_refused_with_one_line_and_code_2():
 
 
 def test_reference_arm_says_why_it_is_unavailable():
-    r = _run("--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1")
+    """Where the reference's CPU build is absent the arm prints one line that says so and exits 0 (where it is present
+    the arm runs it: a minute of CPU time, not part of this test)."""
+    r = _run("--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1",
+             env={"FASTGGUF_REFERENCE_BINARY": "/nonexistent/fastgguf"})
     assert r.returncode == 0
     rec = json.loads(r.stdout.strip().splitlines()[-1])
     assert rec["impl"] == "reference" and isinstance(rec["unavailable"], str) and "\n" not in rec["unavailable"]
