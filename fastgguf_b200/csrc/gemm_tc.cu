@@ -150,6 +150,17 @@ __device__ __forceinline__ void st_dsmem_f32(uint32_t local_addr, int rank, floa
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 __device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+// Write a float to the same shared-memory offset in the CTA of rank `rank`, and count its four bytes on that CTA's
+// mbarrier `local_bar` (same offset there): the receiver waits for BYTES on a barrier of its own instead of for the
+// whole cluster at a cluster barrier, and a sender has nothing to wait for.
+__device__ __forceinline__ void st_async_f32(uint32_t local_addr, uint32_t local_bar, int rank, float v) {
+    uint32_t remote, remote_bar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(local_bar), "r"(rank));
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+                 ::"r"(remote), "r"(__float_as_uint(v)), "r"(remote_bar) : "memory");
+}
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
 // silu(g) * u in f32 with the fast exponential and division (2 ulp each): the result is rounded to bfloat16
@@ -408,7 +419,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms need 1 KB alignment
-    __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 1];
+    __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 2];
     __shared__ uint32_t tmem_base_s;
     __shared__ float inv_s[BN];                   // 1/rms of the token columns (deferred norm), else 1
 
@@ -422,15 +433,22 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     const int kb0 = blockIdx.z * a.kb_per_split;
     const int nkb = min(a.kb_per_split, total_kb - kb0);
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[MAX_STAGES]), tfull = smem_u32(&bars[2 * MAX_STAGES]);
+    const uint32_t inbox = smem_u32(&bars[2 * MAX_STAGES + 1]);
     const uint32_t smem0 = smem_u32(smem);
     // split-K: partial columns arrive here from the whole cluster, [rank][BN / S columns][128 rows] f32; a region
-    // of its own, since a faster CTA pushes while this one is still in its main loop
+    // of its own, since a faster CTA pushes while this one is still in its main loop.  Every CTA of the cluster
+    // (this one included) sends BM floats for each of this CTA's columns that holds a token; `inbox` counts the bytes.
     float *recv = (float *)(smem + stages * STAGE_BYTES);
-    if (split) cluster_arrive_relaxed();          // matched before the first push: every CTA of the cluster runs
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(tfull, 1);
+        mbar_init(inbox, 1);
+        if (split) {
+            const int per0 = BN / S;
+            const int mine = max(0, min(per0, a.M - q0 - (int)blockIdx.z * per0));      // my columns with a token
+            mbar_expect_tx(inbox, (uint32_t)(S * mine * BM * 4));
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -441,6 +459,9 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // the barriers above are initialised: tell the cluster (matched by the wait before the first push, which thereby
+    // also knows that every CTA of the cluster runs and that its inbox counts)
+    if (split) cluster_arrive_release();
     const uint32_t tmem_base = tmem_base_s;
     pdl_launch_dependents();
     if (threadIdx.x == 32) {                      // descriptors into the cache before their first use
@@ -590,7 +611,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
                     const int c = c0 + j, r = c >> per_log, cl = c & (per - 1);
                     const float val = have ? v[j] : 0.f;
                     if (q0 + c >= a.M) continue;                    // a column without a token is never read
-                    if (split) st_dsmem_f32(smem_u32(&recv[((int)blockIdx.z * per + cl) * BM + prow]), r, val);
+                    if (split) st_async_f32(smem_u32(&recv[((int)blockIdx.z * per + cl) * BM + prow]), inbox, r, val);
                     else ((float *)smem)[c * BM + prow] = val;
                 }
             }
@@ -601,8 +622,10 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         // ---- after the barrier this CTA's shared memory holds, for its columns, the partial sums of every CTA of
         // the cluster; they are added in rank order and the epilogue runs on the totals
         if (split) {
-            if (warp < 2) { __syncwarp(); cluster_wait(); }    // the barrier phase opened at the top
-            cluster_sync();
+            // every partial sum for this CTA's columns has landed when the inbox has counted its bytes; nobody waits
+            // for the cluster (the producer and issuer warps only close the barrier phase that opened at the top)
+            if (warp < 2) { __syncwarp(); cluster_wait(); }
+            else if (!mbar_wait(inbox, 0)) raise_error(5);
         } else if (warp >= 2) asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp >= 2) {
             // A warp takes whole columns (tokens) here: its lanes cover the 128 features in four steps, so the sum of
