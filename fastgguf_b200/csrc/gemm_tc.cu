@@ -422,6 +422,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 2];
     __shared__ uint32_t tmem_base_s;
     __shared__ float inv_s[BN];                   // 1/rms of the token columns (deferred norm), else 1
+    __shared__ float inv_part[128];               // partial sums on the way to inv_s
 
     const int warp = warp_index(), lane = threadIdx.x & 31;      // uniform: the role branches below are not divergent
     const int stages = a.stages, epi = a.epi, S = gridDim.z;
@@ -550,7 +551,23 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         }
         pdl_wait();
         // 1/rms of the token columns of this tile, while the main loop runs
-        for (int c = prow; c < BN; c += 128) inv_s[c] = (a.ss_in && q0 + c < a.M) ? inv_rms(a, q0 + c) : 1.0f;
+        // (128 / BN threads per column, each striding over the tiles, and their sums added in thread order)
+        {
+            constexpr int P = 128 / BN;
+            const int c = prow % BN, pp = prow / BN;
+            const bool live = a.ss_in && q0 + c < a.M;
+            float s = 0.f;
+            if (live)
+                for (int tt = pp; tt < a.ss_tiles; tt += P) s += __ldcg(a.ss_in + (size_t)tt * a.M + q0 + c);
+            inv_part[pp * BN + c] = s;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (prow < BN) {
+                float tot = 0.f;
+#pragma unroll
+                for (int p = 0; p < P; p++) tot += inv_part[p * BN + prow];
+                inv_s[prow] = live ? 1.0f / sqrtf(tot / (float)a.ss_size + a.ss_eps) : 1.0f;
+            }
+        }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (split && epi == EPI_ADD_F32) {
             // the residual values this thread adds to after the main loop: columns w and w + 4 of this CTA's share
@@ -571,7 +588,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         tc_fence_after();
         const uint32_t trow = tmem_base + ((uint32_t)(lg * 32) << 16);
         const bool have = ok && nkb > 0;          // the accumulator holds this CTA's part of the sum
-        if (epi == EPI_SILU_MUL) {
+        if (epi == EPI_SILU_MUL && !split) {
             // rows 0..63 of the tile are gate, 64..127 up of the same 64 features: both halves go to
             // shared memory as [token][feature], then all 128 threads share the activations
             float *exg = (float *)smem;           // [BN][64]; the stages are idle once tfull has fired
@@ -618,7 +635,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         }
         tc_fence_before();
     }
-    if (epi != EPI_SILU_MUL) {
+    if (epi != EPI_SILU_MUL || split) {
         // ---- after the barrier this CTA's shared memory holds, for its columns, the partial sums of every CTA of
         // the cluster; they are added in rank order and the epilogue runs on the totals
         if (split) {
@@ -650,6 +667,16 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
                     for (int z = 0; z < 8; z++) v[i] += pz[z];                     // rank order; absent ranks add 0
                 }
                 const float iv = inv_s[c_begin + cl];
+                if (epi == EPI_SILU_MUL) {
+                    // features lane and lane + 32 of the tile's 64: gate in rows 0..63 (v[0], v[1]), up in 64..127
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        const int f = (p0 >> 1) + lane + 32 * i;
+                        if (f < (a.N >> 1))
+                            ((bf16 *)a.out)[(size_t)m * a.ldc + f] = __float2bfloat16_rn(silu_mul(v[i] * iv, v[i + 2] * iv));
+                    }
+                    continue;
+                }
                 float sq = 0.f;
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
@@ -1127,6 +1154,7 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
     // Up to 128 rows the weights stream through the decode kernel, in blocks of 64 tokens whose CTAs run side by side
     // and share each weight tile through L2; beyond that the prefill kernel is faster (measured: 56.6 against 45.5 k tok/s
     // at 96 rows, 65.8 against 74.0 k at 200).
+    if (norm_w && (epi != EPI_ADD_F32 || !xw_out || !ss_out)) return FG_ERR_BAD_DTYPE;
     const bool swap = M <= 128;
     const int total_kb = (K + BK - 1) / BK;
     int bn, splits = 1;
@@ -1135,11 +1163,9 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
         bn = M <= 16 ? 16 : M <= 32 ? 32 : 64;
         int tiles = (N + BM - 1) / BM, blocks = (M + bn - 1) / bn;
         // too few tiles to fill the SMs: a cluster of 2, 4 or 8 CTAs shares each tile along K
-        if (epi != EPI_SILU_MUL) {
-            while (splits < 8 && tiles * blocks * splits < sm_count() * 4 / 5 && total_kb >= 4 * splits) splits *= 2;
-            if (force_splits == 1 || force_splits == 2 || force_splits == 4 || force_splits == 8)
-                if (force_splits <= total_kb) splits = force_splits;
-        }
+        while (splits < 8 && tiles * blocks * splits < sm_count() * 4 / 5 && total_kb >= 4 * splits) splits *= 2;
+        if (force_splits == 1 || force_splits == 2 || force_splits == 4 || force_splits == 8)
+            if (force_splits <= total_kb) splits = force_splits;
         grid = dim3(blocks, tiles, 1);
     } else {
         // tile width: rounds of tiles over the persistent CTAs (one an SM) times the width (a 128-wide tile costs a tenth
@@ -1173,7 +1199,6 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
     if (e) return e;
     int esz = (epi == EPI_F32 || epi == EPI_ADD_F32) ? 4 : 2;
     int vec_ok = ((uintptr_t)out % 16 == 0) && ((size_t)ldc * esz % 16 == 0);
-    if (norm_w && (epi != EPI_ADD_F32 || !xw_out || !ss_out)) return FG_ERR_BAD_DTYPE;
     if (ss_tiles_out) *ss_tiles_out = (int)grid.y;
     GemmArgs a{out, M, N, K, ldc, kb_per_split, vec_ok, ss_in, ss_tiles, ss_size, ss_eps, norm_w, (bf16 *)xw_out, ss_out, epi, 0,
                g_test_skip_copy};

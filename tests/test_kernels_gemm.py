@@ -97,6 +97,22 @@ def test_gemm_tc_silu(M, F, K):
     assert fast_gemm.pipeline_error() == 0
 
 
+@pytest.mark.parametrize("splits", [2, 4, 8])
+@pytest.mark.parametrize("M,F,K", [(1, 192, 2048), (9, 320, 1096), (64, 640, 2048), (40, 64, 4096)])
+def test_gemm_tc_silu_split_k(M, F, K, splits):
+    """Gate and up partial sums of a cluster's CTAs meet in the owner of the token column before the activation."""
+    from fastgguf_b200.ops import fast_gemm
+    a, w = _operands(M, 2 * F, K, torch.bfloat16, 14)
+    g = a.double() @ w[:F].double().T
+    u = a.double() @ w[F:].double().T
+    want = g / (1 + torch.exp(-g)) * u
+    got = fast_gemm.gemm_tc(a, fast_gemm.interleave_gate_up(w[:F], w[F:]), silu=True, force_splits=splits)
+    bound = (a.double().abs() @ w.double().abs().T).max().item()
+    err = (got.double() - want).abs().max().item()
+    assert err <= want.abs().max().item() * 2 ** -8 + 1e-5 * bound * bound
+    assert fast_gemm.pipeline_error() == 0
+
+
 def test_gemm_tc_refuses_unaligned():
     from fastgguf_b200.ops import fast_gemm
     a, w = _operands(4, 32, 36, torch.bfloat16, 5)      # K % 8 != 0: TMA cannot describe the rows
