@@ -154,12 +154,23 @@ __device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier
 // Write a float to the same shared-memory offset in the CTA of rank `rank`, and count its four bytes on that CTA's
 // mbarrier `local_bar` (same offset there): the receiver waits for BYTES on a barrier of its own instead of for the
 // whole cluster at a cluster barrier, and a sender has nothing to wait for.
-__device__ __forceinline__ void st_async_f32(uint32_t local_addr, uint32_t local_bar, int rank, float v) {
+// Two or four consecutive floats into the shared memory of CTA `rank` of the cluster, counted as bytes on that CTA's
+// mbarrier: one packet on the SM-to-SM network instead of two or four (the network moves packets, not bytes: at 64
+// token columns the exchange of single floats took 7.8 us of a 14 us launch).
+__device__ __forceinline__ void st_async_f32x4(uint32_t local_addr, uint32_t local_bar, int rank, const float *v) {
     uint32_t remote, remote_bar;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(local_bar), "r"(rank));
-    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
-                 ::"r"(remote), "r"(__float_as_uint(v)), "r"(remote_bar) : "memory");
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(remote), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+                   "r"(__float_as_uint(v[3])), "r"(remote_bar) : "memory");
+}
+__device__ __forceinline__ void st_async_f32x2(uint32_t local_addr, uint32_t local_bar, int rank, const float *v) {
+    uint32_t remote, remote_bar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(local_bar), "r"(rank));
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.b32 [%0], {%1, %2}, [%3];"
+                 ::"r"(remote), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(remote_bar) : "memory");
 }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
@@ -407,7 +418,7 @@ __device__ __forceinline__ void epilogue_add_coalesced(const GemmArgs &a, uint32
 // runs its code once, and code that has left the SM's instruction cache is fetched again at hundreds of cycles
 // a line: one small kernel that every projection shares stays resident, a family of specialised ones does not.
 // For the same reason the once-per-launch epilogue code is written as rolled loops.
-#define MAX_STAGES 6
+#define MAX_STAGES 9
 
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -436,19 +447,22 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[MAX_STAGES]), tfull = smem_u32(&bars[2 * MAX_STAGES]);
     const uint32_t inbox = smem_u32(&bars[2 * MAX_STAGES + 1]);
     const uint32_t smem0 = smem_u32(smem);
-    // split-K: partial columns arrive here from the whole cluster, [rank][BN / S columns][128 rows] f32; a region
-    // of its own, since a faster CTA pushes while this one is still in its main loop.  Every CTA of the cluster
-    // (this one included) sends BM floats for each of this CTA's columns that holds a token; `inbox` counts the bytes.
+    // split-K: partial columns arrive here from the whole cluster, [rank][group of VW columns][128 rows][VW] f32 with
+    // VW = 4 (2 when a CTA owns only two columns), so that a lane sends the VW columns of its row as one packet and
+    // the lanes of a warp fill consecutive 16 (8) bytes; a region of its own, since a faster CTA pushes while this one
+    // is still in its main loop.  Every CTA of the cluster (this one included) sends BM * VW floats for each of this
+    // CTA's column groups whose first column holds a token; `inbox` counts the bytes.
     float *recv = (float *)(smem + stages * STAGE_BYTES);
+    const int vw_log = (BN / S) >= 4 ? 2 : 1;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(tfull, 1);
         mbar_init(inbox, 1);
         if (split) {
-            const int per0 = BN / S;
-            const int mine = max(0, min(per0, a.M - q0 - (int)blockIdx.z * per0));      // my columns with a token
-            mbar_expect_tx(inbox, (uint32_t)(S * mine * BM * 4));
+            const int per0 = BN / S, vw = 1 << vw_log;
+            const int mine = max(0, min(per0 >> vw_log, (a.M - q0 - (int)blockIdx.z * per0 + vw - 1) >> vw_log));   // my groups with a token
+            mbar_expect_tx(inbox, (uint32_t)(S * mine * BM * vw * 4));
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -619,17 +633,34 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             // Without a split the CTA is its own owner and the tile passes through its (now idle) ring instead.
             const int per = BN / S, per_log = __ffs(per) - 1;       // BN and S are powers of two
             if (split) cluster_wait();            // every CTA of the cluster has started (arrived at its top)
+            const uint32_t recv0 = smem_u32(recv);
+            const int groups = per >> vw_log;     // column groups an owner receives from each rank
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 float v[16];
                 if (have) tc_ld16(trow + c0, v);
+                else {
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    const int c = c0 + j, r = c >> per_log, cl = c & (per - 1);
-                    const float val = have ? v[j] : 0.f;
-                    if (q0 + c >= a.M) continue;                    // a column without a token is never read
-                    if (split) st_async_f32(smem_u32(&recv[((int)blockIdx.z * per + cl) * BM + prow]), inbox, r, val);
-                    else ((float *)smem)[c * BM + prow] = val;
+                    for (int j = 0; j < 16; j++) v[j] = 0.f;
+                }
+                if (!split) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++)
+                        if (q0 + c0 + j < a.M) ((float *)smem)[(c0 + j) * BM + prow] = v[j];      // a column without a token is never read
+                } else if (vw_log == 2) {
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4) {
+                        const int c = c0 + j, r = c >> per_log, cg = (c & (per - 1)) >> 2;
+                        if (q0 + c >= a.M) continue;
+                        st_async_f32x4(recv0 + ((((int)blockIdx.z * groups + cg) * BM + prow) << 4), inbox, r, v + j);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j += 2) {
+                        const int c = c0 + j, r = c >> per_log, cg = (c & (per - 1)) >> 1;
+                        if (q0 + c >= a.M) continue;
+                        st_async_f32x2(recv0 + ((((int)blockIdx.z * groups + cg) * BM + prow) << 3), inbox, r, v + j);
+                    }
                 }
             }
         }
@@ -661,7 +692,12 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
                 for (int i = 0; i < 4; i++) {
                     float pz[8];
 #pragma unroll
-                    for (int z = 0; z < 8; z++) pz[z] = z < S ? part[(z * per + cl) * BM + lane + 32 * i] : 0.f;
+                    for (int z = 0; z < 8; z++) {
+                        const int row = lane + 32 * i;
+                        const int at = split ? ((((z * (per >> vw_log) + (cl >> vw_log)) * BM + row) << vw_log) + (cl & ((1 << vw_log) - 1)))
+                                             : cl * BM + row;
+                        pz[z] = z < S ? part[at] : 0.f;
+                    }
                     v[i] = 0.f;
 #pragma unroll
                     for (int z = 0; z < 8; z++) v[i] += pz[z];                     // rank order; absent ranks add 0
@@ -1032,12 +1068,16 @@ static int make_map(CUtensorMap *map, const void *base, int rows, int K, int ld,
     return r == CUDA_SUCCESS ? 0 : FG_ERR_TENSORMAP;
 }
 
+static int sm_count();
 template <int BN>
 static int launch_decode(const CUtensorMap &tmW, const CUtensorMap &tmX, GemmArgs a, dim3 grid, cudaStream_t stream) {
-    // two CTAs share an SM: ring and (split-K) receive buffer together stay under half its shared memory
+    // two CTAs share an SM: ring and (split-K) receive buffer together stay under half its shared memory ...
     const bool split = grid.z > 1;
     constexpr int stage_bytes = (BM + BN) * BK * 2;
     a.stages = BN == 16 ? (split ? 5 : 6) : BN == 32 ? (split ? 4 : 5) : (split ? 3 : 4);
+    // a launch of one CTA an SM at most that streams a whole matrix (gate/up): a deeper ring, alone on its SM
+    // (measured: 3 % of the step at batch 64, under 1 % at batch 8)
+    if (!split && (int)(grid.x * grid.y) <= sm_count()) a.stages = BN == 16 ? 9 : BN == 32 ? 8 : 6;
     if (a.stages > a.kb_per_split) a.stages = a.kb_per_split;      // a short K loop needs no deeper ring: room for other CTAs
     // without a split the epilogue passes the f32 tile (BN x 128) through the idle ring: the ring is at least that large
     int ring = a.stages * stage_bytes;
