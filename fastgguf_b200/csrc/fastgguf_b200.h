@@ -40,7 +40,7 @@ int fg_attention_generic(const void *q, int ldq, void *out, int ldo, int dtype, 
 int fg_sample(float *logits, int B, int V, int ldl, float temp, int top_k, float top_p, float repeat_penalty,
               int repeat_last_n, const int *seq_slot, unsigned long long *rng, int *hist, int hist_cap,
               int *hist_count, const int *stop_ids, int n_stop, int *out_tokens,
-              unsigned long long *scratch /* [B, 2048] or null */, cudaStream_t stream);
+              unsigned long long *scratch /* [B, 4096] or null */, cudaStream_t stream);
 int fg_argmax(const float *logits, int B, int V, int ldl, int *out, cudaStream_t stream);
 
 /* ---- libfg_tc: bf16 contraction on tcgen05 / TMA / tensor memory */

@@ -132,9 +132,9 @@ Sampler::Sampler(const SamplingParams &p, int n_slots, const std::vector<int> &s
         stop_ = DeviceBuffer((size_t)n_stop_ * 4, "stop ids");
         FG_CUDA(cudaMemcpy(stop_.get(), stop_ids.data(), (size_t)n_stop_ * 4, cudaMemcpyHostToDevice));
     }
-    // 2048 words a batch row: the candidates of the two-stage top-k, or (greedy) the two words in which the blocks
+    // 4096 words a batch row: the candidates of the two-stage top-k, or (greedy) the two words in which the blocks
     // of a row meet.  Owned by this sampler, so samplers of other engines or streams share nothing with it.
-    scratch_ = DeviceBuffer((size_t)bucket_for(std::max(1, n_slots)) * 2048 * 8, "sampler scratch");
+    scratch_ = DeviceBuffer((size_t)bucket_for(std::max(1, n_slots)) * 4096 * 8, "sampler scratch");
     FG_CUDA(cudaMemset(scratch_.get(), 0, scratch_.bytes()));
 }
 
@@ -154,7 +154,7 @@ void Sampler::begin(int row, uint64_t state, const int *prompt, int prompt_len) 
 
 void Sampler::sample(float *logits, int B, int V, int ldl, const int *rows_dev, int *out_dev, cudaStream_t s) {
     const SamplingParams &p = params;
-    if ((size_t)B * 2048 * 8 > scratch_.bytes()) fail(FG_E_USAGE, format("a step of %d rows exceeds the sampler's scratch", B));
+    if ((size_t)B * 4096 * 8 > scratch_.bytes()) fail(FG_E_USAGE, format("a step of %d rows exceeds the sampler's scratch", B));
     FG_LAUNCH("core", fg_sample, logits, B, V, ldl, p.temp, p.top_k, p.top_p, p.repeat_penalty, p.repeat_last_n, rows_dev,
               (unsigned long long *)rng_.get(), (int *)hist_.get(), use_hist_ ? hist_cap_ : 0, (int *)hist_count_.get(),
               (const int *)stop_.get(), n_stop_, out_dev, (unsigned long long *)scratch_.get(), s);

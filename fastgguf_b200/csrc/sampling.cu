@@ -275,13 +275,12 @@ sample_kernel(float *__restrict__ logits, int V, int ldl, SampleParams sp,
     }
 }
 
-// ---- top-k sampling in two stages (k <= 128): the vocabulary of a row is split over TOPK_BLOCKS
-// blocks; each selects the k best of its segment as 64-bit words (value key, then lower index first)
-// with a radix select in shared memory; one block per row then sorts the TOPK_BLOCKS * k candidates
-// and draws exactly as the single-block kernel does.  The k best of the row are among the k best of
-// each segment, and the words order them totally, so the result is the single-block kernel's.
+// ---- top-k sampling in two stages (k <= 128): the vocabulary of a row is split over segments of at most 4,096 entries; a block per segment hands over its K best (K = 64 or 128 >= k) as 64-bit words (value key, then lower index first), sorted;
+// one block per row then finds the K best of those and draws exactly as the single-block kernel does.  The k best
+// of the row are among the K best of each segment, and the words order them totally, so the result is the
+// single-block kernel's.
 #define TOPK_SEG 4096                  // most vocabulary entries a stage-1 block takes
-#define TOPK_CAND 2048                 // candidates per row after stage 1
+#define TOPK_CAND 4096                 // most candidates per row after stage 1 (the caller's scratch holds as many words a row)
 #define TOPK_MAX_K 128
 
 __global__ void __launch_bounds__(64)
@@ -306,129 +305,159 @@ penalty_kernel(float *__restrict__ logits, int V, int ldl, float penalty, int la
     }
 }
 
+// The K largest of the words that the 256 threads of a block hold in registers (PT each; value key, then lower
+// index first; all words are distinct; 0 = empty, the smallest), written to out[0 .. K) in descending order, zeros
+// after the last.  The K-th largest of the threads' own maxima is a lower bound of the K-th largest of all (K
+// entries are at least that large), so only what reaches it - K entries and a few more, PT * K at the very most -
+// is ranked by counting, and a word's rank is its place in the output.  (A radix select over the keys with a
+// histogram in shared memory took 29 us at a vocabulary of 128,256 - logits share their exponent bits, so its first
+// passes are thousands of atomic adds on two or three words - and a bitonic sort of the segment 90 us; sorting the
+// 2,048 candidates of the second stage to use the first 64 took 31 us.)
+#define TOPK_KEEP (TOPK_MAX_K * 16)
+struct TopkScratch {
+    unsigned long long best[256];
+    unsigned long long keep[TOPK_KEEP];
+    unsigned long long bound;
+    int n_keep;
+};
+template <int PT>
+__device__ __forceinline__ void block_topk_ranked(const unsigned long long (&w)[PT], int K, TopkScratch &sc, unsigned long long *out) {
+    static_assert(PT <= 16, "the kept list holds 16 K words");
+    const int tid = threadIdx.x;
+    unsigned long long mine = 0ull;
+#pragma unroll
+    for (int j = 0; j < PT; j++) mine = w[j] > mine ? w[j] : mine;
+    sc.best[tid] = mine;
+    if (tid == 0) { sc.bound = 1ull; sc.n_keep = 0; }    // fewer than K threads with an entry: every entry is kept
+    for (int i = tid; i < K; i += 256) out[i] = 0ull;
+    __syncthreads();
+    {
+        int above = 0;
+        for (int t = 0; t < 256; t++) above += sc.best[t] > mine;
+        if (above == K - 1 && mine != 0ull) sc.bound = mine;
+    }
+    __syncthreads();
+    const unsigned long long lb = sc.bound;
+#pragma unroll
+    for (int j = 0; j < PT; j++)
+        if (w[j] >= lb) sc.keep[atomicAdd(&sc.n_keep, 1)] = w[j];
+    __syncthreads();
+    const int c = sc.n_keep;
+    for (int i = tid; i < c; i += 256) {
+        const unsigned long long x = sc.keep[i];
+        int above = 0;
+        for (int t = 0; t < c; t++) above += sc.keep[t] > x;
+        if (above < K) out[above] = x;
+    }
+}
+
+// Stage 1: the K best words of a segment of at most TOPK_SEG entries.
 __global__ void __launch_bounds__(256)
-topk_stage1_kernel(const float *__restrict__ logits, int V, int ldl, int k, int n_blocks,
-                   unsigned long long *__restrict__ cand) {        // [B, n_blocks * k], zero where unused
-    __shared__ uint32_t keys[TOPK_SEG];
-    __shared__ int hist[256];
-    __shared__ int misc[4];
-    __shared__ int wsum[8];
+topk_stage1_kernel(const float *__restrict__ logits, int V, int ldl, int K, int n_blocks,
+                   unsigned long long *__restrict__ cand) {        // [B, n_blocks * K], zero where unused
+    __shared__ TopkScratch sc;
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.y, tid = threadIdx.x;
     const float *row = logits + (size_t)b * ldl;
     const int per = (V + n_blocks - 1) / n_blocks;
     const int i0 = blockIdx.x * per, n = max(0, min(V, i0 + per) - i0);
-    unsigned long long *out = cand + ((size_t)b * n_blocks + blockIdx.x) * k;
-    for (int i = tid; i < n; i += blockDim.x) keys[i] = float_key(row[i0 + i]);
-    for (int i = tid; i < k; i += blockDim.x) out[i] = 0ull;
-    __syncthreads();
-    if (n == 0) return;
-    const int kk = min(k, n);
-    uint32_t prefix = 0, mask = 0;
-    int need = kk;
-    for (int shift = 24; shift >= 0; shift -= 8) {
-        hist[tid] = 0;
-        __syncthreads();
-        for (int i = tid; i < n; i += blockDim.x)
-            if ((keys[i] & mask) == prefix) atomicAdd(&hist[(keys[i] >> shift) & 255], 1);
-        __syncthreads();
-        // the bin that holds the `need`-th largest matching key, by a suffix sum over the 256 bins with 256 threads
-        // (thread t takes bin 255 - t): the one whose running count reaches `need`.  One thread walking the bins took
-        // as long as the counting itself.
-        {
-            const int x = hist[255 - tid], lane = tid & 31, w = tid >> 5;
-            int incl = x;
+    unsigned long long w[TOPK_SEG / 256];
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) { int y = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += y; }
-            if (lane == 31) wsum[w] = incl;
-            if (tid == 0) { misc[0] = 0; misc[1] = need; }       // never kept: the matching keys are at least `need`
-            __syncthreads();
-            int before = 0;
-            for (int j = 0; j < w; j++) before += wsum[j];
-            incl += before;
-            if (incl >= need && incl - x < need) { misc[0] = 255 - tid; misc[1] = need - (incl - x); }
-        }
-        __syncthreads();
-        prefix |= (uint32_t)misc[0] << shift;
-        mask |= 255u << shift;
-        need = misc[1];
-        __syncthreads();
+    for (int j = 0; j < TOPK_SEG / 256; j++) {
+        const int i = tid + 256 * j;
+        w[j] = i < n ? (((unsigned long long)float_key(row[i0 + i]) << 32) | (uint32_t)(~(uint32_t)(i0 + i))) : 0ull;
     }
-    // everything above the k-th key, and the first `need` equal to it in index order
-    if (tid == 0) misc[2] = 0;
-    __syncthreads();
-    int taken_eq = 0;
-    for (int c0 = 0; c0 < n; c0 += blockDim.x) {
-        int i = c0 + tid;
-        uint32_t key = i < n ? keys[i] : 0u;
-        int gt = i < n && key > prefix, eq = i < n && key == prefix;
-        unsigned ball = __ballot_sync(0xffffffffu, eq);
-        int lane = tid & 31, w = tid >> 5;
-        if (lane == 0) wsum[w] = __popc(ball);
-        __syncthreads();
-        int before = 0, tot = 0;
-        for (int j = 0; j < 8; j++) { if (j < w) before += wsum[j]; tot += wsum[j]; }
-        int rank = taken_eq + before + __popc(ball & ((1u << lane) - 1));
-        if (gt || (eq && rank < need)) {
-            int at = atomicAdd(&misc[2], 1);
-            out[at] = ((unsigned long long)key << 32) | (uint32_t)(~(uint32_t)(i0 + i));
+    block_topk_ranked(w, K, sc, cand + ((size_t)b * n_blocks + blockIdx.x) * K);
+}
+
+// m chunks of K words in shared memory, each sorted descending (m and K powers of two) -> the K largest of all,
+// sorted descending, in w[0 .. K): chunk p takes max(A[i], B[K - 1 - i]) with its partner chunk p + m / 2, which
+// leaves the K largest of both as a bitonic sequence, and log2 K merge steps sort it again; the number of chunks
+// halves every round.  The time does not depend on the values.
+__device__ void topk_merge_desc(unsigned long long *w, int m, int K) {
+    const int k_log = __ffs(K) - 1;
+    for (; m > 1; m >>= 1) {
+        const int half = m >> 1;
+        for (int e = threadIdx.x; e < half * K; e += blockDim.x) {
+            const int p = e >> k_log, i = e & (K - 1);
+            const unsigned long long b = w[(p + half) * K + (K - 1 - i)];
+            if (b > w[e]) w[e] = b;
         }
-        taken_eq += tot;
         __syncthreads();
+        for (int s_log = k_log - 1; s_log >= 0; s_log--) {
+            for (int e = threadIdx.x; e < (half * K >> 1); e += blockDim.x) {
+                const int i = ((e >> s_log) << (s_log + 1)) + (e & ((1 << s_log) - 1)), j = i + (1 << s_log);
+                const unsigned long long x = w[i], y = w[j];
+                if (x < y) { w[i] = y; w[j] = x; }
+            }
+            __syncthreads();
+        }
     }
 }
 
-__global__ void __launch_bounds__(1024)
-topk_stage2_kernel(const unsigned long long *__restrict__ cand_in, int n_cand, int k, SampleParams sp,
+// Stage 2, one block per row: the K best of the segments' sorted candidates by merging, and the draw.  (Sorting all
+// candidates to use the first 64 took 31 us.)
+__global__ void __launch_bounds__(256)
+topk_stage2_kernel(const unsigned long long *__restrict__ cand_in, int n_chunks, int K, int k, SampleParams sp,
                    const int *__restrict__ seq_slot, unsigned long long *__restrict__ rng,
                    int *__restrict__ hist, int hist_cap, int *__restrict__ hist_count, int *__restrict__ out_tokens) {
     __shared__ unsigned long long cand[TOPK_CAND];
+    __shared__ float wgt[TOPK_MAX_K];
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.x, tid = threadIdx.x, slot = seq_slot[b];
-    for (int i = tid; i < TOPK_CAND; i += blockDim.x) cand[i] = i < n_cand ? cand_in[(size_t)b * n_cand + i] : 0ull;
+    int m = 1;
+    while (m < n_chunks) m <<= 1;                         // chunks beyond the segments are empty
+    for (int i = tid; i < m * K; i += blockDim.x) cand[i] = i < n_chunks * K ? cand_in[(size_t)b * n_chunks * K + i] : 0ull;
     __syncthreads();
-    for (int size = 2; size <= TOPK_CAND; size <<= 1) {
-        for (int stride = size >> 1; stride > 0; stride >>= 1) {
-            for (int i = tid; i < TOPK_CAND; i += blockDim.x) {
-                int j = i ^ stride;
-                if (j > i) {
-                    unsigned long long x = cand[i], y = cand[j];
-                    bool desc = (i & size) == 0;
-                    if (desc ? x < y : x > y) { cand[i] = y; cand[j] = x; }
+    topk_merge_desc(cand, m, K);
+    // the weights exp((v - top) / temp) of the k best, one thread each (0 beyond them: adding it changes no sum); the
+    // sums below add them in index order, as the serial sampler does (the same floats in the same order: the same token)
+    if (tid < TOPK_MAX_K)
+        wgt[tid] = (tid < k && tid < K && cand[tid] != 0ull)
+                       ? expf((key_float((uint32_t)(cand[tid] >> 32)) - key_float((uint32_t)(cand[0] >> 32))) / sp.temp) : 0.f;
+    __syncthreads();
+    const int n = __syncthreads_count(tid < k && tid < K && cand[tid] != 0ull);      // the candidates fill the front
+    if (tid == 0) {
+        // (weights are read eight at a time, ahead of the additions that wait for one another)
+        float sum = 0.f;
+#pragma unroll 16
+        for (int i = 0; i < TOPK_MAX_K; i++) sum += wgt[i];
+        int keep = n;
+        float tot = sum;
+        if (sp.top_p > 0.f && sp.top_p < 1.0f) {
+            float cum = 0.f;
+            const float lim = sp.top_p * sum;
+            bool found = false;
+            for (int i0 = 0; i0 < n && !found; i0 += 8) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] = wgt[i0 + j];
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    if (found || i0 + j >= n) continue;
+                    cum += v[j];
+                    if (cum >= lim) { keep = i0 + j + 1; found = true; }
                 }
             }
-            __syncthreads();
+            tot = cum;                                 // the same floats added in the same order as a sum over the kept ones
         }
-    }
-    // the weights exp((v - top) / temp) of the k best, one thread each; the sums below add them in index order,
-    // as the serial sampler does (the same floats in the same order: the same token)
-    __shared__ float wgt[TOPK_MAX_K];
-    if (tid < k) wgt[tid] = expf((key_float((uint32_t)(cand[tid] >> 32)) - key_float((uint32_t)(cand[0] >> 32))) / sp.temp);
-    __syncthreads();
-    if (tid == 0) {
-        int n = 0;
-        while (n < k && cand[n] != 0ull) n++;
-        float sum = 0.f;
-        for (int i = 0; i < n; i++) sum += wgt[i];
-        int keep = n;
-        if (sp.top_p > 0.f && sp.top_p < 1.0f) {
-            float cum = 0.f, lim = sp.top_p * sum;
-            for (int i = 0; i < n; i++) {
-                cum += wgt[i];
-                if (cum >= lim) { keep = i + 1; break; }
-            }
-        }
-        float tot = 0.f;
-        for (int i = 0; i < keep; i++) tot += wgt[i];
         uint64_t st = rng[slot];
         float r = (float)(xorshift64star(&st) >> 40) / 16777216.0f * tot;
         rng[slot] = st;
         int pick = keep - 1;
-        for (int i = 0; i < keep; i++) {
-            r -= wgt[i];
-            if (r < 0.f) { pick = i; break; }
+        bool found = false;
+        for (int i0 = 0; i0 < keep && !found; i0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = wgt[i0 + j];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                if (found || i0 + j >= keep) continue;
+                r -= v[j];
+                if (r < 0.f) { pick = i0 + j; found = true; }
+            }
         }
         int chosen = (int)(~(uint32_t)(cand[pick] & 0xffffffffull));
         out_tokens[b] = chosen;
@@ -503,6 +532,260 @@ greedy_kernel(const float *__restrict__ logits, int V, int ldl, const int *__res
     }
 }
 
+// ---- sampling without top-k (top_k <= 0) over a large vocabulary, on NUC_BLOCKS blocks a row.
+// The candidates are everything above max - 20 * temp (fastgguf.c:4027-4034); top-p keeps the most probable of them
+// whose mass reaches top_p * total (:4039-4047), here as a threshold on the logit found in two rounds of 2,048 bins
+// each over the candidates' range (entries that fall into the same one of the 4 million bins are kept or dropped
+// together); the draw walks the kept entries in index order (the same law as the reference's walk in sorted
+// order, another token for the same draw).  Masses are integers, exp((v - max) / temp) * 2^40: integer sums do not
+// depend on the order in which blocks arrive, so a row's token depends on its logits and its generator alone.
+// One block of 1,024 threads walking the whole row took 1.3 ms at a vocabulary of 128,256.
+// State of a row in the caller's scratch (64-bit words; all zero on entry, zero again when the last kernel ends):
+#define NUC_BLOCKS 32
+#define NUC_BINS 2048
+enum { NUC_MAX = 0, NUC_ARRIVE = 1, NUC_SUM = 2, NUC_NEED = 3, NUC_BIN1 = 4, NUC_BIN2 = 5, NUC_BLOCK = 6, NUC_REST = 7,
+       NUC_HIST = 16, NUC_MASS = NUC_HIST + NUC_BINS, NUC_WORDS = NUC_MASS + NUC_BLOCKS };
+static_assert(NUC_WORDS <= TOPK_CAND, "the state of a row fits the scratch row");
+
+struct NucleusRow {
+    float mx, inv_temp, width1, scale1, scale2;        // bins: width1 = 20 temp / 2048 of logit, scale = 1 / width
+    float cut;
+};
+__device__ __forceinline__ NucleusRow nucleus_row(unsigned long long max_word, float temp) {
+    NucleusRow r;
+    r.mx = key_float((uint32_t)(max_word >> 32));
+    r.inv_temp = 1.0f / temp;
+    r.cut = r.mx - 20.0f * temp;
+    r.width1 = 20.0f * temp / (float)NUC_BINS;
+    r.scale1 = (float)NUC_BINS / (20.0f * temp);
+    r.scale2 = r.scale1 * (float)NUC_BINS;
+    return r;
+}
+// the same roundings wherever they are evaluated (no contraction left to the compiler)
+__device__ __forceinline__ int nucleus_bin1(const NucleusRow &r, float v) {
+    return min(NUC_BINS - 1, max(0, (int)__fmul_rn(__fsub_rn(r.mx, v), r.scale1)));
+}
+__device__ __forceinline__ int nucleus_bin2(const NucleusRow &r, float v, int bin1) {
+    const float inside = __fsub_rn(__fsub_rn(r.mx, v), __fmul_rn((float)bin1, r.width1));
+    return min(NUC_BINS - 1, max(0, (int)__fmul_rn(inside, r.scale2)));
+}
+__device__ __forceinline__ unsigned long long nucleus_mass(const NucleusRow &r, float v) {
+    const unsigned long long m = (unsigned long long)__fmul_rn(expf(__fmul_rn(__fsub_rn(v, r.mx), r.inv_temp)), 1099511627776.0f);
+    return m ? m : 1ull;
+}
+// bin1 < 0: no top-p, every candidate is kept
+__device__ __forceinline__ bool nucleus_kept(const NucleusRow &r, float v, int bin1, int bin2) {
+    if (!(v > r.cut)) return false;
+    if (bin1 < 0) return true;
+    const int b1 = nucleus_bin1(r, v);
+    return b1 < bin1 || (b1 == bin1 && nucleus_bin2(r, v, bin1) <= bin2);
+}
+// true in every thread of the block that arrives last at the row's counter (which it resets)
+__device__ __forceinline__ bool nucleus_last_block(unsigned long long *st) {
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const bool last = atomicAdd(&st[NUC_ARRIVE], 1ull) == (unsigned long long)(NUC_BLOCKS - 1);
+        if (last) st[NUC_ARRIVE] = 0ull;
+        s_last = last;
+    }
+    __syncthreads();
+    __threadfence();
+    return s_last != 0;
+}
+// The first bin, counting from bin 0, at which the running sum of hist[] reaches `need` (there is one: the bins hold
+// at least `need`): its index and the sum before it.  256 threads, eight bins each; clears the histogram.
+__device__ __forceinline__ void nucleus_scan(unsigned long long *hist, unsigned long long need, unsigned long long *bin_out,
+                                             unsigned long long *before_out) {
+    __shared__ unsigned long long s_sum[256];
+    const int tid = threadIdx.x;
+    unsigned long long h[NUC_BINS / 256], mine = 0ull;
+#pragma unroll
+    for (int j = 0; j < NUC_BINS / 256; j++) { h[j] = __ldcg(&hist[tid * (NUC_BINS / 256) + j]); mine += h[j]; hist[tid * (NUC_BINS / 256) + j] = 0ull; }
+    s_sum[tid] = mine;
+    __syncthreads();
+    unsigned long long before = 0ull;
+    for (int t = 0; t < tid; t++) before += s_sum[t];
+    if (before < need && before + mine >= need) {
+#pragma unroll
+        for (int j = 0; j < NUC_BINS / 256; j++) {
+            if (before + h[j] >= need) { *bin_out = (unsigned long long)(tid * (NUC_BINS / 256) + j); *before_out = before; break; }
+            before += h[j];
+        }
+    }
+}
+
+// 1: the row's largest logit
+__global__ void __launch_bounds__(256)
+nucleus_max_kernel(const float *__restrict__ logits, int V, int ldl, unsigned long long *__restrict__ scratch, int stride) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ unsigned long long s_best[8];
+    const int b = blockIdx.y;
+    const float *row = logits + (size_t)b * ldl;
+    const int per = (V + NUC_BLOCKS - 1) / NUC_BLOCKS, i0 = blockIdx.x * per, i1 = min(V, i0 + per);
+    unsigned long long best = 0ull;
+    for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+        const unsigned long long w = ((unsigned long long)float_key(row[i]) << 32) | (uint32_t)(~(uint32_t)i);
+        best = w > best ? w : best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    if ((threadIdx.x & 31) == 0) s_best[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++) best = s_best[w] > best ? s_best[w] : best;
+        atomicMax(&scratch[(size_t)b * stride + NUC_MAX], best);
+    }
+}
+
+// 2 and 3: masses of the candidates by bin (round 1: of the whole range; round 2: inside the bin where round 1 found
+// the threshold); the block that arrives last finds the bin of the threshold
+__global__ void __launch_bounds__(256)
+nucleus_hist_kernel(const float *__restrict__ logits, int V, int ldl, float temp, float top_p, int round,
+                    unsigned long long *__restrict__ scratch, int stride) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ unsigned long long s_hist[NUC_BINS];
+    unsigned long long *st = scratch + (size_t)blockIdx.y * stride;
+    const float *row = logits + (size_t)blockIdx.y * ldl;
+    const NucleusRow r = nucleus_row(__ldcg(&st[NUC_MAX]), temp);
+    const int bin1 = round == 2 ? (int)__ldcg(&st[NUC_BIN1]) : 0;
+    const int per = (V + NUC_BLOCKS - 1) / NUC_BLOCKS, i0 = blockIdx.x * per, i1 = min(V, i0 + per);
+    for (int i = threadIdx.x; i < NUC_BINS; i += blockDim.x) s_hist[i] = 0ull;
+    __syncthreads();
+    unsigned long long total = 0ull;
+    for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+        const float v = row[i];
+        if (!(v > r.cut)) continue;
+        const unsigned long long m = nucleus_mass(r, v);
+        if (round == 1) { total += m; atomicAdd(&s_hist[nucleus_bin1(r, v)], m); }
+        else if (nucleus_bin1(r, v) == bin1) atomicAdd(&s_hist[nucleus_bin2(r, v, bin1)], m);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < NUC_BINS; i += blockDim.x)
+        if (s_hist[i]) atomicAdd(&st[NUC_HIST + i], s_hist[i]);
+    if (round == 1) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+        if ((threadIdx.x & 31) == 0 && total) atomicAdd(&st[NUC_SUM], total);
+    }
+    if (!nucleus_last_block(st)) return;
+    unsigned long long need;
+    if (round == 1) {
+        const unsigned long long sum = __ldcg(&st[NUC_SUM]);
+        need = (unsigned long long)((double)sum * (double)top_p);
+        need = need < 1ull ? 1ull : (need > sum ? sum : need);
+    } else need = __ldcg(&st[NUC_NEED]);
+    __shared__ unsigned long long s_bin, s_before;
+    nucleus_scan(st + NUC_HIST, need, &s_bin, &s_before);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        st[round == 1 ? NUC_BIN1 : NUC_BIN2] = s_bin;
+        st[NUC_NEED] = need - s_before;                 // what the next round has to find inside the bin
+    }
+}
+
+// 4: the kept mass of each block's entries; the block that arrives last draws and finds the block the draw falls into
+__global__ void __launch_bounds__(256)
+nucleus_mass_kernel(const float *__restrict__ logits, int V, int ldl, float temp, int with_top_p, const int *__restrict__ seq_slot,
+                    unsigned long long *__restrict__ rng, unsigned long long *__restrict__ scratch, int stride) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ unsigned long long s_w[8];
+    unsigned long long *st = scratch + (size_t)blockIdx.y * stride;
+    const float *row = logits + (size_t)blockIdx.y * ldl;
+    const NucleusRow r = nucleus_row(__ldcg(&st[NUC_MAX]), temp);
+    const int bin1 = with_top_p ? (int)__ldcg(&st[NUC_BIN1]) : -1, bin2 = with_top_p ? (int)__ldcg(&st[NUC_BIN2]) : 0;
+    const int per = (V + NUC_BLOCKS - 1) / NUC_BLOCKS, i0 = blockIdx.x * per, i1 = min(V, i0 + per);
+    unsigned long long total = 0ull;
+    for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+        const float v = row[i];
+        if (nucleus_kept(r, v, bin1, bin2)) total += nucleus_mass(r, v);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = total;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++) total += s_w[w];
+        st[NUC_MASS + blockIdx.x] = total;
+    }
+    if (!nucleus_last_block(st)) return;
+    if (threadIdx.x == 0) {
+        unsigned long long tot = 0ull;
+        for (int k = 0; k < NUC_BLOCKS; k++) tot += __ldcg(&st[NUC_MASS + k]);
+        const int slot = seq_slot[blockIdx.y];
+        uint64_t g = rng[slot];
+        const unsigned long long u = xorshift64star(&g) >> 40;          // 24 bits, as rng_uniform (fastgguf.c:3979-3981)
+        rng[slot] = g;
+        // r = u / 2^24 * tot, in integers: tot < 2^58, so the product needs its high word
+        unsigned long long rest = (__umul64hi(u, tot) << 40) | ((u * tot) >> 24);
+        int blk = 0;
+        for (; blk < NUC_BLOCKS - 1; blk++) {
+            const unsigned long long m = __ldcg(&st[NUC_MASS + blk]);
+            if (rest < m) break;
+            rest -= m;
+        }
+        st[NUC_BLOCK] = (unsigned long long)blk;
+        st[NUC_REST] = rest;
+    }
+}
+
+// 5: the block the draw fell into walks its entries in index order; it also writes the token and clears the state
+__global__ void __launch_bounds__(256)
+nucleus_walk_kernel(const float *__restrict__ logits, int V, int ldl, float temp, int with_top_p, const int *__restrict__ seq_slot,
+                    int *__restrict__ hist, int hist_cap, int *__restrict__ hist_count, int *__restrict__ out_tokens,
+                    unsigned long long *__restrict__ scratch, int stride) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ unsigned long long s_part[256];
+    unsigned long long *st = scratch + (size_t)blockIdx.x * stride;
+    const float *row = logits + (size_t)blockIdx.x * ldl;
+    const unsigned long long max_word = st[NUC_MAX];
+    const NucleusRow r = nucleus_row(max_word, temp);
+    const int bin1 = with_top_p ? (int)st[NUC_BIN1] : -1, bin2 = with_top_p ? (int)st[NUC_BIN2] : 0;
+    const int blk = (int)st[NUC_BLOCK];
+    const int per = (V + NUC_BLOCKS - 1) / NUC_BLOCKS, i0 = blk * per, i1 = min(V, i0 + per);
+    // thread t takes the entries [i0 + t * span, i0 + (t + 1) * span): the threads in order cover the block in index order
+    const int span = (per + 255) / 256, a0 = min(i1, i0 + (int)threadIdx.x * span), a1 = min(i1, a0 + span);
+    unsigned long long mine = 0ull;
+    for (int i = a0; i < a1; i++) { const float v = row[i]; if (nucleus_kept(r, v, bin1, bin2)) mine += nucleus_mass(r, v); }
+    s_part[threadIdx.x] = mine;
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    unsigned long long rest = st[NUC_REST];
+    int t = 0;
+    for (; t < 255; t++) { if (rest < s_part[t]) break; rest -= s_part[t]; }
+    int chosen = (int)(~(uint32_t)(max_word & 0xffffffffull));           // (never used: the walk ends inside the kept entries)
+    int last = -1;
+    const int b0 = min(i1, i0 + t * span), b1 = min(i1, b0 + span);
+    for (int i = b0; i < b1; i++) {
+        const float v = row[i];
+        if (!nucleus_kept(r, v, bin1, bin2)) continue;
+        last = i;
+        const unsigned long long m = nucleus_mass(r, v);
+        if (rest < m) break;
+        rest -= m;
+    }
+    if (last >= 0) chosen = last;
+    out_tokens[blockIdx.x] = chosen;
+    if (hist) {
+        const int slot = seq_slot[blockIdx.x];
+        int *h = hist + (size_t)slot * hist_cap;
+        int c = hist_count[slot];
+        if (c < hist_cap) h[c] = chosen;
+        else { for (int i = 1; i < hist_cap; i++) h[i - 1] = h[i]; h[hist_cap - 1] = chosen; }
+        hist_count[slot] = c + 1;
+    }
+    st[NUC_MAX] = 0ull; st[NUC_SUM] = 0ull; st[NUC_NEED] = 0ull; st[NUC_BIN1] = 0ull; st[NUC_BIN2] = 0ull;
+    st[NUC_BLOCK] = 0ull; st[NUC_REST] = 0ull;
+}
+
 extern "C" int fg_sample(float *logits, int B, int V, int ldl, float temp, int top_k, float top_p,
                          float repeat_penalty, int repeat_last_n, const int *seq_slot,
                          unsigned long long *rng, int *hist, int hist_cap, int *hist_count,
@@ -516,23 +799,41 @@ extern "C" int fg_sample(float *logits, int B, int V, int ldl, float temp, int t
                          seq_slot, hist, hist_cap, hist_count, out_tokens, scratch, TOPK_CAND);
     SampleParams sp{temp, top_p, repeat_penalty, top_k, repeat_last_n};
     if (temp > 0.f && top_k > 0 && top_k <= TOPK_MAX_K && scratch && B <= 65535) {
-        // two stages; `scratch` holds B * 2048 words
+        // two stages; `scratch` holds B * 4096 words
         int k = top_k < V ? top_k : V;
-        int n_blocks = TOPK_CAND / (k <= 64 ? 64 : 128);
-        if ((V + n_blocks - 1) / n_blocks <= TOPK_SEG) {
-            int kc = k <= 64 ? 64 : 128;                   // slots per block (>= k); unused ones stay zero
+        int K = k <= 64 ? 64 : 128;                        // words a segment hands over (>= k); unused ones are zero
+        int n_blocks = (V + TOPK_SEG - 1) / TOPK_SEG;
+        int padded = 1;
+        while (padded < n_blocks) padded <<= 1;               // the second stage merges a power of two of segments
+        if (padded * K <= TOPK_CAND) {
             if (penalizes) {
                 int e = fg_launch(penalty_kernel, dim3(B), dim3(64), 0, stream, logits, V, ldl, repeat_penalty,
                                   repeat_last_n, seq_slot, (const int *)hist, hist_cap, (const int *)hist_count, stop_ids, n_stop);
                 if (e) return e;
             }
             int e = fg_launch(topk_stage1_kernel, dim3(n_blocks, B), dim3(256), 0, stream, (const float *)logits, V, ldl,
-                              kc < k ? kc : k, n_blocks, scratch);
+                              K, n_blocks, scratch);
             if (e) return e;
-            int per_block = kc < k ? kc : k;
-            return fg_launch(topk_stage2_kernel, dim3(B), dim3(1024), 0, stream, (const unsigned long long *)scratch,
-                             n_blocks * per_block, k, sp, seq_slot, rng, hist, hist_cap, hist_count, out_tokens);
+            return fg_launch(topk_stage2_kernel, dim3(B), dim3(256), 0, stream, (const unsigned long long *)scratch,
+                             n_blocks, K, k, sp, seq_slot, rng, hist, hist_cap, hist_count, out_tokens);
         }
+    }
+    if (temp > 0.f && top_k <= 0 && scratch && B <= 65535 && V >= 8192) {
+        // no top-k over a large vocabulary: NUC_BLOCKS blocks a row, five short kernels
+        const int with_top_p = top_p > 0.f && top_p < 1.0f;
+        int e = 0;
+        if (penalizes)
+            e = fg_launch(penalty_kernel, dim3(B), dim3(64), 0, stream, logits, V, ldl, repeat_penalty, repeat_last_n, seq_slot,
+                          (const int *)hist, hist_cap, (const int *)hist_count, stop_ids, n_stop);
+        if (!e) e = fg_launch(nucleus_max_kernel, dim3(NUC_BLOCKS, B), dim3(256), 0, stream, (const float *)logits, V, ldl, scratch, TOPK_CAND);
+        for (int round = 1; round <= 2 && with_top_p && !e; round++)
+            e = fg_launch(nucleus_hist_kernel, dim3(NUC_BLOCKS, B), dim3(256), 0, stream, (const float *)logits, V, ldl, temp, top_p,
+                          round, scratch, TOPK_CAND);
+        if (!e) e = fg_launch(nucleus_mass_kernel, dim3(NUC_BLOCKS, B), dim3(256), 0, stream, (const float *)logits, V, ldl, temp,
+                              with_top_p, seq_slot, rng, scratch, TOPK_CAND);
+        if (!e) e = fg_launch(nucleus_walk_kernel, dim3(B), dim3(256), 0, stream, (const float *)logits, V, ldl, temp, with_top_p,
+                              seq_slot, hist, hist_cap, hist_count, out_tokens, scratch, TOPK_CAND);
+        return e;
     }
     sample_kernel<<<B, SAMPLE_THREADS, 0, stream>>>(logits, V, ldl, sp, seq_slot, rng, hist, hist_cap,
                                                     hist_count, stop_ids, n_stop, out_tokens);

@@ -237,9 +237,9 @@ def sample(logits: torch.Tensor, *, temp: float, top_k: int, top_p: float, repea
     cap = 0 if hist is None else hist.shape[1]
     n_stop = 0 if stop_ids is None else stop_ids.numel()
     scratch = None
-    if temp > 0 and 0 < top_k <= 128:
-        # candidates of the two-stage top-k: 2048 words a row
-        scratch = torch.empty((B, 2048), dtype=torch.int64, device=logits.device)
+    if temp > 0 and top_k <= 128:
+        # 4096 words a row: candidates of the two-stage top-k, or the state of the sampler without top-k (zero on entry)
+        scratch = torch.zeros((B, 4096), dtype=torch.int64, device=logits.device)
     check(lib().fg_sample(ptr(logits), B, V, logits.stride(0), float(temp), int(top_k), float(top_p),
                           float(repeat_penalty), int(repeat_last_n), ptr(_i32(seq_slot, "seq_slot")), ptr(rng),
                           ptr(hist), cap, ptr(hist_count), ptr(stop_ids), n_stop, ptr(out), ptr(scratch), stream()),

@@ -134,6 +134,27 @@ def test_sampler_matches_plain_token_for_token(V, opts):
             hists[b].append(tok)
 
 
+@pytest.mark.parametrize("V,top_k", [(150001, 64), (128256, 100), (70000, 128), (4097, 65)])
+def test_two_stage_top_k_at_large_vocabularies(V, top_k):
+    """Segment counts that are no power of two, 128 words a segment, and the best entries crowded into one segment."""
+    from fastgguf_b200 import ops
+    g = torch.Generator().manual_seed(V + top_k)
+    B = 3
+    logits = (torch.randn(B, V, generator=g) * 2).float()
+    logits[1, 5000:5000 + 200] += 30.0                               # every candidate of the row from one segment
+    logits[2, V - 1] = logits[2, 0] = logits[2].max() + 2.0          # a tie between the first and the last entry
+    seeds = [(0x9E3779B97F4A7C15 * (i + 3)) % 2 ** 64 for i in range(B)]
+    opts = dict(temp=0.9, top_k=top_k, top_p=0.97, repeat_penalty=1.0, repeat_last_n=0)
+    for rounds in range(2):
+        rng, rows = _sampler_state(B, seeds)
+        got = ops.sample(logits.clone().cuda(), seq_slot=rows, rng=rng, hist=None, hist_count=None, stop_ids=None, **opts).cpu().tolist()
+        for b in range(B):
+            tok, state = P.plain_sample(logits[b].numpy(), seeds[b], [], stop_ids=(), **opts)
+            assert got[b] == tok, (rounds, b)
+            assert rng[b].item() % 2 ** 64 == state
+            seeds[b] = state
+
+
 def test_sampler_without_top_k_follows_the_distribution():
     """top_k = 0 walks the candidates in index order: another token for the same draw, the same law."""
     from fastgguf_b200 import ops
@@ -149,6 +170,62 @@ def test_sampler_without_top_k_follows_the_distribution():
                       seq_slot=rows, rng=rng, hist=None, hist_count=None, stop_ids=None).cpu().numpy()
     freq = np.bincount(toks, minlength=4) / 4000.0
     assert np.abs(freq - [0.625, 0.375, 0, 0]).max() < 0.03
+
+
+def test_sampler_without_top_k_over_a_large_vocabulary():
+    """The kernels that split a row over many blocks: the law of the draw, the top-p cut, rows that do not depend on
+    their neighbours, and a state that is left clean for the next call."""
+    from fastgguf_b200 import ops
+    V, n = 20000, 3000
+    p = np.array([0.5, 0.3, 0.15, 0.05])
+    where = [7, 9000, 13001, V - 1]                                  # in different blocks of the row
+    base = torch.full((V,), -40.0)
+    for w, q in zip(where, p):
+        base[w] = float(np.log(q))
+    base[100] = float(np.log(0.5)) - 25.0                            # below max - 20 * temp: never a candidate
+    logits = base.repeat(n, 1).cuda()
+    seeds = [(0x9E3779B97F4A7C15 * (i + 1)) % 2 ** 64 for i in range(n)]
+    rng, rows = _sampler_state(n, seeds)
+    kw = dict(repeat_penalty=1.0, repeat_last_n=0, seq_slot=rows, rng=rng, hist=None, hist_count=None, stop_ids=None)
+    toks = ops.sample(logits.clone(), temp=1.0, top_k=0, top_p=1.0, **kw).cpu().numpy()
+    assert set(np.unique(toks)) <= set(where)
+    freq = np.array([(toks == w).mean() for w in where])
+    assert np.abs(freq - p).max() < 0.035
+    toks = ops.sample(logits.clone(), temp=1.0, top_k=0, top_p=0.6, **kw).cpu().numpy()
+    freq = np.array([(toks == w).mean() for w in where])
+    assert np.abs(freq - [0.625, 0.375, 0, 0]).max() < 0.035
+    # temperature 2: probabilities ~ sqrt(p), and the far entry is a candidate now
+    toks = ops.sample(logits.clone(), temp=2.0, top_k=0, top_p=1.0, **kw).cpu().numpy()
+    q = np.sqrt(np.append(p, 0.5 * np.exp(-25.0)))
+    q /= q.sum()
+    freq = np.array([(toks == w).mean() for w in where + [100]])
+    assert np.abs(freq - q).max() < 0.035
+    # random rows: alone or in a batch, the same generator state gives the same token; the second call starts clean
+    g = torch.Generator().manual_seed(5)
+    rnd = (torch.randn(6, 50000, generator=g) * 4).float().cuda()
+    outs = []
+    for rep in range(2):
+        rng6, rows6 = _sampler_state(6, seeds[:6])
+        outs.append(ops.sample(rnd.clone(), temp=0.8, top_k=0, top_p=0.9, repeat_penalty=1.0, repeat_last_n=0, seq_slot=rows6,
+                               rng=rng6, hist=None, hist_count=None, stop_ids=None).cpu().tolist())
+    assert outs[0] == outs[1]
+    for b in (0, 3, 5):
+        rng1, rows1 = _sampler_state(1, [seeds[b]])
+        alone = ops.sample(rnd[b:b + 1].clone(), temp=0.8, top_k=0, top_p=0.9, repeat_penalty=1.0, repeat_last_n=0, seq_slot=rows1,
+                           rng=rng1, hist=None, hist_count=None, stop_ids=None).cpu().tolist()
+        assert alone[0] == outs[0][b]
+    # the nucleus of a random row: every drawn token lies in the smallest set of most probable tokens that reaches top_p
+    row = rnd[0].double().cpu().numpy() / 0.8
+    pr = np.exp(row - row.max()); pr /= pr.sum()
+    order = np.argsort(-pr)
+    k = int(np.searchsorted(np.cumsum(pr[order]), 0.9)) + 1
+    nucleus = set(order[:k + 2].tolist())                            # (entries tied with the last one within a bin are kept too)
+    many = rnd[0:1].repeat(2000, 1)
+    rngm, rowsm = _sampler_state(2000, seeds[:2000])
+    drawn = ops.sample(many, temp=0.8, top_k=0, top_p=0.9, repeat_penalty=1.0, repeat_last_n=0, seq_slot=rowsm, rng=rngm,
+                       hist=None, hist_count=None, stop_ids=None).cpu().tolist()
+    assert set(drawn) <= nucleus
+    assert len(set(drawn)) > k // 3                                   # and it is not stuck on a few of them
 
 
 def test_decode_advance():
