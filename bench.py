@@ -10,9 +10,9 @@ context 8192 with prompts that end shortly before it, so that decoding runs near
 decode step of the whole batch.  ``value`` is decoded tokens a second timed on the device (CUDA events around K
 graph-replayed steps, the median of 5 such regions); ``e2e`` is the same through ``Engine.generate`` with host token
 lists in and out; ``prefill`` is one step of 2,048 prompt tokens; ``roofline`` divides the bytes a decode step has to
-read (every weight once, the cache of the live requests) by its time; ``points`` holds decode at batch 1 and 64 and
-``points_detail`` what each of them was made of.  Every step reads gigabytes of weights, far more than the 126 MB L2,
-so no flush is needed between timed steps.
+read (every weight once, the cache of the live requests) by its time; ``points`` holds decode at batch 1 and 64, and
+at the headline batch with the reference's default sampler instead of greedy; ``points_detail`` what each of them was
+made of.  Every step reads gigabytes of weights, far more than the 126 MB L2, so no flush is needed between timed steps.
 """
 import argparse
 import json
@@ -195,7 +195,7 @@ def main():
         lo = min(prompt_min, hi)
         return [rng.integers(0, c["vocab_size"], size=int(L)).tolist() for L in rng.integers(lo, hi + 1, size=n)]
 
-    def timed_decode(batch, warmup, steps, repeats):
+    def timed_decode(batch, warmup, steps, repeats, params=params):
         """(median ms per step over `repeats` regions of `steps` steps, launches per step, mean context tokens)."""
         prompts = make_prompts(batch, warmup + steps * repeats)
         session = engine.session(prompts, params)
@@ -304,6 +304,13 @@ def main():
             detail["decode_b%d" % b] = {"ms_per_step": round(ms_b, 4), "mean_context": round(ctx_b / b, 1), "bytes": int(bytes_b),
                                         "frac": round(bytes_b / (ms_b * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
                                         "sm_mhz": pc.summary()["sm_mhz"], "reasons": pc.summary()["reasons"]}
+        # the headline batch again with the reference's default sampler (temperature 1, top-k 64, top-p 0.95) instead of greedy
+        sampled = SamplingParams(temp=1.0, top_k=64, top_p=0.95, seed=1)
+        timed_decode(args.batch, 3, 3, 1, sampled)
+        ms_s, _, ctx_s, _ = timed_decode(args.batch, W, min(K, 128), REPEATS, sampled)
+        points["decode_b%d_sampled" % args.batch] = round(args.batch * 1000.0 / ms_s, 1)
+        detail["decode_b%d_sampled" % args.batch] = {"ms_per_step": round(ms_s, 4), "mean_context": round(ctx_s / args.batch, 1),
+                                                     "sampler": "temp 1.0 top_k 64 top_p 0.95"}
         rec["points"] = points
         rec["points_detail"] = detail
     print(json.dumps(rec))
