@@ -532,6 +532,7 @@ int fg_engine_stats(const fg_engine *e, char **json_out) {
         j.set("d2h_bytes", s.d2h_bytes);
         j.set("launches_per_step", s.launches_per_step);
         j.set("graphs", s.graphs);
+        j.set("backends", (long long)e->engine->backend_count());
         j.set("launches", launch_count());
         *json_out = dup_string(j.dump());
     });

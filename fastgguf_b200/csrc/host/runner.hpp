@@ -200,6 +200,7 @@ public:
     cudaStream_t stream = nullptr, capture_stream = nullptr;
     bool own_stream = false;
     struct Stats { long long steps = 0, h2d_bytes = 0, d2h_bytes = 0, launches_per_step = 0, graphs = 0; } stats;
+    size_t backend_count() const { return backends_.size(); }        // sets of sampling options kept with their graphs
 
 private:
     std::list<std::pair<std::string, std::unique_ptr<SamplingBackend>>> backends_;   // most recently used first

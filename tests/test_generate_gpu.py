@@ -93,3 +93,22 @@ def test_context_full_ends_with_length(models):
     out = engine.generate([random_tokens(60, cfg["vocab_size"], 90)], temp=0, max_tokens=0, ignore_eos=True)
     # 60 prompt tokens + 4 fed tokens fill the 64 positions; the 5th sampled token is still emitted
     assert len(out[0].tokens) == 5 and out[0].finish_reason == "length"
+
+
+def test_calls_that_differ_only_in_seed_share_one_backend_and_few_option_sets_are_kept(models):
+    """The recorded decode graphs belong to a set of sampling options, not to a seed: new seeds record nothing, and of
+    many option sets only the most recent few keep their graphs and activation memory."""
+    from fastgguf_b200.engine.api import Engine
+    d, cfg, _ = models["a"]
+    engine = Engine.from_dir(d, dtype="bfloat16", max_tokens=1024, max_batch=2)
+    prompts = [[3, 5, 7, 11], [2, 4]]
+    engine.generate(prompts, max_tokens=4, temp=0.9, top_k=8, top_p=0.9, seed=1, ignore_eos=True)
+    first = engine.stats()
+    assert first["backends"] == 1 and first["graphs"] >= 1
+    outs = [engine.generate(prompts, max_tokens=4, temp=0.9, top_k=8, top_p=0.9, seed=s, ignore_eos=True) for s in (2, 3, 2)]
+    after = engine.stats()
+    assert after["backends"] == 1 and after["graphs"] == first["graphs"]
+    assert [c.tokens for c in outs[0]] == [c.tokens for c in outs[2]]          # the seed still decides the tokens
+    for i in range(6):
+        engine.generate(prompts, max_tokens=2, temp=0.5 + 0.1 * i, top_k=8, top_p=0.9, seed=1, ignore_eos=True)
+    assert engine.stats()["backends"] <= 4
