@@ -23,6 +23,7 @@
 //   warp 1      MMA issuer (the same way): tcgen05.mma 128 x BN x 16; its commit frees the stage.
 //   warps 2-5   epilogue: tcgen05.ld of the f32 tile, then one of
 //               store bf16 | store f32 | add into f32 (residual) | silu(gate) * up -> bf16
+//               (the decode kernel has eight epilogue warps, 2-9: two per lane group of tensor memory)
 //
 // The silu epilogue expects the gate and up matrices interleaved in blocks of 64 rows
 // (g0..g63, u0..u63, g64..g127, ...): a 128-row weight tile then holds gate and up of the same
@@ -40,6 +41,9 @@
 #define BK 64           // K elements per stage: 64 bf16 = one 128-byte swizzle row
 #define UMMA_K 16
 #define GEMM_THREADS 192
+// decode kernel: producer, issuer and four epilogue warps at 16 token columns, eight at 32 and 64
+#define DEC_EPI_WARPS(BN) ((BN) >= 32 ? 8 : 4)
+#define DEC_THREADS(BN) (64 + 32 * DEC_EPI_WARPS(BN))
 #define WAIT_LIMIT_CYCLES 2000000000ll
 #define WAIT_SHORT_CYCLES 1000000ll
 
@@ -421,19 +425,21 @@ __device__ __forceinline__ void epilogue_add_coalesced(const GemmArgs &a, uint32
 #define MAX_STAGES 9
 
 template <int BN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(DEC_THREADS(BN), 1)
 gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmArgs a) {
     constexpr int W_BYTES = BM * BK * 2, X_BYTES = BN * BK * 2;
     constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
     constexpr int TMEM_COLS = BN <= 32 ? 32 : BN;
     constexpr int RES_AHEAD = 8;                  // residual values of the split-K sum fetched during the main loop
+    constexpr int EW = DEC_EPI_WARPS(BN), ET = 32 * EW;           // epilogue warps and threads
+    auto epi_sync = [] { asm volatile("bar.sync 1, %0;" ::"n"(ET) : "memory"); };
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms need 1 KB alignment
     __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 2];
     __shared__ uint32_t tmem_base_s;
     __shared__ float inv_s[BN];                   // 1/rms of the token columns (deferred norm), else 1
-    __shared__ float inv_part[128];               // partial sums on the way to inv_s
+    __shared__ float inv_part[256];               // partial sums on the way to inv_s
 
     const int warp = warp_index(), lane = threadIdx.x & 31;      // uniform: the role branches below are not divergent
     const int stages = a.stages, epi = a.epi, S = gridDim.z;
@@ -554,6 +560,11 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         // ------------------------------------------------------------ epilogue (warps 2..5)
         const int lg = warp & 3;                  // the TMEM lane group this warp may read
         const int prow = lg * 32 + lane;          // row of the tile this thread owns
+        // At 32 and 64 columns two warps share each lane group of tensor memory (warps 2..5 and 6..9) and take alternate
+        // runs of 16 columns: with one epilogue warp a scheduler every instruction's latency is exposed, and at 64
+        // columns the once-per-launch epilogue was two thirds of a split contraction's time (o: 8.3 -> 7.3 us a layer;
+        // at 16 columns the larger CTA cost 1 % of the step instead).
+        const int half = EW == 8 ? (warp - 2) >> 2 : 0, et = half * 128 + prow;
         const bool emit = epi == EPI_ADD_F32 && a.norm_w != nullptr;
         // the next norm's weights of the features this thread finishes (lane + 32 i): weights, so they are fetched
         // before the wait on the preceding kernel (a miss in L2 behind the weight tiles in flight takes microseconds)
@@ -565,32 +576,32 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         }
         pdl_wait();
         // 1/rms of the token columns of this tile, while the main loop runs
-        // (128 / BN threads per column, each striding over the tiles, and their sums added in thread order)
+        // (ET / BN threads per column, each striding over the tiles, and their sums added in thread order)
         {
-            constexpr int P = 128 / BN;
-            const int c = prow % BN, pp = prow / BN;
+            constexpr int P = ET / BN;
+            const int c = et % BN, pp = et / BN;
             const bool live = a.ss_in && q0 + c < a.M;
             float s = 0.f;
             if (live)
                 for (int tt = pp; tt < a.ss_tiles; tt += P) s += __ldcg(a.ss_in + (size_t)tt * a.M + q0 + c);
             inv_part[pp * BN + c] = s;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (prow < BN) {
+            epi_sync();
+            if (et < BN) {
                 float tot = 0.f;
 #pragma unroll
-                for (int p = 0; p < P; p++) tot += inv_part[p * BN + prow];
-                inv_s[prow] = live ? 1.0f / sqrtf(tot / (float)a.ss_size + a.ss_eps) : 1.0f;
+                for (int p = 0; p < P; p++) tot += inv_part[p * BN + et];
+                inv_s[et] = live ? 1.0f / sqrtf(tot / (float)a.ss_size + a.ss_eps) : 1.0f;
             }
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        epi_sync();
         if (split && epi == EPI_ADD_F32) {
-            // the residual values this thread adds to after the main loop: columns w and w + 4 of this CTA's share
+            // the residual values this thread adds to after the main loop: columns w and w + EW of this CTA's share
             const int per = BN / S, c_begin = blockIdx.z * per, w = warp - 2;
 #pragma unroll
             for (int j = 0; j < 2; j++)
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    const int cl = w + 4 * j, m = q0 + c_begin + cl, nn = p0 + lane + 32 * i;
+                    const int cl = w + EW * j, m = q0 + c_begin + cl, nn = p0 + lane + 32 * i;
                     res_pre[4 * j + i] = (cl < per && nn < a.N && m < a.M) ? __ldcg((const float *)a.out + (size_t)m * a.ldc + nn) : 0.f;
                 }
         }
@@ -611,18 +622,18 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             if (ok) {
                 float *ex = prow < 64 ? exg : exu;
 #pragma unroll 1
-                for (int c0 = 0; c0 < ncol; c0 += 16) {
+                for (int c0 = 16 * half; c0 < ncol; c0 += 4 * EW) {
                     float v[16];
                     tc_ld16(trow + c0, v);
 #pragma unroll
                     for (int j = 0; j < 16; j++) ex[(c0 + j) * 64 + (prow & 63)] = v[j];
                 }
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            epi_sync();
             const int fl = prow & 63, f = (p0 >> 1) + fl;
             if (ok && f < (a.N >> 1)) {
 #pragma unroll 1
-                for (int c = prow >> 6; c < ncol; c += 2) {         // the halves take alternate tokens
+                for (int c = et >> 6; c < ncol; c += EW / 2) {      // 64 threads a token
                     const float iv = inv_s[c];
                     ((bf16 *)a.out)[(size_t)(q0 + c) * a.ldc + f] =
                         __float2bfloat16_rn(silu_mul(exg[c * 64 + fl] * iv, exu[c * 64 + fl] * iv));
@@ -636,7 +647,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             const uint32_t recv0 = smem_u32(recv);
             const int groups = per >> vw_log;     // column groups an owner receives from each rank
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
+            for (int c0 = 16 * half; c0 < BN; c0 += 4 * EW) {
                 float v[16];
                 if (have) tc_ld16(trow + c0, v);
                 else {
@@ -674,7 +685,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             // for the cluster (the producer and issuer warps only close the barrier phase that opened at the top)
             if (warp < 2) { __syncwarp(); cluster_wait(); }
             else if (!mbar_wait(inbox, 0)) raise_error(5);
-        } else if (warp >= 2) asm volatile("bar.sync 1, 128;" ::: "memory");
+        } else if (warp >= 2) epi_sync();
         if (warp >= 2) {
             // A warp takes whole columns (tokens) here: its lanes cover the 128 features in four steps, so the sum of
             // squares of a column needs one warp reduction and no exchange between warps, and it comes before the
@@ -684,7 +695,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             const bool emit = epi == EPI_ADD_F32 && a.norm_w != nullptr;
             const float *part = split ? recv : (const float *)smem;
 #pragma unroll 1
-            for (int cl = w; cl < per; cl += 4) {
+            for (int cl = w; cl < per; cl += EW) {
                 const int m = q0 + c_begin + cl;
                 if (m >= a.M) break;                                               // tokens fill the columns from 0
                 float v[4];
@@ -719,7 +730,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
                     const int n = p0 + lane + 32 * i;
                     v[i] *= iv;
                     if (epi == EPI_ADD_F32 && n < a.N) {
-                        v[i] += (split && cl < 8) ? (cl < 4 ? res_pre[i] : res_pre[4 + i]) : ((const float *)a.out)[(size_t)m * a.ldc + n];
+                        v[i] += (split && cl < 2 * EW) ? (cl < EW ? res_pre[i] : res_pre[4 + i]) : ((const float *)a.out)[(size_t)m * a.ldc + n];
                         sq += v[i] * v[i];
                     }
                 }
@@ -1089,7 +1100,7 @@ static int launch_decode(const CUtensorMap &tmW, const CUtensorMap &tmX, GemmArg
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_decode_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
         if (e != cudaSuccess) return (int)e;
     }
-    return fg_launch_cluster(gemm_tc_decode_kernel<BN>, grid, dim3(GEMM_THREADS), (size_t)smem, stream, (int)grid.z, tmW, tmX, a);
+    return fg_launch_cluster(gemm_tc_decode_kernel<BN>, grid, dim3(DEC_THREADS(BN)), (size_t)smem, stream, (int)grid.z, tmW, tmX, a);
 }
 
 template <int BN, int STAGES, int EPI>
