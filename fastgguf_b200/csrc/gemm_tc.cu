@@ -340,17 +340,17 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
 //   residual: global -> (coalesced) -> tile;   thread = row: tile + accumulator -> new residual, x * w, sum of squares
 //   -> tile;   tile -> (coalesced) -> global.   16-byte chunks are swizzled by row, all accesses are conflict-free.
 template <int BN>
-__device__ __forceinline__ void epilogue_add_coalesced(const GemmArgs &a, uint32_t trow, int p0, int q0, int qt, int lg,
-                                                       int lane, uint8_t *stage) {
+__device__ __forceinline__ void epilogue_add_coalesced(const GemmArgs &a, uint32_t trow, int p0, int q0, int ss_index, int lg,
+                                                       int lane, uint8_t *stage, int c_begin = 0, int c_end = BN / 32) {
     float *T = (float *)stage;                    // [32][32] f32
     uint8_t *X = stage + 4096;                    // [32][32] bf16
     const int m_base = p0 + lg * 32, m_own = m_base + lane;
     const float iv = (a.ss_in && m_own < a.M) ? inv_rms(a, m_own) : 1.0f;
     float sq = 0.f;
-    // Every global load of a chunk is requested one chunk ahead, the norm weights too (behind the stores into the
-    // tile the compiler would not move them, and each would wait for L2 on its own).
-    float4 rl[8], g[8], rl_next[8], g_next[8];
-    auto request = [&](int c, float4 (&r)[8], float4 (&gw)[8]) {
+    // The residual values of a chunk are requested one chunk ahead, the norm weights of a chunk at its start (behind
+    // the stores into the tile the compiler would not move them, and each would wait for L2 on its own).
+    float4 rl[8], g[8], rl_next[8];
+    auto request = [&](int c, float4 (&r)[8]) {
         const int n0 = q0 + c * 32;
 #pragma unroll
         for (int pass = 0; pass < 8; pass++) {
@@ -358,16 +358,16 @@ __device__ __forceinline__ void epilogue_add_coalesced(const GemmArgs &a, uint32
             r[pass] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (m < a.M && n0 < a.N) r[pass] = __ldcg((const float4 *)((const float *)a.out + (size_t)m * a.ldc + n0) + ch);
         }
-#pragma unroll
-        for (int ch = 0; ch < 8; ch++)
-            gw[ch] = (a.norm_w && n0 < a.N) ? __ldg((const float4 *)(a.norm_w + n0) + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
     };
-    request(0, rl, g);
+    request(c_begin, rl);
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; c++) {
+    for (int c = c_begin; c < c_end; c++) {                // the chunks of 32 columns this warp takes
         const int n0 = q0 + c * 32;
         if (n0 >= a.N) break;
-        if (c + 1 < BN / 32) request(c + 1, rl_next, g_next);
+#pragma unroll
+        for (int ch = 0; ch < 8; ch++)
+            g[ch] = a.norm_w ? __ldg((const float4 *)(a.norm_w + n0) + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c + 1 < c_end) request(c + 1, rl_next);
 #pragma unroll
         for (int pass = 0; pass < 8; pass++) {
             const int row = pass * 4 + (lane >> 3), ch = lane & 7;
@@ -411,9 +411,9 @@ __device__ __forceinline__ void epilogue_add_coalesced(const GemmArgs &a, uint32
         }
         __syncwarp();
 #pragma unroll
-        for (int i = 0; i < 8; i++) { rl[i] = rl_next[i]; g[i] = g_next[i]; }
+        for (int i = 0; i < 8; i++) rl[i] = rl_next[i];
     }
-    if (a.norm_w && m_own < a.M) a.ss_out[(size_t)qt * a.M + m_own] = sq;
+    if (a.norm_w && m_own < a.M) a.ss_out[(size_t)ss_index * a.M + m_own] = sq;
 }
 
 // ---------------------------------------------------------------------------- decode: weights stream once
@@ -918,8 +918,13 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
+// The residual-add epilogue is exposed whole when a launch is one round of tiles (o and down at 2,048 rows), and with
+// one epilogue warp a scheduler every instruction's latency shows: that variant runs eight epilogue warps, two per
+// lane group of tensor memory, each half of the tile's columns (and writes two partial sums of squares a tile).
+#define PAIR_EPI_WARPS(EPI) ((EPI) == EPI_ADD_F32 ? 8 : 4)
+#define PAIR_THREADS(EPI) (64 + 32 * PAIR_EPI_WARPS(EPI))
 template <int BN, int STAGES, int EPI>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(PAIR_THREADS(EPI), 1)
 gemm_tc_prefill_pair_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, GemmArgs a,
                             int n_pt, int n_tiles) {
     constexpr int P_BYTES = BM * BK * 2, Q_BYTES = (BN / 2) * BK * 2;      // this CTA's share of a stage
@@ -942,7 +947,7 @@ gemm_tc_prefill_pair_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        for (int i = 0; i < 2; i++) { mbar_init(tfull0 + 8 * i, 1); mbar_init(tempty0 + 8 * i, 8); }   // 4 epilogue warps x 2 CTAs
+        for (int i = 0; i < 2; i++) { mbar_init(tfull0 + 8 * i, 1); mbar_init(tempty0 + 8 * i, 2 * PAIR_EPI_WARPS(EPI)); }   // epilogue warps x 2 CTAs
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -1016,9 +1021,10 @@ gemm_tc_prefill_pair_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs): this CTA's 128 rows
+        // ------------------------------------------------------------ epilogue (warps 2.., both CTAs): this CTA's 128 rows
         pdl_wait();
-        const int lg = warp & 3, prow = lg * 32 + lane;
+        constexpr int EW = PAIR_EPI_WARPS(EPI);
+        const int lg = warp & 3, prow = lg * 32 + lane, half = EW == 8 ? (warp - 2) >> 2 : 0;
         int i = 0;
         for (int tile = pair; tile < n_tiles; tile += n_pairs, i++) {
             const int acc = i & 1;
@@ -1028,9 +1034,12 @@ gemm_tc_prefill_pair_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
             tc_fence_after();
             const uint32_t trow = tmem_base + ((uint32_t)(lg * 32) << 16) + acc * BN;
             if (EPI == EPI_ADD_F32 && a.vec_ok && (a.N & 31) == 0)
-                epilogue_add_coalesced<BN>(a, trow, p0, qt * BN, qt, lg, lane, smem + STAGES * STAGE_BYTES + lg * EPI_STAGE_BYTES);
-            else
-                epilogue_token_major<BN, EPI>(a, trow, p0, qt * BN, qt, prow);
+                epilogue_add_coalesced<BN>(a, trow, p0, qt * BN, qt * (EW / 4) + half, lg, lane,
+                                           smem + STAGES * STAGE_BYTES + (half * 4 + lg) * EPI_STAGE_BYTES, half * (BN / 64), EW == 8 ? (half + 1) * (BN / 64) : BN / 32);
+            else if (half == 0)
+                epilogue_token_major<BN, EPI>(a, trow, p0, qt * BN, qt * (EW / 4), prow);
+            else if (EPI == EPI_ADD_F32 && a.norm_w && p0 + prow < a.M)
+                a.ss_out[(size_t)(qt * 2 + 1) * a.M + p0 + prow] = 0.f;      // the second partial sum of a tile the row-wise path leaves empty
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8 * acc);      // the leader's barrier counts both CTAs' warps
@@ -1124,7 +1133,7 @@ static int launch_prefill(const CUtensorMap &tmP, const CUtensorMap &tmQ, const 
 static int sm_count();
 template <int BN, int STAGES, int EPI>
 static int launch_prefill_pair(const CUtensorMap &tmP, const CUtensorMap &tmQ, const GemmArgs &a, cudaStream_t stream) {
-    constexpr int smem = STAGES * (BM + BN / 2) * BK * 2 + 1024 + (EPI == EPI_ADD_F32 ? 4 * EPI_STAGE_BYTES : 0);
+    constexpr int smem = STAGES * (BM + BN / 2) * BK * 2 + 1024 + (EPI == EPI_ADD_F32 ? PAIR_EPI_WARPS(EPI) * EPI_STAGE_BYTES : 0);
     static FgPerDevice configured;
     static int n_sm = 0;
     if (fg_needs_setup(configured)) {
@@ -1136,7 +1145,7 @@ static int launch_prefill_pair(const CUtensorMap &tmP, const CUtensorMap &tmQ, c
     int pairs = n_sm / 2;
     // the CTAs of a pair are neighbours along x
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * (n_tiles < pairs ? n_tiles : pairs), 1, 1); cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.gridDim = dim3(2 * (n_tiles < pairs ? n_tiles : pairs), 1, 1); cfg.blockDim = dim3(PAIR_THREADS(EPI));
     cfg.dynamicSmemBytes = smem; cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     int n = 0;
@@ -1164,7 +1173,7 @@ static int dispatch(bool swap, int bn, const CUtensorMap &tmP, const CUtensorMap
         }
     } else {
         switch (bn) {
-        case -256: return launch_prefill_pair<256, 6, EPI>(tmP, tmQ, a, st);
+        case -256: return launch_prefill_pair<256, EPI == EPI_ADD_F32 ? 5 : 6, EPI>(tmP, tmQ, a, st);      // (room for eight epilogue tiles)
         case 128: return launch_prefill<128, 6, EPI>(tmP, tmQ, a, st);
         case 192: if (EPI != EPI_SILU_MUL) return launch_prefill<192, 5, EPI == EPI_SILU_MUL ? EPI_BF16 : EPI>(tmP, tmQ, a, st); break;
         case 256: return launch_prefill<256, 4, EPI>(tmP, tmQ, a, st);
@@ -1250,7 +1259,7 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
     if (e) return e;
     int esz = (epi == EPI_F32 || epi == EPI_ADD_F32) ? 4 : 2;
     int vec_ok = ((uintptr_t)out % 16 == 0) && ((size_t)ldc * esz % 16 == 0);
-    if (ss_tiles_out) *ss_tiles_out = (int)grid.y;
+    if (ss_tiles_out) *ss_tiles_out = (int)grid.y * (bn == -256 && epi == EPI_ADD_F32 ? 2 : 1);
     GemmArgs a{out, M, N, K, ldc, kb_per_split, vec_ok, ss_in, ss_tiles, ss_size, ss_eps, norm_w, (bf16 *)xw_out, ss_out, epi, 0,
                g_test_skip_copy};
     switch (epi) {
