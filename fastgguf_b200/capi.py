@@ -159,6 +159,8 @@ _SIGNATURES = {
                     TOKEN_CALLBACK, c_void_p, P(c_void_p)],
     "fg_result_get": [c_void_p, c_int, P(P(c_int)), P(c_int), P(c_int)],
     "fg_engine_stats": [c_void_p, P(c_void_p)],
+    "fg_engine_profile": [c_void_p, c_int],
+    "fg_engine_profile_report": [c_void_p, P(c_void_p)],
     "fg_session_begin": [c_void_p, c_int, P(c_int), P(c_int64), P(Sampling), P(c_int), c_int, P(c_void_p)],
     "fg_session_advance": [c_void_p, P(c_int), c_int],
     "fg_session_slots": [c_void_p, P(c_int)],

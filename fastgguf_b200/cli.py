@@ -30,7 +30,8 @@ CHAT_OPTIONS_HELP = (
     "                  --prompt ID,ID,...  (repeat for a batch)  --prompts-file FILE (one prompt a line)\n"
     "                  --stop-id ID (repeat; added to the model's own stop tokens)\n"
     "                  --dtype bfloat16|float32  --batch N  --ignore-eos  --json\n"
-    "                  --stream  (print \"request token\" lines to the standard error as tokens are made)\n")
+    "                  --stream  (print \"request token\" lines to the standard error as tokens are made)\n"
+    "                  --profile (device time per kernel launcher; runs the kernels one after another)\n")
 
 
 class UsageError(Exception):
@@ -40,8 +41,9 @@ class UsageError(Exception):
 def parse_generate_args(argv: List[str]) -> dict:
     """Positional [ctx], then --option value pairs (fastgguf.c:6957-6974)."""
     o = dict(ctx=2048, temp=1.0, top_k=64, top_p=0.95, repeat_penalty=1.0, repeat_last_n=64, max_tokens=512,
-             seed=0, prompts=[], stop_ids=[], dtype="bfloat16", batch=None, ignore_eos=False, json=False, stream=False)
-    flags = {"--ignore-eos": "ignore_eos", "--json": "json", "--stream": "stream"}
+             seed=0, prompts=[], stop_ids=[], dtype="bfloat16", batch=None, ignore_eos=False, json=False, stream=False,
+             profile=False)
+    flags = {"--ignore-eos": "ignore_eos", "--json": "json", "--stream": "stream", "--profile": "profile"}
     valued = {"--temp": ("temp", float), "--top-k": ("top_k", int), "--top-p": ("top_p", float),
               "--repeat-penalty": ("repeat_penalty", float), "--repeat-last-n": ("repeat_last_n", int),
               "--max-tokens": ("max_tokens", int), "--seed": ("seed", int), "--dtype": ("dtype", str),
@@ -115,6 +117,8 @@ def cmd_generate(model_dir: str, argv: List[str]) -> int:
         say(f"[Sampler] temp={o['temp']:.2f} top_k={o['top_k']} top_p={o['top_p']:.2f}", end="")
     say(f" repeat_penalty={o['repeat_penalty']:.2f} (last {o['repeat_last_n']}) max_tokens={o['max_tokens']} "
         f"seed={o['seed']}")
+    if o["profile"]:
+        engine.profile(True)
     t0 = time.time()
     try:
         out = engine.generate(o["prompts"], temp=o["temp"], top_k=o["top_k"], top_p=o["top_p"],
@@ -133,6 +137,13 @@ def cmd_generate(model_dir: str, argv: List[str]) -> int:
         for i, c in enumerate(out):
             print(f"[{i}] {' '.join(str(t) for t in c.tokens)}  ({c.finish_reason})")
     say(f"[gen: {n_gen} tok in {dt:.2f}s @ {n_gen / max(dt, 1e-9):.2f} tok/s, prompts included]")
+    if o["profile"]:
+        # device time per kernel launcher, kernels run one after another (no graphs, no overlap of dependent launches)
+        rows = engine.profile_report()
+        total = sum(r["ms"] for r in rows) or 1.0
+        say(f"[profile] {sum(r['calls'] for r in rows)} launches, {total:.3f} ms on the device")
+        for r in rows[:24]:
+            say(f"[profile] {r['ms']:10.3f} ms {100 * r['ms'] / total:5.1f} %  {r['calls']:6d} x  {r['name']}")
     return 0
 
 

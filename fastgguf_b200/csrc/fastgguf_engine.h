@@ -179,6 +179,12 @@ int fg_result_get(const fg_result *r, int i, const int **tokens, int *n_tokens, 
 void fg_result_destroy(fg_result *r);
 /* {"steps", "h2d_bytes", "d2h_bytes", "launches_per_step", "graphs"} accumulated over fg_generate calls. */
 int fg_engine_stats(const fg_engine *e, char **json_out);
+/* Per-launcher device times.  While on, every kernel launcher call of this engine is bracketed by two events (kernels
+ * then run one after another, without the overlap of dependent launches) and fg_generate runs its decode steps
+ * eagerly; fg_session_begin is refused.  The report is a JSON list [{"name", "calls", "ms"}], longest first, of
+ * everything launched since profiling was switched on or last reported.  One engine at a time. */
+int fg_engine_profile(fg_engine *e, int on);
+int fg_engine_profile_report(fg_engine *e, char **json_out);
 
 /* A batch on the graph path, step by step (what the benchmark times): begin runs the prompts and samples
  * the first tokens; each advance runs one decode step for the sequences `live` (indices into the batch). */

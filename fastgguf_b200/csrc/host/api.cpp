@@ -538,12 +538,27 @@ int fg_engine_stats(const fg_engine *e, char **json_out) {
     });
 }
 
+int fg_engine_profile(fg_engine *e, int on) {
+    return guarded([&] {
+        NEED(e);
+        profile_enable(on != 0, e->engine->stream);
+    });
+}
+
+int fg_engine_profile_report(fg_engine *e, char **json_out) {
+    return guarded([&] {
+        NEED(e); NEED(json_out);
+        *json_out = dup_string(profile_report_json());
+    });
+}
+
 int fg_session_begin(fg_engine *e, int n_prompts, const int *prompt_tokens, const int64_t *offsets, const fg_sampling *sampling,
                      const int *stop_ids, int n_stop, fg_session **out) {
     return guarded([&] {
         NEED(e); NEED(out); NEED(prompt_tokens); NEED(offsets);
         auto prompts = prompts_from(n_prompts, prompt_tokens, offsets);
         if (prompts.empty()) fail(FG_E_USAGE, "a batch needs at least one prompt");
+        if (profile_on()) fail(FG_E_USAGE, "a session replays recorded graphs, whose kernels cannot be timed one by one: profile through generate");
         SamplingParams p = params_from(sampling);
         SamplingBackend &b = e->engine->backend(p, int_list(stop_ids, n_stop, "stop_ids"));
         b.seed = resolve_seed(p.seed);

@@ -3,10 +3,12 @@
 
 #include <dlfcn.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdlib>
 #include <map>
 #include <mutex>
+#include <vector>
 
 namespace fg {
 
@@ -30,6 +32,69 @@ static std::atomic<long long> g_launches{0};
 
 long long launch_count() { return g_launches.load(); }
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+// ---- per-launcher times
+namespace {
+struct ProfileRecord { std::string name; cudaEvent_t begin, end; };
+struct ProfileState {
+    bool on = false;
+    cudaStream_t stream = nullptr;
+    std::vector<ProfileRecord> records;
+} g_profile;
+}  // namespace
+
+static void profile_clear() {
+    for (auto &r : g_profile.records) { cudaEventDestroy(r.begin); cudaEventDestroy(r.end); }
+    g_profile.records.clear();
+}
+
+void profile_enable(bool on, cudaStream_t stream) {
+    if (g_profile.on && g_profile.stream) cudaStreamSynchronize(g_profile.stream);
+    profile_clear();
+    g_profile.on = on;
+    g_profile.stream = stream;
+}
+
+bool profile_on() { return g_profile.on; }
+
+ProfileScope::ProfileScope(const char *name, const char *detail) {
+    if (!g_profile.on) return;
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(g_profile.stream, &st) != cudaSuccess || st != cudaStreamCaptureStatusNone) return;
+    ProfileRecord r;
+    r.name = detail ? std::string(name) + " " + detail : std::string(name);
+    if (cudaEventCreate(&r.begin) != cudaSuccess) return;
+    if (cudaEventCreate(&r.end) != cudaSuccess) { cudaEventDestroy(r.begin); return; }
+    cudaEventRecord(r.begin, g_profile.stream);
+    index = (int)g_profile.records.size();
+    g_profile.records.push_back(std::move(r));
+}
+
+ProfileScope::~ProfileScope() {
+    if (index >= 0 && index < (int)g_profile.records.size()) cudaEventRecord(g_profile.records[(size_t)index].end, g_profile.stream);
+}
+
+std::string profile_report_json() {
+    if (g_profile.stream) FG_CUDA(cudaStreamSynchronize(g_profile.stream));
+    std::map<std::string, std::pair<long long, double>> by_name;
+    for (auto &r : g_profile.records) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, r.begin, r.end) != cudaSuccess) continue;
+        auto &e = by_name[r.name];
+        e.first++;
+        e.second += ms;
+    }
+    profile_clear();
+    std::vector<std::pair<std::string, std::pair<long long, double>>> rows(by_name.begin(), by_name.end());
+    std::sort(rows.begin(), rows.end(), [](const auto &a, const auto &b) { return a.second.second > b.second.second; });
+    std::string out = "[";
+    for (size_t i = 0; i < rows.size(); i++) {
+        std::string name;
+        for (char c : rows[i].first) { if (c == '"' || c == '\\') name += '\\'; name += c; }
+        out += format("%s{\"name\": \"%s\", \"calls\": %lld, \"ms\": %.6f}", i ? ", " : "", name.c_str(), rows[i].second.first, rows[i].second.second);
+    }
+    return out + "]";
+}
 
 static std::string own_folder() {
     Dl_info info;

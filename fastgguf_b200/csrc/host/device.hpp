@@ -33,8 +33,21 @@ void count_launch();
 #define FG_LAUNCH(module, fn, ...)                                                                           \
     do {                                                                                                     \
         ::fg::count_launch();                                                                                \
+        ::fg::ProfileScope fg_profile_scope_(#fn);                                                           \
         ::fg::check_kernel(FG_KERNEL(module, fn)(__VA_ARGS__), #fn);                                         \
     } while (0)
+// Per-launcher device times, for `--profile`: while it is on, every launcher call is bracketed by two events on
+// `stream` (which also ends the overlap of dependent launches: the times are those of kernels running one after
+// another) and decode steps run eagerly, since events inside a recorded graph cannot be read.  One engine at a time.
+void profile_enable(bool on, cudaStream_t stream);
+bool profile_on();
+// [{"name": launcher (and shape), "calls": n, "ms": total}, ...] by falling time; waits for the stream, clears the records
+std::string profile_report_json();
+struct ProfileScope {
+    explicit ProfileScope(const char *name, const char *detail = nullptr);
+    ~ProfileScope();
+    int index = -1;
+};
 // Reads and clears the error flags of the kernel libraries that are loaded; throws FG_E_KERNEL if one is set.
 void raise_on_device_error(const char *where);
 

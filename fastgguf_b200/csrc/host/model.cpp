@@ -1,6 +1,8 @@
 // See model.hpp.
 #include "model.hpp"
 
+#include <cstdlib>
+
 #include <algorithm>
 #include <cstring>
 #include <regex>
@@ -82,6 +84,10 @@ DecoderModel::DecoderModel(const ModelSpec &spec_, int dtype, int device, cudaSt
     int n_sm = 0;
     FG_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device));
     runtime.n_sm = n_sm;
+    // FASTGGUF_PLAIN_KERNELS=1: the any-size FMA kernels everywhere - the same results up to rounding, slower; a safety
+    // switch in the manner of the reference's FASTGGUF_BATCH=0 (fastgguf.c:5126-5127).  Read when an engine is made.
+    const char *plain = getenv("FASTGGUF_PLAIN_KERNELS");
+    runtime.plain_kernels = plain && plain[0] == '1';
     embedding_ = dynamic_cast<Embedding *>(build(FG_ROLE_EMBEDDING, spec.embedding));
     for (auto &layer : spec.layers) {
         Mixer *mixer = dynamic_cast<Mixer *>(build(FG_ROLE_MIXER, layer.mixer));

@@ -138,7 +138,7 @@ Tensor Linear::forward(Runtime &rt, const Tensor &a_in, const DeferredNorm *defe
     if (!out.defined()) out = rt.arena->matrix(M, N, out_dtype);
     if (out.rows != M || out.cols != N) fail(FG_E_INTERNAL, "contraction: the output has the wrong shape");
     if (M == 0) return out;
-    if (fast_ && a.dtype == FG_BF16 && (out.dtype == FG_BF16 || out.dtype == FG_F32)) {
+    if (fast_ && !rt.plain_kernels && a.dtype == FG_BF16 && (out.dtype == FG_BF16 || out.dtype == FG_F32)) {
         int epi = accumulate ? EPI_ADD_F32 : out.dtype == FG_BF16 ? EPI_BF16 : EPI_F32;
         const float *ss_in = nullptr;
         int ss_tiles = 0, ss_size = 1;
@@ -156,6 +156,7 @@ Tensor Linear::forward(Runtime &rt, const Tensor &a_in, const DeferredNorm *defe
         }
         int tiles_out = 0;
         count_launch();
+        ProfileScope scope("fg_gemm_tc", profile_on() ? format("%lld x %lld, %lld rows%s", (long long)N, (long long)K, (long long)M, accumulate ? ", residual add" : "").c_str() : nullptr);
         int code = FG_KERNEL("tc", fg_gemm_tc)(a.data, (int)a.ld, W.data, (int)W.ld, out.data, (int)out.ld, epi, (int)M, (int)N,
                                                (int)K, 0, ss_in, ss_tiles, ss_size, ss_eps, norm_w, xw_out.data, ss_out,
                                                &tiles_out, rt.stream);
@@ -177,7 +178,7 @@ Tensor Linear::forward(Runtime &rt, const Tensor &a_in, const DeferredNorm *defe
 bool Linear::forward_silu(Runtime &rt, const Tensor &a_in, const DeferredNorm *deferred, Tensor *out) const {
     const Tensor &W = w_.t;
     Tensor a = deferred ? deferred->xw : a_in;
-    if (!fast_ || a.dtype != FG_BF16 || W.rows % 128) return false;
+    if (!fast_ || rt.plain_kernels || a.dtype != FG_BF16 || W.rows % 128) return false;
     const int64_t M = a.rows, F = W.rows / 2;
     Tensor t = rt.arena->matrix(M, F, FG_BF16);
     if (M == 0) { *out = t; return true; }
@@ -186,6 +187,7 @@ bool Linear::forward_silu(Runtime &rt, const Tensor &a_in, const DeferredNorm *d
     float ss_eps = 0.f;
     if (deferred) { ss_in = deferred->ss; ss_tiles = deferred->tiles; ss_size = deferred->size; ss_eps = deferred->eps; }
     count_launch();
+    ProfileScope scope("fg_gemm_tc", profile_on() ? format("%lld x %lld, %lld rows, silu", (long long)W.rows, (long long)a.cols, (long long)M).c_str() : nullptr);
     int code = FG_KERNEL("tc", fg_gemm_tc)(a.data, (int)a.ld, W.data, (int)W.ld, t.data, (int)t.ld, EPI_SILU_MUL, (int)M,
                                            (int)W.rows, (int)a.cols, 0, ss_in, ss_tiles, ss_size, ss_eps, nullptr, nullptr,
                                            nullptr, &tiles_out, rt.stream);
@@ -212,8 +214,8 @@ int decode_splits(int n_sm, int n_seq, int n_heads, int n_kv_heads, int table_wi
     return s;
 }
 
-static bool fast_attention_ok(const Tensor &q, const LayerIO &io, int head_dim) {
-    return q.dtype == FG_BF16 && io.cache_dtype == FG_BF16 && (head_dim == 64 || head_dim == 128) && io.page_size == 64 &&
+static bool fast_attention_ok(const Runtime &rt, const Tensor &q, const LayerIO &io, int head_dim) {
+    return !rt.plain_kernels && q.dtype == FG_BF16 && io.cache_dtype == FG_BF16 && (head_dim == 64 || head_dim == 128) && io.page_size == 64 &&
            q.ld % 2 == 0 && ((uintptr_t)q.data % 4) == 0;
 }
 
@@ -221,7 +223,7 @@ static Tensor attention(Runtime &rt, const Tensor &q, const Batch &b, const Laye
                         int window) {
     const int *table = b.block_tables.at((size_t)io.group);
     Tensor out = rt.arena->matrix(q.rows, (int64_t)H * hd, q.dtype);
-    if (fast_attention_ok(q, io, hd)) {
+    if (fast_attention_ok(rt, q, io, hd)) {
         if (b.single_token) {
             int n_splits = decode_splits(rt.n_sm, b.n_seq, H, KV, b.table_width, hd);
             float *part_o = nullptr, *part_ml = nullptr;
@@ -259,7 +261,7 @@ Tensor rope_attention(Runtime &rt, const Tensor &qkv, const Batch &b, const Laye
     // A decode step in bfloat16 with head size 64 / 128 on the entry's own cache runs as ONE kernel.  It reads
     // positions, the page table and its own pages before waiting for the kernel in front of it; see common.cuh
     // for why that is allowed here and only here.
-    if (io.write_cache && b.single_token && fast_attention_ok(qkv, io, hd) && qkv.ld % 8 == 0 && ((uintptr_t)qkv.data % 16) == 0) {
+    if (io.write_cache && b.single_token && fast_attention_ok(rt, qkv, io, hd) && qkv.ld % 8 == 0 && ((uintptr_t)qkv.data % 16) == 0) {
         int n_splits = decode_splits(rt.n_sm, b.n_seq, H, KV, b.table_width, hd);
         if (n_splits == 1 || n_splits == 2 || n_splits == 4 || n_splits == 8) {
             Tensor out = rt.arena->matrix(qkv.rows, (int64_t)H * hd, FG_BF16);
@@ -536,7 +538,7 @@ public:
         const Weight &g = tensor_of(tensors, "gate_proj.weight"), &u = tensor_of(tensors, "up_proj.weight");
         int dt = g.t.dtype == u.t.dtype ? g.t.dtype : FG_F32;
         Weight both = concat_rows({g, u}, dt, rt.stream);
-        if (dt == FG_BF16 && F_ % 64 == 0 && E_ % 8 == 0) {
+        if (dt == FG_BF16 && F_ % 64 == 0 && E_ % 8 == 0 && !rt.plain_kernels) {
             // gate, up and SiLU-mul in one tensor-core kernel: rows interleaved in blocks of 64
             std::vector<int64_t> rows;
             for (int64_t blk = 0; blk < F_ / 64; blk++) {

@@ -28,6 +28,7 @@ struct Runtime {
     cudaStream_t stream = nullptr;
     Arena *arena = nullptr;           // activations of the step being run
     bool recording = false;           // the step is being recorded into a CUDA graph
+    bool plain_kernels = false;       // the safety switch: the any-size FMA kernels everywhere, bfloat16 included
 };
 
 struct TensorDecl {

@@ -483,7 +483,7 @@ std::vector<Completion> Engine::generate(const std::vector<std::vector<int>> &pr
     b.seed = resolve_seed(params.seed);
     if (batch_size <= 0) batch_size = opts.max_batch;
     if (batch_size > opts.max_batch) fail(FG_E_USAGE, format("batch_size %d exceeds the engine's %d sequence slots", batch_size, opts.max_batch));
-    bool graphs = use_graphs < 0 ? opts.use_graphs : use_graphs != 0;
+    bool graphs = (use_graphs < 0 ? opts.use_graphs : use_graphs != 0) && !profile_on();
     std::vector<Completion> out;
     for (auto &rng : plan_batches((int)prompts.size(), batch_size)) {
         std::vector<std::vector<int>> part(prompts.begin() + rng.first, prompts.begin() + rng.second);

@@ -203,6 +203,15 @@ class Engine:
     def stats(self) -> dict:
         return capi.take_json(capi.lib().fg_engine_stats, self._handle)
 
+    def profile(self, on: bool = True) -> None:
+        """Per-launcher device times: while on, kernels run one after another between two events each, and ``generate``
+        runs its decode steps eagerly (sessions are refused)."""
+        capi.check(capi.lib().fg_engine_profile(self._handle, 1 if on else 0))
+
+    def profile_report(self) -> list:
+        """``[{"name", "calls", "ms"}, ...]``, longest first, of everything launched since ``profile(True)`` or the last report."""
+        return capi.take_json(capi.lib().fg_engine_profile_report, self._handle)
+
     def check_device(self) -> None:
         """Wait for the engine's stream; raise if a bounded wait inside a kernel ran out."""
         capi.check(capi.lib().fg_engine_check_device(self._handle))

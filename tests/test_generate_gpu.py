@@ -112,3 +112,46 @@ def test_calls_that_differ_only_in_seed_share_one_backend_and_few_option_sets_ar
     for i in range(6):
         engine.generate(prompts, max_tokens=2, temp=0.5 + 0.1 * i, top_k=8, top_p=0.9, seed=1, ignore_eos=True)
     assert engine.stats()["backends"] <= 4
+
+
+def test_profile_lists_launchers_and_records_no_graph(models):
+    from fastgguf_b200.engine.api import Engine
+    d, cfg, W = models["b"]
+    engine = Engine.from_dir(d, dtype="bfloat16", max_tokens=1024, max_batch=2)
+    prompts = [[3, 5, 7, 11, 13], [2, 4]]
+    plain = engine.generate(prompts, max_tokens=5, temp=0, ignore_eos=True, use_graphs=False)
+    engine.profile(True)
+    out = engine.generate(prompts, max_tokens=5, temp=0, ignore_eos=True)
+    rows = engine.profile_report()
+    engine.profile(False)
+    assert [c.tokens for c in out] == [c.tokens for c in plain]              # eager steps: the same tokens
+    names = {r["name"].split(" ")[0] for r in rows}
+    assert rows and all(r["calls"] > 0 and r["ms"] > 0 for r in rows)
+    assert "fg_gemm_tc" in names or "fg_gemm_generic" in names
+    assert any(n.startswith("fg_attention") or n.startswith("fg_rope") for n in names)
+    assert rows == sorted(rows, key=lambda r: -r["ms"])
+    assert engine.profile_report() == []                                       # a report clears the records
+
+
+def test_plain_kernels_switch_gives_the_same_tokens(models, monkeypatch):
+    """FASTGGUF_PLAIN_KERNELS=1 puts a bfloat16 engine on the any-size kernels: the same results up to rounding."""
+    from fastgguf_b200.engine.api import Engine
+    from fastgguf_b200.engine.batch import StepEntry
+    d, cfg, W = models["a"]
+    toks = random_tokens(40, cfg["vocab_size"], 9)
+    fast = Engine.from_dir(d, dtype="bfloat16", max_tokens=256, max_batch=1)
+    monkeypatch.setenv("FASTGGUF_PLAIN_KERNELS", "1")
+    slow = Engine.from_dir(d, dtype="bfloat16", max_tokens=256, max_batch=1)
+    monkeypatch.delenv("FASTGGUF_PLAIN_KERNELS")
+    got = []
+    for e in (fast, slow):
+        e.profile(True)
+        s = e.acquire()
+        got.append(np.asarray(e.step_host([StepEntry(s, toks, list(range(len(toks))))])))
+        e.release(s)
+        names = {r["name"].split(" ")[0] for r in e.profile_report()}
+        e.profile(False)
+        assert ("fg_gemm_tc" in names) == (e is fast) and ("fg_gemm_generic" in names) == (e is slow)
+    want = plain_llama.plain_forward(cfg, W, toks).numpy()
+    scale = np.abs(want).max()
+    assert np.abs(got[1] - want).max() <= 1e-2 * scale and np.abs(got[0] - want).max() <= 1e-2 * scale
