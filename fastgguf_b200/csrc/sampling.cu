@@ -534,7 +534,7 @@ greedy_kernel(const float *__restrict__ logits, int V, int ldl, const int *__res
 
 // ---- sampling without top-k (top_k <= 0) over a large vocabulary, on NUC_BLOCKS blocks a row.
 // The candidates are everything above max - 20 * temp (fastgguf.c:4027-4034); top-p keeps the most probable of them
-// whose mass reaches top_p * total (:4039-4047), here as a threshold on the logit found in two rounds of 2,048 bins
+// whose mass reaches top_p * total (:4039-4047), here as a threshold on the logit found in two passes of 2,048 bins
 // each over the candidates' range (entries that fall into the same one of the 4 million bins are kept or dropped
 // together); the draw walks the kept entries in index order (the same law as the reference's walk in sorted
 // order, another token for the same draw).  Masses are integers, exp((v - max) / temp) * 2^40: integer sums do not
@@ -643,10 +643,10 @@ nucleus_max_kernel(const float *__restrict__ logits, int V, int ldl, unsigned lo
     }
 }
 
-// 2 and 3: masses of the candidates by bin (round 1: of the whole range; round 2: inside the bin where round 1 found
+// 2 and 3: masses of the candidates by bin (first pass: of the whole range; second pass: inside the bin where the first found
 // the threshold); the block that arrives last finds the bin of the threshold
 __global__ void __launch_bounds__(256)
-nucleus_hist_kernel(const float *__restrict__ logits, int V, int ldl, float temp, float top_p, int round,
+nucleus_hist_kernel(const float *__restrict__ logits, int V, int ldl, float temp, float top_p, int pass,
                     unsigned long long *__restrict__ scratch, int stride) {
     pdl_launch_dependents();
     pdl_wait();
@@ -654,7 +654,7 @@ nucleus_hist_kernel(const float *__restrict__ logits, int V, int ldl, float temp
     unsigned long long *st = scratch + (size_t)blockIdx.y * stride;
     const float *row = logits + (size_t)blockIdx.y * ldl;
     const NucleusRow r = nucleus_row(__ldcg(&st[NUC_MAX]), temp);
-    const int bin1 = round == 2 ? (int)__ldcg(&st[NUC_BIN1]) : 0;
+    const int bin1 = pass == 2 ? (int)__ldcg(&st[NUC_BIN1]) : 0;
     const int per = (V + NUC_BLOCKS - 1) / NUC_BLOCKS, i0 = blockIdx.x * per, i1 = min(V, i0 + per);
     for (int i = threadIdx.x; i < NUC_BINS; i += blockDim.x) s_hist[i] = 0ull;
     __syncthreads();
@@ -663,20 +663,20 @@ nucleus_hist_kernel(const float *__restrict__ logits, int V, int ldl, float temp
         const float v = row[i];
         if (!(v > r.cut)) continue;
         const unsigned long long m = nucleus_mass(r, v);
-        if (round == 1) { total += m; atomicAdd(&s_hist[nucleus_bin1(r, v)], m); }
+        if (pass == 1) { total += m; atomicAdd(&s_hist[nucleus_bin1(r, v)], m); }
         else if (nucleus_bin1(r, v) == bin1) atomicAdd(&s_hist[nucleus_bin2(r, v, bin1)], m);
     }
     __syncthreads();
     for (int i = threadIdx.x; i < NUC_BINS; i += blockDim.x)
         if (s_hist[i]) atomicAdd(&st[NUC_HIST + i], s_hist[i]);
-    if (round == 1) {
+    if (pass == 1) {
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
         if ((threadIdx.x & 31) == 0 && total) atomicAdd(&st[NUC_SUM], total);
     }
     if (!nucleus_last_block(st)) return;
     unsigned long long need;
-    if (round == 1) {
+    if (pass == 1) {
         const unsigned long long sum = __ldcg(&st[NUC_SUM]);
         need = (unsigned long long)((double)sum * (double)top_p);
         need = need < 1ull ? 1ull : (need > sum ? sum : need);
@@ -685,8 +685,8 @@ nucleus_hist_kernel(const float *__restrict__ logits, int V, int ldl, float temp
     nucleus_scan(st + NUC_HIST, need, &s_bin, &s_before);
     __syncthreads();
     if (threadIdx.x == 0) {
-        st[round == 1 ? NUC_BIN1 : NUC_BIN2] = s_bin;
-        st[NUC_NEED] = need - s_before;                 // what the next round has to find inside the bin
+        st[pass == 1 ? NUC_BIN1 : NUC_BIN2] = s_bin;
+        st[NUC_NEED] = need - s_before;                 // what the next pass has to find inside the bin
     }
 }
 
@@ -826,9 +826,9 @@ extern "C" int fg_sample(float *logits, int B, int V, int ldl, float temp, int t
             e = fg_launch(penalty_kernel, dim3(B), dim3(64), 0, stream, logits, V, ldl, repeat_penalty, repeat_last_n, seq_slot,
                           (const int *)hist, hist_cap, (const int *)hist_count, stop_ids, n_stop);
         if (!e) e = fg_launch(nucleus_max_kernel, dim3(NUC_BLOCKS, B), dim3(256), 0, stream, (const float *)logits, V, ldl, scratch, TOPK_CAND);
-        for (int round = 1; round <= 2 && with_top_p && !e; round++)
+        for (int pass = 1; pass <= 2 && with_top_p && !e; pass++)
             e = fg_launch(nucleus_hist_kernel, dim3(NUC_BLOCKS, B), dim3(256), 0, stream, (const float *)logits, V, ldl, temp, top_p,
-                          round, scratch, TOPK_CAND);
+                          pass, scratch, TOPK_CAND);
         if (!e) e = fg_launch(nucleus_mass_kernel, dim3(NUC_BLOCKS, B), dim3(256), 0, stream, (const float *)logits, V, ldl, temp,
                               with_top_p, seq_slot, rng, scratch, TOPK_CAND);
         if (!e) e = fg_launch(nucleus_walk_kernel, dim3(B), dim3(256), 0, stream, (const float *)logits, V, ldl, temp, with_top_p,
