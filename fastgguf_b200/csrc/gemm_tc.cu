@@ -1174,6 +1174,7 @@ static int dispatch(bool swap, int bn, const CUtensorMap &tmP, const CUtensorMap
     } else {
         switch (bn) {
         case -256: return launch_prefill_pair<256, EPI == EPI_ADD_F32 ? 5 : 6, EPI>(tmP, tmQ, a, st);      // (room for eight epilogue tiles)
+        case -192: if (EPI != EPI_SILU_MUL) return launch_prefill_pair<192, 6, EPI == EPI_SILU_MUL ? EPI_BF16 : EPI>(tmP, tmQ, a, st); break;
         case 128: return launch_prefill<128, 6, EPI>(tmP, tmQ, a, st);
         case 192: if (EPI != EPI_SILU_MUL) return launch_prefill<192, 5, EPI == EPI_SILU_MUL ? EPI_BF16 : EPI>(tmP, tmQ, a, st); break;
         case 256: return launch_prefill<256, 4, EPI>(tmP, tmQ, a, st);
@@ -1183,7 +1184,11 @@ static int dispatch(bool swap, int bn, const CUtensorMap &tmP, const CUtensorMap
 }
 
 // Upper bound of the tiles along N that the residual-add epilogue writes sums of squares for.
-extern "C" int fg_gemm_tc_max_ss_tiles(int N) { return (N + BM - 1) / BM; }
+extern "C" int fg_gemm_tc_max_ss_tiles(int N) {
+    // 128-wide tiles, or two partial sums for each 192-wide tile of a pair of CTAs
+    const int narrow = (N + BM - 1) / BM, halves = 2 * ((N + 191) / 192);
+    return narrow > halves ? narrow : halves;
+}
 
 // X: [M, K] bf16 (row stride ldx), W: [N, K] bf16 (row stride ldw); epi as the enum above.
 // ss_in (optional): X holds rows x * w of a deferred RMSNorm; ss_in[t * M + m], t < ss_tiles, are partial
@@ -1242,24 +1247,25 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
         static int pair_on = -1;
         if (pair_on < 0) { const char *e = getenv("FASTGGUF_PAIR"); pair_on = !(e && e[0] == '0'); }
         bool pair = false;
-        if (pair_on && bn == 256 && M > 128 && sms >= 2) {
-            const long long tp = (long long)((M + 255) / 256) * ((N + 255) / 256);
-            const long long rounds_pair = (tp + sms / 2 - 1) / (sms / 2), rounds_one = (t256 + sms - 1) / sms;
+        if (pair_on && bn >= 192 && M > 128 && sms >= 2) {
+            const long long tp = (long long)((M + 255) / 256) * ((N + bn - 1) / bn);
+            const long long rounds_pair = (tp + sms / 2 - 1) / (sms / 2), rounds_one = ((bn == 256 ? t256 : t192) + sms - 1) / sms;
             pair = rounds_pair <= rounds_one;
         }
-        if (force_splits == -2 && sms >= 2) pair = true;               // tests: the pair kernel at any size
-        if (pair) { bn = -256; grid = dim3((M + 255) / 256, (N + 255) / 256, 1); }
+        if (force_splits == -2 && sms >= 2) { pair = true; if (bn < 192) bn = 256; }      // tests: the pair kernel at any size
+        if (force_splits == -4 && sms >= 2 && epi != EPI_SILU_MUL) { pair = true; bn = 192; }      // tests: ... on 256 x 192 tiles
+        if (pair) { grid = dim3((M + 255) / 256, (N + bn - 1) / bn, 1); bn = -bn; }
     }
     int kb_per_split = (total_kb + splits - 1) / splits;       // a split may be empty: it adds zeros
     grid.z = splits;
     CUtensorMap tmP, tmQ;
     int e = swap ? make_map(&tmP, W, N, K, ldw, BM) : make_map(&tmP, X, M, K, ldx, BM);
     if (e) return e;
-    e = swap ? make_map(&tmQ, X, M, K, ldx, bn) : make_map(&tmQ, W, N, K, ldw, bn < 0 ? 128 : bn);
+    e = swap ? make_map(&tmQ, X, M, K, ldx, bn) : make_map(&tmQ, W, N, K, ldw, bn < 0 ? -bn / 2 : bn);
     if (e) return e;
     int esz = (epi == EPI_F32 || epi == EPI_ADD_F32) ? 4 : 2;
     int vec_ok = ((uintptr_t)out % 16 == 0) && ((size_t)ldc * esz % 16 == 0);
-    if (ss_tiles_out) *ss_tiles_out = (int)grid.y * (bn == -256 && epi == EPI_ADD_F32 ? 2 : 1);
+    if (ss_tiles_out) *ss_tiles_out = (int)grid.y * (bn < 0 && epi == EPI_ADD_F32 ? 2 : 1);
     GemmArgs a{out, M, N, K, ldc, kb_per_split, vec_ok, ss_in, ss_tiles, ss_size, ss_eps, norm_w, (bf16 *)xw_out, ss_out, epi, 0,
                g_test_skip_copy};
     switch (epi) {

@@ -141,25 +141,26 @@ def test_gemm_tc_prefill_tile_widths_and_started_norm(M, N, K):
     assert fast_gemm.pipeline_error() == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(512, 512, 256), (300, 384, 2048), (700, 1000, 520), (129, 256, 72), (2048, 2048, 512)])
-def test_gemm_tc_prefill_pair_of_ctas(M, N, K):
-    """The kernel that puts a pair of CTAs on a 256 x 256 tile (forced here; the engine picks it for large
-    shapes): whole and ragged tiles in every direction, every epilogue, the next norm started."""
+@pytest.mark.parametrize("width", [-2, -4])
+@pytest.mark.parametrize("M,N,K", [(512, 512, 256), (300, 384, 2048), (700, 1000, 520), (129, 256, 72), (2048, 2048, 512), (513, 3072, 264)])
+def test_gemm_tc_prefill_pair_of_ctas(M, N, K, width):
+    """The kernel that puts a pair of CTAs on a 256 x 256 tile (width -2) or a 256 x 192 tile (-4) (forced here; the
+    engine picks it for large shapes): whole and ragged tiles in every direction, every epilogue, the next norm started."""
     from fastgguf_b200.ops import fast_gemm
     a, w = _operands(M, N, K, torch.bfloat16, 8)
     want = a.double() @ w.double().T
-    _check(fast_gemm.gemm_tc(a, w, out_dtype=torch.float32, force_splits=-2), a, w, want, False)
-    _check(fast_gemm.gemm_tc(a, w, force_splits=-2), a, w, want, True)
+    _check(fast_gemm.gemm_tc(a, w, out_dtype=torch.float32, force_splits=width), a, w, want, False)
+    _check(fast_gemm.gemm_tc(a, w, force_splits=width), a, w, want, True)
     res = torch.randn(M, N, device="cuda")
     nw = (1 + 0.1 * torch.randn(N, device="cuda")).float()
     acc = res.clone()
-    out, started = fast_gemm.gemm_tc(a, w, out=acc, accumulate=True, emit_norm_weight=nw, emit_eps=1e-5, force_splits=-2)
+    out, started = fast_gemm.gemm_tc(a, w, out=acc, accumulate=True, emit_norm_weight=nw, emit_eps=1e-5, force_splits=width)
     x = want + res.double()
     _check(acc, a, w, x, False)
     assert (started.xw.double() - x * nw.double()).abs().max().item() <= 2 ** -7 * (x * nw.double()).abs().max().item()
     ss = started.ss[:started.tiles].double().sum(0)
     assert ((ss - (x * x).sum(1)).abs() / (x * x).sum(1)).max().item() < 1e-4
-    if N % 128 == 0:
+    if N % 128 == 0 and width == -2:
         F = N // 2
         gate, up = w[:F], w[F:]
         got = fast_gemm.gemm_tc(a, fast_gemm.interleave_gate_up(gate, up), silu=True, force_splits=-2)
