@@ -122,6 +122,8 @@ def test_attention_prefill(H, KV, hd, window):
                                             (4, 4, 64, 100), (4, 2, 64, 64), (4, 2, 64, 128), (8, 2, 64, 65),
                                             (6, 2, 128, 128), (3, 1, 128, 65)])
 def test_attention_prefill_tcgen05(H, KV, hd, window):
+    """(Both variants of the kernel - one and two score tiles - run at both head sizes when the suite is also run with
+    FASTGGUF_ATTN_PIPE=0 and =3; by default head size 64 takes one tile, 128 two.)"""
     from fastgguf_b200.ops import fast_attention
     new = [200, 1, 67, 5, 300]
     case = make_case([0, 300, 60, 0, 129], new, H, KV, hd, torch.bfloat16, 14)
@@ -130,6 +132,21 @@ def test_attention_prefill_tcgen05(H, KV, hd, window):
                                               case["k_pool"], case["v_pool"], len(new), max(new), H, KV, hd, scale, window)
     assert fast_attention.prefill_tc_error() == 0
     assert _err(got, plain(case, H, KV, hd, scale, window)) < 1.5e-2
+
+
+@pytest.mark.parametrize("H,KV,hd", [(6, 2, 128), (8, 2, 64)])
+def test_attention_prefill_tcgen05_batch_of_long_unequal_prompts(H, KV, hd):
+    """Prompts of 64 to 2,048 tokens in one step: tiles of 1 to 32 iterations side by side, rows that finish long
+    after the last MMA of their tile and rows that finish before it (every wait on a barrier has to name the right
+    phase at either end)."""
+    from fastgguf_b200.ops import fast_attention
+    new = [1500, 64, 700, 2048, 300, 129]
+    case = make_case([0, 0, 64, 0, 1000, 0], new, H, KV, hd, torch.bfloat16, 31)
+    scale = 1.0 / math.sqrt(hd)
+    got = fast_attention.attention_prefill_tc(case["q"], case["cu_rows"], case["seq_start"], case["table"],
+                                              case["k_pool"], case["v_pool"], len(new), max(new), H, KV, hd, scale, 0)
+    assert fast_attention.prefill_tc_error() == 0
+    assert _err(got, plain(case, H, KV, hd, scale, 0)) < 1.5e-2
 
 
 @pytest.mark.parametrize("n_splits", [None, 1, 4, 8])
