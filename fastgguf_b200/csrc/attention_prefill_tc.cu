@@ -27,6 +27,7 @@
 //
 // Every mbarrier wait is bounded (error flag, tensor memory freed, copies in flight awaited).
 #include <cuda.h>
+#include <climits>
 #include "common.cuh"
 
 #define FG_ERR_PIPELINE 10003
@@ -138,6 +139,27 @@ __device__ __forceinline__ uint32_t make_idesc(int M, int N, int b_mn_major) {
            ((uint32_t)(M >> 4) << 24);
 }
 __device__ __forceinline__ void raise_error(int role) { atomicCAS(&g_attn_error, 0, (FG_ERR_PIPELINE << 8) | role); }
+
+// One 32-key chunk of a row's scores: p = 2^(v * scale - base) as bf16 pairs into w, their sum added to `acc`, the
+// largest raw score kept in `mx_raw` (the scale is positive, so the largest scaled score is mx_raw * scale).
+// MASKED: keys outside [lo, hi] count as -infinity.
+template <bool MASKED>
+__device__ __forceinline__ void softmax_chunk(const float (&v)[32], int key, int lo, int hi, float scale, float neg_base,
+                                              float &mx_raw, float &acc, uint32_t (&w)[16]) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+        float a = v[i], b = v[i + 1];
+        if (MASKED) {
+            if (key + i < lo || key + i > hi) a = -INFINITY;
+            if (key + i + 1 < lo || key + i + 1 > hi) b = -INFINITY;
+        }
+        mx_raw = fmaxf(mx_raw, fmaxf(a, b));
+        const float p0 = ex2(fmaf(a, scale, neg_base)), p1 = ex2(fmaf(b, scale, neg_base));
+        acc += p0 + p1;
+        __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
+        w[i >> 1] = *(uint32_t *)&t;
+    }
+}
 
 // PIPE: 64 keys an iteration with TWO score tiles in tensor memory and two P tiles in shared memory, so that S of
 // iteration j + 1 is computed while the softmax of iteration j runs and P V of iteration j while the softmax of j + 1
@@ -320,70 +342,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             // whose new scores exceed that makes its warp redo the tile in two passes with the true maximum.
             float corr = 1.f, sum = 0.f;
             bool redo = !__all_sync(0xffffffffu, m != -INFINITY);
-            if (!redo) {
-                float mx = -INFINITY;
+            // a warp whose 32 rows all see every key of this tile runs the loops without the mask's compares
+            const bool any_masked = __any_sync(0xffffffffu, masked);
+            // probabilities of the tile relative to `base`, written to the P tile; the largest RAW score in mx
+            auto pass = [&](float base, float &mx_raw, float &acc) {
+                const float neg_base = -base;
 #pragma unroll 1
                 for (int c = 0; c < KEYS / 32; c++) {
                     float v[32];
                     tc_ld32(srow + c * 32, v);
                     uint32_t w[16];
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float x0 = v[i] * scale_log2, x1 = v[i + 1] * scale_log2;
-                        int key = key0 + c * 32 + i;
-                        if (masked && (key < lo || key > hi)) x0 = -INFINITY;
-                        if (masked && (key + 1 < lo || key + 1 > hi)) x1 = -INFINITY;
-                        mx = fmaxf(mx, fmaxf(x0, x1));
-                        float p0 = ex2(x0 - m), p1 = ex2(x1 - m);
-                        sum += p0 + p1;
-                        __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
-                        w[i >> 1] = *(uint32_t *)&t;
-                    }
-#pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        int cc = (c & 1) * 4 + k;
-                        uint32_t dst = pj + (c >> 1) * (ROWS * 128) + r * 128 + ((cc ^ (r & 7)) << 4);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                                     ::"r"(dst), "r"(w[4 * k]), "r"(w[4 * k + 1]), "r"(w[4 * k + 2]), "r"(w[4 * k + 3]) : "memory");
-                    }
-                }
-                redo = __any_sync(0xffffffffu, mx > m + 8.0f);
-            }
-            float m_keep = m;
-            if (redo) {
-                float mx = -INFINITY;
-#pragma unroll 1
-                for (int c = 0; c < KEYS / 32; c++) {
-                    float v[32];
-                    tc_ld32(srow + c * 32, v);
-#pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        int key = key0 + c * 32 + i;
-                        float x = v[i] * scale_log2;
-                        if (masked && (key < lo || key > hi)) x = -INFINITY;
-                        mx = fmaxf(mx, x);
-                    }
-                }
-                const float m_new = fmaxf(m, mx);
-                corr = m == -INFINITY ? 1.f : ex2(m - m_new);                 // m_new >= m; nothing seen yet: keep zeros
-                const float base = m_new == -INFINITY ? 0.f : m_new;
-                sum = 0.f;
-#pragma unroll 1
-                for (int c = 0; c < KEYS / 32; c++) {
-                    float v[32];
-                    tc_ld32(srow + c * 32, v);
-                    uint32_t w[16];
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float x0 = v[i] * scale_log2, x1 = v[i + 1] * scale_log2;
-                        int key = key0 + c * 32 + i;
-                        if (masked && (key < lo || key > hi)) x0 = -INFINITY;
-                        if (masked && (key + 1 < lo || key + 1 > hi)) x1 = -INFINITY;
-                        float p0 = ex2(x0 - base), p1 = ex2(x1 - base);
-                        sum += p0 + p1;
-                        __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
-                        w[i >> 1] = *(uint32_t *)&t;
-                    }
+                    if (any_masked) softmax_chunk<true>(v, key0 + c * 32, masked ? lo : INT_MIN, masked ? hi : INT_MAX, scale_log2, neg_base, mx_raw, acc, w);
+                    else softmax_chunk<false>(v, 0, 0, 0, scale_log2, neg_base, mx_raw, acc, w);
                     // 32 keys = four 16-byte chunks of this row, in the 64-key chunk c / 2
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
@@ -393,6 +363,33 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                                      ::"r"(dst), "r"(w[4 * k]), "r"(w[4 * k + 1]), "r"(w[4 * k + 2]), "r"(w[4 * k + 3]) : "memory");
                     }
                 }
+            };
+            if (!redo) {
+                float mx_raw = -INFINITY;
+                pass(m, mx_raw, sum);
+                redo = __any_sync(0xffffffffu, mx_raw * scale_log2 > m + 8.0f);
+            }
+            float m_keep = m;
+            if (redo) {
+                float mx_raw = -INFINITY;
+#pragma unroll 1
+                for (int c = 0; c < KEYS / 32; c++) {
+                    float v[32];
+                    tc_ld32(srow + c * 32, v);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        int key = key0 + c * 32 + i;
+                        float x = v[i];
+                        if (masked && (key < lo || key > hi)) x = -INFINITY;
+                        mx_raw = fmaxf(mx_raw, x);
+                    }
+                }
+                const float m_new = fmaxf(m, mx_raw * scale_log2);            // the scale is positive
+                corr = m == -INFINITY ? 1.f : ex2(m - m_new);                 // m_new >= m; nothing seen yet: keep zeros
+                const float base = m_new == -INFINITY ? 0.f : m_new;
+                sum = 0.f;
+                float unused = -INFINITY;
+                pass(base, unused, sum);
                 m_keep = m_new;
             }
             l = l * corr + sum;
