@@ -225,8 +225,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         const int r = (warp & 3) * 32 + lane;
         t_row = r / Gc; g_row = g0 + r % Gc;
         valid = t_row < tq && g_row < G;
-        hi = valid ? start + q0 + t_row : -1;
-        lo = (window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0;
+        // A row past the tile's tokens or heads has a zero query and is never stored.  It sees every key, so that it
+        // neither asks for the masked loop nor, with a maximum that stays at minus infinity, for the second pass in
+        // every iteration of its warp (group sizes that do not divide 128 leave such rows in every tile).
+        hi = valid ? start + q0 + t_row : INT_MAX;
+        lo = !valid ? INT_MIN : (window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0;
         const bf16 *src = q + (size_t)(row0 + q0 + t_row) * ldq + (size_t)(kvh * G + g_row) * HD;
 #pragma unroll
         for (int c = 0; c < HD / 8; c++) {
