@@ -43,6 +43,7 @@ __device__ int g_attn_error = 0;
 // how long a wait may last, in SM cycles; a variable so that a test can shorten it (fg_attention_prefill_tc_test_hook)
 __device__ long long g_attn_wait_limit = WAIT_LIMIT_CYCLES;
 static int g_test_skip_copy = 0;
+static int g_variant = -2;             // -2: not read yet; -1: chosen by shape; else bit 0 / bit 1 = two score tiles at head size 64 / 128
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -520,16 +521,19 @@ extern "C" int fg_attention_prefill_tc(const void *q, int ldq, void *out, int ld
     e = pool_map(&tmV, v_pool, rows, hd);
     if (e) return e;
     // The variant with two score tiles: at head size 128 it takes a fifth off the kernel (3B shapes, 2,048 tokens: 81 ->
-    // 62 us a layer); at head size 64, where the other variant already walks 128 keys an iteration, it is 3 % slower.
-    // FASTGGUF_ATTN_PIPE overrides (bit 0: head size 64, bit 1: head size 128); the tests run both variants at both sizes.
-    static int pipe = -1;
-    if (pipe < 0) { const char *e = getenv("FASTGGUF_ATTN_PIPE"); pipe = e ? atoi(e) : 2; }
-    if (hd == 64) {
-        if (pipe & 1) return launch_tc<64, true>(tmK, tmV, q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, n_seq, max_new, H, KV, scale, window, stream);
-        return launch_tc<64, false>(tmK, tmV, q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, n_seq, max_new, H, KV, scale, window, stream);
-    }
-    if (pipe & 2) return launch_tc<128, true>(tmK, tmV, q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, n_seq, max_new, H, KV, scale, window, stream);
-    return launch_tc<128, false>(tmK, tmV, q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, n_seq, max_new, H, KV, scale, window, stream);
+    // 62 us a layer).  At head size 64, where the other variant already walks 128 keys an iteration, it is slower on one
+    // prompt of 2,048 tokens (55 against 45 us: the heaviest tile's chain of iterations bounds the kernel) and faster
+    // where many tiles share the GPU: 4,096 tokens 126 against 133 us, 32,768 tokens 6.54 against 6.77 ms, eight prompts
+    // of 2,048 tokens 270 against 315 us - so it runs from 4,096 rows of new tokens on.  FASTGGUF_ATTN_PIPE or
+    // fg_attention_prefill_tc_variant override (bit 0: head size 64, bit 1: head size 128; negative: this rule).
+    if (g_variant == -2) { const char *e = getenv("FASTGGUF_ATTN_PIPE"); g_variant = e ? atoi(e) : -1; }
+    const bool pipe = g_variant >= 0 ? ((g_variant >> (hd == 64 ? 0 : 1)) & 1) != 0
+                                     : hd == 128 || (long long)n_seq * max_new >= 4096;
+#define TC_RUN(HD, PIPE) launch_tc<HD, PIPE>(tmK, tmV, q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, n_seq, \
+                                             max_new, H, KV, scale, window, stream)
+    if (hd == 64) return pipe ? TC_RUN(64, true) : TC_RUN(64, false);
+    return pipe ? TC_RUN(128, true) : TC_RUN(128, false);
+#undef TC_RUN
 }
 
 // For the test of the bounded waits: wait_limit_cycles > 0 sets how long a wait may last (0 restores the default of
@@ -540,6 +544,12 @@ extern "C" int fg_attention_prefill_tc_test_hook(long long wait_limit_cycles, in
     long long v = wait_limit_cycles > 0 ? wait_limit_cycles : WAIT_LIMIT_CYCLES;
     g_test_skip_copy = skip_copy ? 1 : 0;
     return (int)cudaMemcpyToSymbol(g_attn_wait_limit, &v, sizeof v);
+}
+
+// Which variant runs: see fg_attention_prefill_tc.  Negative: chosen by head size and step shape (the default).
+extern "C" int fg_attention_prefill_tc_variant(int bits) {
+    g_variant = bits < 0 ? -1 : (bits & 3);
+    return 0;
 }
 
 extern "C" int fg_attention_prefill_tc_error(void) {

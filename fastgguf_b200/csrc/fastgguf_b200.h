@@ -69,6 +69,7 @@ int fg_attention_prefill_tc(const void *q, int ldq, void *out, int ldo, const in
                             int n_pages, int n_seq, int max_new, int H, int KV, int hd, int page_size, float scale,
                             int window, cudaStream_t stream);
 int fg_attention_prefill_tc_error(void);
+int fg_attention_prefill_tc_variant(int bits);   /* bit 0 / 1: two score tiles at head size 64 / 128; negative: by shape */
 int fg_attention_prefill_tc_test_hook(long long wait_limit_cycles, int skip_copy);   /* tests only */
 /* fg_attention_decode_noalloc: see fastgguf_noalloc.h */
 

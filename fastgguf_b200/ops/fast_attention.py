@@ -20,6 +20,7 @@ register_signatures("attn", {
     "fg_attention_prefill_tc": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "fg_attention_prefill_tc_error": [],
+    "fg_attention_prefill_tc_variant": [c_int],
     "fg_attention_prefill": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
 })
@@ -105,6 +106,12 @@ def attention_prefill_tc(q, cu_rows, seq_start, block_table, k_pool, v_pool, n_s
                                               k_pool.shape[2], float(scale), int(window), stream()),
           "attention_prefill_tc")
     return out
+
+
+def prefill_tc_variant(bits: int) -> None:
+    """Which form of the tcgen05 prefill attention runs: bit 0 / bit 1 = two score tiles in tensor memory at head
+    size 64 / 128; negative = chosen by head size and step shape (the default)."""
+    check(lib("attn").fg_attention_prefill_tc_variant(int(bits)), "attention_prefill_tc_variant")
 
 
 def prefill_tc_error() -> int:

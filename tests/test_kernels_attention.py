@@ -12,6 +12,15 @@ pytestmark = pytest.mark.gpu
 PAGE = 64
 
 
+@pytest.fixture(params=[0, 3], ids=["one-score-tile", "two-score-tiles"])
+def tc_variant(request):
+    """Both forms of the tcgen05 prefill kernel at both head sizes, whatever the step's shape would choose."""
+    from fastgguf_b200.ops import fast_attention
+    fast_attention.prefill_tc_variant(request.param)
+    yield request.param
+    fast_attention.prefill_tc_variant(-1)
+
+
 def make_case(lens_before, new, H, KV, hd, dtype, seed, boost=True, ramp=0.0):
     """Sequences with `lens_before[i]` cached tokens that bring `new[i]` more.  Returns everything
     the kernels need plus dense per-sequence K, V (float64) for the plain computation."""
@@ -121,9 +130,7 @@ def test_attention_prefill(H, KV, hd, window):
 @pytest.mark.parametrize("H,KV,hd,window", [(8, 2, 64, 0), (3, 1, 128, 0), (24, 8, 128, 0), (20, 1, 64, 0),
                                             (4, 4, 64, 100), (4, 2, 64, 64), (4, 2, 64, 128), (8, 2, 64, 65),
                                             (6, 2, 128, 128), (3, 1, 128, 65)])
-def test_attention_prefill_tcgen05(H, KV, hd, window):
-    """(Both variants of the kernel - one and two score tiles - run at both head sizes when the suite is also run with
-    FASTGGUF_ATTN_PIPE=0 and =3; by default head size 64 takes one tile, 128 two.)"""
+def test_attention_prefill_tcgen05(H, KV, hd, window, tc_variant):
     from fastgguf_b200.ops import fast_attention
     new = [200, 1, 67, 5, 300]
     case = make_case([0, 300, 60, 0, 129], new, H, KV, hd, torch.bfloat16, 14)
@@ -135,7 +142,7 @@ def test_attention_prefill_tcgen05(H, KV, hd, window):
 
 
 @pytest.mark.parametrize("H,KV,hd", [(6, 2, 128), (8, 2, 64)])
-def test_attention_prefill_tcgen05_batch_of_long_unequal_prompts(H, KV, hd):
+def test_attention_prefill_tcgen05_batch_of_long_unequal_prompts(H, KV, hd, tc_variant):
     """Prompts of 64 to 2,048 tokens in one step: tiles of 1 to 32 iterations side by side, rows that finish long
     after the last MMA of their tile and rows that finish before it (every wait on a barrier has to name the right
     phase at either end)."""
