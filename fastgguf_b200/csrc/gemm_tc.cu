@@ -698,20 +698,14 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             for (int cl = w; cl < per; cl += EW) {
                 const int m = q0 + c_begin + cl;
                 if (m >= a.M) break;                                               // tokens fill the columns from 0
-                float v[4];
+                // a short rolled loop over the ranks, the four features' loads in flight together
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
+                const float *pc = split ? part + ((((cl >> vw_log) * BM + lane) << vw_log) + (cl & ((1 << vw_log) - 1))) : part + cl * BM + lane;
+                const int zstride = split ? ((per >> vw_log) * BM) << vw_log : 0, istride = split ? 32 << vw_log : 32;
+#pragma unroll 1
+                for (int z = 0; z < S; z++, pc += zstride) {                       // rank order
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    float pz[8];
-#pragma unroll
-                    for (int z = 0; z < 8; z++) {
-                        const int row = lane + 32 * i;
-                        const int at = split ? ((((z * (per >> vw_log) + (cl >> vw_log)) * BM + row) << vw_log) + (cl & ((1 << vw_log) - 1)))
-                                             : cl * BM + row;
-                        pz[z] = z < S ? part[at] : 0.f;
-                    }
-                    v[i] = 0.f;
-#pragma unroll
-                    for (int z = 0; z < 8; z++) v[i] += pz[z];                     // rank order; absent ranks add 0
+                    for (int i = 0; i < 4; i++) v[i] += pc[i * istride];
                 }
                 const float iv = inv_s[c_begin + cl];
                 if (epi == EPI_SILU_MUL) {
