@@ -47,6 +47,13 @@ int fg_argmax(const float *logits, int B, int V, int ldl, int *out, cudaStream_t
 int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *out, int ldc, int epi, int M, int N, int K,
                int force_splits, const float *ss_in, int ss_tiles, int ss_size, float ss_eps, const float *norm_w,
                void *xw_out, float *ss_out, int *ss_tiles_out /* host */, cudaStream_t stream);
+/* the same with device memory the call may use: with fg_gemm_tc_workspace_bytes(M, N, K, epi) of it (0: none needed) a
+   prefill contraction of few output tiles is split along K over all SMs and summed, in order, by a second kernel */
+int fg_gemm_tc_ws(const void *X, int ldx, const void *W, int ldw, void *out, int ldc, int epi, int M, int N, int K,
+                  int force_splits, const float *ss_in, int ss_tiles, int ss_size, float ss_eps, const float *norm_w,
+                  void *xw_out, float *ss_out, int *ss_tiles_out /* host */, void *workspace, long long workspace_bytes,
+                  cudaStream_t stream);
+long long fg_gemm_tc_workspace_bytes(int M, int N, int K, int epi);
 int fg_gemm_tc_max_ss_tiles(int N);
 int fg_gemm_tc_error(void);
 /* tests only: shorten the bounded waits and make the decode kernel's pipeline stall, see gemm_tc.cu */

@@ -202,6 +202,7 @@ struct GemmArgs {
     float *ss_out;        // [tiles, M]
     int epi, stages;      // decode kernel: epilogue and ring depth are run-time values
     int test_skip_copy;   // tests only: the decode kernel's producer omits the activation copy of its first stage
+    int splits;           // prefill kernel: > 1 = partial products of `kb_per_split` K-blocks each into out[split][M][ldc]
 };
 
 __device__ __forceinline__ float inv_rms(const GemmArgs &a, int m) {
@@ -213,7 +214,8 @@ __device__ __forceinline__ float inv_rms(const GemmArgs &a, int m) {
 // Epilogue of a token-major tile: thread = token row p0 + prow, columns = weight rows q0 .. q0 + BN.
 // `qt` is the index of the tile along the features (row of ss_out it writes).
 template <int BN, int EPI>
-__device__ __forceinline__ void epilogue_token_major(const GemmArgs &a, uint32_t trow, int p0, int q0, int qt, int prow) {
+__device__ __forceinline__ void epilogue_token_major(const GemmArgs &a, uint32_t trow, int p0, int q0, int qt, int prow,
+                                                     size_t out_row0 = 0) {
     // thread = token row, columns = weight rows (features): runs of 16 consecutive outputs
     const int m = p0 + prow;
     const bool m_ok = m < a.M;
@@ -254,7 +256,7 @@ __device__ __forceinline__ void epilogue_token_major(const GemmArgs &a, uint32_t
             if (!m_ok || n0 >= a.N) continue;
 #pragma unroll
             for (int j = 0; j < 16; j++) v[j] *= iv;
-            const size_t idx = (size_t)m * a.ldc + n0;
+            const size_t idx = (out_row0 + (size_t)m) * a.ldc + n0;       // (out_row0: the split's block of a partial product)
             const bool full = a.vec_ok && n0 + 16 <= a.N;
             if (EPI == EPI_BF16) {
                 bf16 *dst = (bf16 *)a.out + idx;
@@ -771,6 +773,13 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_con
 
     const int warp = warp_index(), lane = threadIdx.x & 31;
     const int nkb = (a.K + BK - 1) / BK;
+    // Split along K (a.splits > 1, plain f32 epilogue only): the tile index also counts the split, slowest, and split z
+    // writes the product over its K-blocks into block z of the output; gemm_splitk_finish_kernel adds the blocks.
+    const int per_split = a.splits > 1 ? n_tiles / a.splits : n_tiles;
+    auto kb_range = [&](int tile, int &kb_begin, int &kb_end) {
+        if (a.splits > 1) { kb_begin = (tile / per_split) * a.kb_per_split; kb_end = min(nkb, kb_begin + a.kb_per_split); }
+        else { kb_begin = 0; kb_end = nkb; }
+    };
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
     const uint32_t tfull0 = smem_u32(&bars[2 * STAGES]), tempty0 = smem_u32(&bars[2 * STAGES + 2]);
     const uint32_t smem0 = smem_u32(smem);
@@ -802,8 +811,10 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_con
         int s = 0, ph = 0, issued = 0;                 // ring position, pass over the ring (parity), stages filled so far
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-            const int p0 = (tile % n_pt) * BM, q0 = (tile / n_pt) * BN;
-            for (int kb = 0; kb < nkb; kb++) {
+            const int t2 = tile % per_split, p0 = (t2 % n_pt) * BM, q0 = (t2 / n_pt) * BN;
+            int kb_begin, kb_end;
+            kb_range(tile, kb_begin, kb_end);
+            for (int kb = kb_begin; kb < kb_end; kb++) {
                 ok = __all_sync(0xffffffffu, mbar_wait(empty0 + 8 * s, ph ^ 1));
                 if (!ok) { raise_error(1); break; }
                 if (elect_one()) {
@@ -831,7 +842,9 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_con
             // the epilogue must have emptied this accumulator (its use before the last one)
             if (!__all_sync(0xffffffffu, mbar_wait(tempty0 + 8 * acc, ((i >> 1) & 1) ^ 1))) { raise_error(4); break; }
             tc_fence_after();
-            for (int kb = 0; kb < nkb; kb++) {
+            int kb_begin, kb_end;
+            kb_range(tile, kb_begin, kb_end);
+            for (int kb = kb_begin; kb < kb_end; kb++) {
                 ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, ph));
                 if (!ok) { raise_error(2); break; }
                 tc_fence_after();
@@ -841,7 +854,7 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_con
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; k++) {
                         const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
-                        tc_mma_bf16(tmem_base + acc * BN, pdesc + koff, qdesc + koff, idesc, (kb | k) != 0);
+                        tc_mma_bf16(tmem_base + acc * BN, pdesc + koff, qdesc + koff, idesc, ((kb - kb_begin) | k) != 0);
                     }
                     tc_commit(empty0 + 8 * s);
                 }
@@ -858,14 +871,14 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_con
         int i = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, i++) {
             const int acc = i & 1;
-            const int pt = tile % n_pt, qt = tile / n_pt;
+            const int t2 = tile % per_split, pt = t2 % n_pt, qt = t2 / n_pt;
             if (!mbar_wait(tfull0 + 8 * acc, (i >> 1) & 1)) { raise_error(3); break; }
             tc_fence_after();
             const uint32_t trow = tmem_base + ((uint32_t)(lg * 32) << 16) + acc * BN;
             if (EPI == EPI_ADD_F32 && a.vec_ok && (a.N & 31) == 0)
                 epilogue_add_coalesced<BN>(a, trow, pt * BM, qt * BN, qt, lg, lane, smem + STAGES * STAGE_BYTES + lg * EPI_STAGE_BYTES);
             else
-                epilogue_token_major<BN, EPI>(a, trow, pt * BM, qt * BN, qt, prow);
+                epilogue_token_major<BN, EPI>(a, trow, pt * BM, qt * BN, qt, prow, (size_t)(tile / per_split) * (size_t)a.M);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tempty0 + 8 * acc) : "memory");
@@ -875,6 +888,71 @@ gemm_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_con
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// Second half of a prefill contraction split along K: out = epilogue(sum over the splits of ws[split][M][N]), the
+// splits added in their order.  A warp takes one token row and 128 features (lane + 32 i), so that the sum of squares
+// of the started norm is one warp reduction; ss_out is indexed by 128-feature tile like the decode kernel's.
+template <int EPI>
+__global__ void __launch_bounds__(256)
+gemm_splitk_finish_kernel(GemmArgs a, const float *__restrict__ ws, int S) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, m = blockIdx.y * 8 + (threadIdx.x >> 5), qt = blockIdx.x, q0 = qt * 128;
+    if (m >= a.M) return;
+    // everything this warp reads is asked for at once: the partial sums of squares of the row (a lane each), the
+    // residual values and norm weights of its features, then the partial products
+    float ss_mine[2] = {0.f, 0.f};
+    if (a.ss_in) {
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+            if (lane + 32 * h < a.ss_tiles) ss_mine[h] = __ldcg(a.ss_in + (size_t)(lane + 32 * h) * a.M + m);
+    }
+    float res[4] = {0.f, 0.f, 0.f, 0.f}, nw[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int n = q0 + lane + 32 * i;
+        if (n >= a.N) continue;
+        if (EPI == EPI_ADD_F32) res[i] = ((const float *)a.out)[(size_t)m * a.ldc + n];
+        if (EPI == EPI_ADD_F32 && a.norm_w) nw[i] = a.norm_w[n];
+    }
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    const float *p = ws + (size_t)m * a.N + q0 + lane;
+    const size_t zstride = (size_t)a.M * a.N;
+#pragma unroll 1
+    for (int z = 0; z < S; z++, p += zstride) {
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            if (q0 + lane + 32 * i < a.N) v[i] += __ldcg(p + 32 * i);
+    }
+    float iv = 1.0f;
+    if (a.ss_in) {
+        // the sum in tile order, as inv_rms adds it (up to 64 tiles; more fall back to its loop)
+        if (a.ss_tiles <= 64) {
+            float s = 0.f;
+            for (int t = 0; t < a.ss_tiles; t++) s += __shfl_sync(0xffffffffu, t < 32 ? ss_mine[0] : ss_mine[1], t & 31);
+            iv = 1.0f / sqrtf(s / (float)a.ss_size + a.ss_eps);
+        } else iv = inv_rms(a, m);
+    }
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int n = q0 + lane + 32 * i;
+        if (n >= a.N) continue;
+        const size_t idx = (size_t)m * a.ldc + n;
+        float x = v[i] * iv;
+        if (EPI == EPI_BF16) { ((bf16 *)a.out)[idx] = __float2bfloat16_rn(x); continue; }
+        if (EPI == EPI_ADD_F32) x += res[i];
+        ((float *)a.out)[idx] = x;
+        if (EPI == EPI_ADD_F32 && a.norm_w) {
+            a.xw_out[(size_t)m * a.N + n] = __float2bfloat16_rn(x * nw[i]);
+            sq += x * x;
+        }
+    }
+    if (EPI == EPI_ADD_F32 && a.norm_w) {
+        sq = warp_sum(sq);
+        if (lane == 0) a.ss_out[(size_t)qt * a.M + m] = sq;
     }
 }
 
@@ -1118,7 +1196,7 @@ static int launch_prefill(const CUtensorMap &tmP, const CUtensorMap &tmQ, const 
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
     }
-    int n_pt = (a.M + BM - 1) / BM, n_tiles = n_pt * ((a.N + BN - 1) / BN);
+    int n_pt = (a.M + BM - 1) / BM, n_tiles = n_pt * ((a.N + BN - 1) / BN) * (a.splits > 1 ? a.splits : 1);
     dim3 grid(n_tiles < n_sm ? n_tiles : n_sm);
     return fg_launch(gemm_tc_prefill_kernel<BN, STAGES, EPI>, grid, dim3(GEMM_THREADS), (size_t)smem, stream, tmP, tmQ, a,
                      n_pt, n_tiles);
@@ -1203,10 +1281,51 @@ static int sm_count() {
     return n;
 }
 
+// How a prefill contraction with few output tiles is split along K: 128 x 128 tiles, as many splits as bring the CTAs
+// towards one an SM, each at least 8 K-blocks long.  0: no split (the decode kernel's range, enough tiles, short K).
+static int prefill_splits(int M, int N, int K, int epi, int *kb_per_split) {
+    if (M <= 128 || epi == EPI_SILU_MUL) return 0;
+    const int total_kb = (K + BK - 1) / BK, sms = sm_count();
+    const long long tiles = (long long)((M + BM - 1) / BM) * ((N + 127) / 128);
+    if (tiles * 2 > sms || total_kb < 16) return 0;
+    int S = (int)(sms / tiles);
+    if (S > 8) S = 8;
+    if (S > total_kb / 8) S = total_kb / 8;
+    // what the split saves (K-blocks off each CTA's walk) against what the second kernel costs (about 5 us, 20 K-blocks)
+    if (S < 2 || (long long)total_kb * (S - 1) < 24ll * S) return 0;
+    const int kbs = (total_kb + S - 1) / S;
+    *kb_per_split = kbs;
+    return (total_kb + kbs - 1) / kbs;             // no empty split
+}
+
+// Bytes of workspace with which fg_gemm_tc_ws splits this contraction along K (0: it does not split it).
+extern "C" long long fg_gemm_tc_workspace_bytes(int M, int N, int K, int epi) {
+    int kbs = 0;
+    const int S = prefill_splits(M, N, K, epi, &kbs);
+    return S ? (long long)S * M * N * 4 : 0;
+}
+
+extern "C" int fg_gemm_tc_ws(const void *X, int ldx, const void *W, int ldw, void *out, int ldc, int epi,
+                             int M, int N, int K, int force_splits, const float *ss_in, int ss_tiles, int ss_size,
+                             float ss_eps, const float *norm_w, void *xw_out, float *ss_out, int *ss_tiles_out,
+                             void *workspace, long long workspace_bytes, cudaStream_t stream);
+
 extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *out, int ldc, int epi,
                           int M, int N, int K, int force_splits, const float *ss_in, int ss_tiles, int ss_size,
                           float ss_eps, const float *norm_w, void *xw_out, float *ss_out, int *ss_tiles_out,
                           cudaStream_t stream) {
+    return fg_gemm_tc_ws(X, ldx, W, ldw, out, ldc, epi, M, N, K, force_splits, ss_in, ss_tiles, ss_size, ss_eps, norm_w, xw_out,
+                         ss_out, ss_tiles_out, nullptr, 0, stream);
+}
+
+// As fg_gemm_tc, with `workspace_bytes` of 16-byte aligned device memory that the call may use (and the kernels it
+// launches, until they have run): with at least fg_gemm_tc_workspace_bytes(M, N, K, epi) of it, a prefill contraction
+// of few output tiles (o and down at a few hundred rows: 32 CTAs walking all of K) runs as partial products over
+// slices of K on all SMs and a second kernel that adds them in order and applies the epilogue.
+extern "C" int fg_gemm_tc_ws(const void *X, int ldx, const void *W, int ldw, void *out, int ldc, int epi,
+                             int M, int N, int K, int force_splits, const float *ss_in, int ss_tiles, int ss_size,
+                             float ss_eps, const float *norm_w, void *xw_out, float *ss_out, int *ss_tiles_out,
+                             void *workspace, long long workspace_bytes, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return FG_ERR_BAD_SIZE;
     if (epi == EPI_SILU_MUL && N % 128) return FG_ERR_BAD_SIZE;
@@ -1214,6 +1333,32 @@ extern "C" int fg_gemm_tc(const void *X, int ldx, const void *W, int ldw, void *
     // and share each weight tile through L2; beyond that the prefill kernel is faster (measured: 56.6 against 45.5 k tok/s
     // at 96 rows, 65.8 against 74.0 k at 200).
     if (norm_w && (epi != EPI_ADD_F32 || !xw_out || !ss_out)) return FG_ERR_BAD_DTYPE;
+    if (workspace && force_splits == 0 && ((uintptr_t)workspace & 15) == 0 && N % 4 == 0) {
+        int kbs = 0;
+        const int S = prefill_splits(M, N, K, epi, &kbs);
+        if (S && (long long)S * M * N * 4 <= workspace_bytes) {
+            CUtensorMap tmP, tmQ;
+            int e = make_map(&tmP, X, M, K, ldx, BM);
+            if (e) return e;
+            e = make_map(&tmQ, W, N, K, ldw, 128);
+            if (e) return e;
+            GemmArgs part{workspace, M, N, K, N, kbs, 1, nullptr, 0, 1, 0.f, nullptr, nullptr, nullptr, EPI_F32, 0, g_test_skip_copy, S};
+            e = launch_prefill<128, 6, EPI_F32>(tmP, tmQ, part, stream);
+            if (e) return e;
+            const int esz = (epi == EPI_F32 || epi == EPI_ADD_F32) ? 4 : 2;
+            const int vec = ((uintptr_t)out % 16 == 0) && ((size_t)ldc * esz % 16 == 0);
+            if (ss_tiles_out) *ss_tiles_out = (N + 127) / 128;
+            GemmArgs fin{out, M, N, K, ldc, kbs, vec, ss_in, ss_tiles, ss_size, ss_eps, norm_w, (bf16 *)xw_out, ss_out, epi, 0, 0, S};
+            dim3 grid((N + 127) / 128, (M + 7) / 8);
+            const float *ws = (const float *)workspace;
+            switch (epi) {
+            case EPI_BF16: return fg_launch(gemm_splitk_finish_kernel<EPI_BF16>, grid, dim3(256), 0, stream, fin, ws, S);
+            case EPI_F32: return fg_launch(gemm_splitk_finish_kernel<EPI_F32>, grid, dim3(256), 0, stream, fin, ws, S);
+            case EPI_ADD_F32: return fg_launch(gemm_splitk_finish_kernel<EPI_ADD_F32>, grid, dim3(256), 0, stream, fin, ws, S);
+            }
+            return FG_ERR_BAD_DTYPE;
+        }
+    }
     const bool swap = M <= 128;
     const int total_kb = (K + BK - 1) / BK;
     int bn, splits = 1;

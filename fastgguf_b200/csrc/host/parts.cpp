@@ -157,9 +157,12 @@ Tensor Linear::forward(Runtime &rt, const Tensor &a_in, const DeferredNorm *defe
         int tiles_out = 0;
         count_launch();
         ProfileScope scope("fg_gemm_tc", profile_on() ? format("%lld x %lld, %lld rows%s", (long long)N, (long long)K, (long long)M, accumulate ? ", residual add" : "").c_str() : nullptr);
-        int code = FG_KERNEL("tc", fg_gemm_tc)(a.data, (int)a.ld, W.data, (int)W.ld, out.data, (int)out.ld, epi, (int)M, (int)N,
-                                               (int)K, 0, ss_in, ss_tiles, ss_size, ss_eps, norm_w, xw_out.data, ss_out,
-                                               &tiles_out, rt.stream);
+        // scratch memory for a split along K (a prompt of a few hundred rows through a projection of few output tiles)
+        const long long ws_bytes = FG_KERNEL("tc", fg_gemm_tc_workspace_bytes)((int)M, (int)N, (int)K, epi);
+        void *ws = ws_bytes > 0 ? rt.arena->alloc((size_t)ws_bytes) : nullptr;
+        int code = FG_KERNEL("tc", fg_gemm_tc_ws)(a.data, (int)a.ld, W.data, (int)W.ld, out.data, (int)out.ld, epi, (int)M, (int)N,
+                                                  (int)K, 0, ss_in, ss_tiles, ss_size, ss_eps, norm_w, xw_out.data, ss_out,
+                                                  &tiles_out, ws, ws_bytes, rt.stream);
         if (code != KERNEL_BAD_SIZE) {
             check_kernel(code, "fg_gemm_tc");
             if (emit) {

@@ -11,7 +11,7 @@ needs no scratch memory.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_float, c_int, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_void_p
 from dataclasses import dataclass
 from typing import Optional
 
@@ -25,9 +25,19 @@ _BAD_SIZE = 10002
 register_signatures("tc", {
     "fg_gemm_tc": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "fg_gemm_tc_ws": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                      c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p],
+    "fg_gemm_tc_workspace_bytes": [c_int, c_int, c_int, c_int],
     "fg_gemm_tc_error": [],
     "fg_gemm_tc_max_ss_tiles": [c_int],
 })
+
+
+def workspace_bytes(M: int, N: int, K: int, epi: int) -> int:
+    """Bytes of scratch memory with which the contraction is split along K (0: it is not split)."""
+    fn = lib("tc").fg_gemm_tc_workspace_bytes
+    fn.restype = c_longlong
+    return int(fn(M, N, K, epi))
 
 
 @dataclass
@@ -59,7 +69,7 @@ def pipeline_error() -> int:
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
             out_dtype: Optional[torch.dtype] = None, accumulate: bool = False, silu: bool = False,
             force_splits: int = 0, deferred: Optional["DeferredNorm"] = None,
-            emit_norm_weight: Optional[torch.Tensor] = None, emit_eps: float = 0.0):
+            emit_norm_weight: Optional[torch.Tensor] = None, emit_eps: float = 0.0, split_k: bool = True):
     """out[m, n] (+)= sum_k a[m, k] w[n, k] on the tensor cores; None if the sizes are refused.
 
     ``silu=True``: ``w`` is [2F, K] with gate and up interleaved in blocks of 64 rows (see
@@ -67,6 +77,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = N
     ``deferred``: ``a`` is ``deferred.xw`` and the rows' 1/rms is applied in the epilogue.
     ``emit_norm_weight`` (with ``accumulate``): also start the next RMSNorm from the updated ``out``;
     the call then returns ``(out, DeferredNorm)``.
+    ``split_k=False``: no scratch memory is offered, so a contraction of few output tiles is not split along K.
     """
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_tc takes bfloat16 operands")
@@ -108,9 +119,12 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = N
             raise KernelError("gemm_tc: emitting a norm needs the residual-add epilogue and a float32 weight [N]")
         xw_out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
         ss_out = torch.empty((int(lib("tc").fg_gemm_tc_max_ss_tiles(N)), M), dtype=torch.float32, device=a.device)
-    code = lib("tc").fg_gemm_tc(ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out.stride(0), epi,
-                                M, rows, K, int(force_splits), ptr(ss_in), ss_tiles, ss_size, float(ss_eps),
-                                ptr(emit_norm_weight), ptr(xw_out), ptr(ss_out), ctypes.byref(tiles_out), stream())
+    need = workspace_bytes(M, rows, K, epi) if split_k and not force_splits else 0
+    scratch = torch.empty(need, dtype=torch.uint8, device=a.device) if need else None
+    code = lib("tc").fg_gemm_tc_ws(ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out.stride(0), epi,
+                                   M, rows, K, int(force_splits), ptr(ss_in), ss_tiles, ss_size, float(ss_eps),
+                                   ptr(emit_norm_weight), ptr(xw_out), ptr(ss_out), ctypes.byref(tiles_out),
+                                   ptr(scratch), need, stream())
     if code == _BAD_SIZE:
         return None
     check(code, "gemm_tc")

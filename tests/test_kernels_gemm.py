@@ -169,3 +169,47 @@ def test_gemm_tc_prefill_pair_of_ctas(M, N, K, width):
         bound = (a.double().abs() @ w.double().abs().T).max().item()
         assert (got.double() - ref).abs().max().item() <= ref.abs().max().item() * 2 ** -8 + 1e-5 * bound * bound
     assert fast_gemm.pipeline_error() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(200, 2048, 8192), (256, 512, 4096), (384, 1000, 2048), (130, 264, 4096)])
+def test_gemm_tc_prefill_split_along_k(M, N, K):
+    """A few hundred rows through a projection of few output tiles: partial products over slices of K on all SMs and a
+    second kernel that adds them in order and applies the epilogue - plain, bfloat16, residual add with the next norm
+    started, and with a norm on the input side whose 1/rms that kernel applies (its row sums in 5 and in 40 parts)."""
+    from fastgguf_b200.ops import fast_gemm
+    for epi in (fast_gemm.EPI_BF16, fast_gemm.EPI_F32, fast_gemm.EPI_ADD_F32):
+        assert fast_gemm.workspace_bytes(M, N, K, epi) > 0               # the shapes are ones that the split takes
+    assert fast_gemm.workspace_bytes(64, N, K, fast_gemm.EPI_F32) == 0   # the decode kernel's range
+    assert fast_gemm.workspace_bytes(4096, 4096, K, fast_gemm.EPI_F32) == 0      # enough tiles
+    a, w = _operands(M, N, K, torch.bfloat16, 9)
+    want = a.double() @ w.double().T
+    got = fast_gemm.gemm_tc(a, w, out_dtype=torch.float32)
+    _check(got, a, w, want, False)
+    whole = fast_gemm.gemm_tc(a, w, out_dtype=torch.float32, split_k=False)
+    assert (got - whole).abs().max().item() <= 2e-6 * (a.double().abs() @ w.double().abs().T).max().item()
+    _check(fast_gemm.gemm_tc(a, w), a, w, want, True)
+    res = torch.randn(M, N, device="cuda")
+    nw = (1 + 0.1 * torch.randn(N, device="cuda")).float()
+    acc = res.clone()
+    out, started = fast_gemm.gemm_tc(a, w, out=acc, accumulate=True, emit_norm_weight=nw, emit_eps=1e-5)
+    x = want + res.double()
+    _check(acc, a, w, x, False)
+    assert started.tiles == (N + 127) // 128
+    assert (started.xw.double() - x * nw.double()).abs().max().item() <= 2 ** -7 * (x * nw.double()).abs().max().item()
+    ss = started.ss[:started.tiles].double().sum(0)
+    assert ((ss - (x * x).sum(1)).abs() / (x * x).sum(1)).max().item() < 1e-4
+    # a norm on the input side: rows x (float32) arrive as bf16(x * weight) with the sums of squares of x in parts
+    g = torch.Generator(device="cpu").manual_seed(10)
+    xin = (torch.randn(M, K, generator=g) * torch.linspace(0.2, 3.0, M)[:, None]).cuda()
+    wn = (1 + 0.1 * torch.randn(K, generator=g)).cuda()
+    xw = (xin * wn).to(torch.bfloat16)
+    for parts in (5, 40):
+        edges = torch.linspace(0, K, parts + 1).long().tolist()
+        ss_in = torch.stack([(xin[:, lo:hi].double() ** 2).sum(1).float() for lo, hi in zip(edges[:-1], edges[1:])])
+        d = fast_gemm.DeferredNorm(xw, ss_in.contiguous(), parts, K, 1e-5, xin, wn)
+        inv = 1.0 / torch.sqrt((xin.double() ** 2).mean(1) + 1e-5)
+        want_n = (xw.double() * inv[:, None]) @ w.double().T
+        got_n = fast_gemm.gemm_tc(xw, w, out_dtype=torch.float32, deferred=d)
+        bound = ((xw.double().abs() * inv[:, None]) @ w.double().abs().T).max().item()
+        assert (got_n.double() - want_n).abs().max().item() <= 4e-6 * bound
+    assert fast_gemm.pipeline_error() == 0
