@@ -137,6 +137,18 @@ static inline int fg_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// Plain stream order: the kernel starts when everything before it on the stream has finished (its
+// griddepcontrol instructions are then no-ops; its successor may still be released early by it).
+template <typename... KArgs, typename... Args>
+static inline int fg_launch_in_order(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cfg.attrs = nullptr;
+    cfg.numAttrs = 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // the same, for a thread-block cluster of (1, 1, cluster_z) CTAs
 template <typename... KArgs, typename... Args>
 static inline int fg_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

@@ -1351,10 +1351,14 @@ extern "C" int fg_gemm_tc_ws(const void *X, int ldx, const void *W, int ldw, voi
             GemmArgs fin{out, M, N, K, ldc, kbs, vec, ss_in, ss_tiles, ss_size, ss_eps, norm_w, (bf16 *)xw_out, ss_out, epi, 0, 0, S};
             dim3 grid((N + 127) / 128, (M + 7) / 8);
             const float *ws = (const float *)workspace;
+            // The second kernel starts in plain stream order, when the partial products are complete.  Launched as a
+            // dependent it sat resident on every SM while they ran, its own successor (a contraction with tensor
+            // memory and nearly all of an SM's shared memory) started beside them too, and one prompt step in a few
+            // hundred then never finished; with the successor held back until this kernel runs, none did.
             switch (epi) {
-            case EPI_BF16: return fg_launch(gemm_splitk_finish_kernel<EPI_BF16>, grid, dim3(256), 0, stream, fin, ws, S);
-            case EPI_F32: return fg_launch(gemm_splitk_finish_kernel<EPI_F32>, grid, dim3(256), 0, stream, fin, ws, S);
-            case EPI_ADD_F32: return fg_launch(gemm_splitk_finish_kernel<EPI_ADD_F32>, grid, dim3(256), 0, stream, fin, ws, S);
+            case EPI_BF16: return fg_launch_in_order(gemm_splitk_finish_kernel<EPI_BF16>, grid, dim3(256), 0, stream, fin, ws, S);
+            case EPI_F32: return fg_launch_in_order(gemm_splitk_finish_kernel<EPI_F32>, grid, dim3(256), 0, stream, fin, ws, S);
+            case EPI_ADD_F32: return fg_launch_in_order(gemm_splitk_finish_kernel<EPI_ADD_F32>, grid, dim3(256), 0, stream, fin, ws, S);
             }
             return FG_ERR_BAD_DTYPE;
         }

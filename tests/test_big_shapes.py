@@ -39,3 +39,32 @@ def test_one_layer_of_a_large_configuration(tmp_path, which):
         assert rel_err(np.stack(g), w) < 3e-2
     from fastgguf_b200.ops import fast_attention, fast_gemm
     assert fast_gemm.pipeline_error() == 0 and fast_attention.prefill_tc_error() == 0
+
+
+def test_many_prompt_steps_of_a_few_hundred_tokens_in_a_row(tmp_path):
+    """Prompts of 129 to 400 tokens through two layers of the 1B layer sizes, 240 steps back to back without anything
+    between them that waits for the device: the output and down projections run split along K here (partial products,
+    then a kernel that adds them), and every kernel may start while the ones before it still run.  The same prompt
+    gives the same bits at the start and at the end."""
+    from fastgguf_b200.engine.api import Engine
+    from fastgguf_b200.engine.batch import StepEntry
+    from fastgguf_b200.ops import fast_gemm
+    cfg_dict = dict(TINY_B, num_hidden_layers=2, vocab_size=515, max_position_embeddings=4096, hidden_size=2048,
+                    num_attention_heads=32, num_key_value_heads=8, head_dim=64, intermediate_size=8192)
+    cfg_dict["rope_scaling"] = dict(TINY_B["rope_scaling"], factor=8.0, original_max_position_embeddings=128)
+    assert fast_gemm.workspace_bytes(200, 2048, 8192, fast_gemm.EPI_ADD_F32) > 0        # the split is taken at these sizes
+    model_dir = make_model_dir(tmp_path, cfg_dict, 12, torch.bfloat16)
+    engine = Engine.from_dir(model_dir, dtype="bfloat16", max_tokens=1024, max_batch=2)
+    prompts = {n: random_tokens(n, cfg_dict["vocab_size"], 300 + n) for n in (129, 160, 192, 256, 300, 400)}
+    first = {}
+    for i in range(240):
+        n = list(prompts)[i % len(prompts)]
+        slot = engine.acquire()
+        out = engine.step([StepEntry(slot, prompts[n], [n - 1])])
+        engine.release(slot)
+        if n not in first:
+            first[n] = out.clone()
+        elif i >= 234:
+            assert torch.equal(out, first[n])
+    torch.cuda.synchronize()
+    assert fast_gemm.pipeline_error() == 0
