@@ -1284,7 +1284,9 @@ static int sm_count() {
 // How a prefill contraction with few output tiles is split along K: 128 x 128 tiles, as many splits as bring the CTAs
 // towards one an SM, each at least 8 K-blocks long.  0: no split (the decode kernel's range, enough tiles, short K).
 static int prefill_splits(int M, int N, int K, int epi, int *kb_per_split) {
-    if (M <= 128 || epi == EPI_SILU_MUL) return 0;
+    static int off = -1;                           // FASTGGUF_SPLITK=0: never (the prefill kernels as they were without it)
+    if (off < 0) { const char *e = getenv("FASTGGUF_SPLITK"); off = (e && e[0] == '0') ? 1 : 0; }
+    if (off || M <= 128 || epi == EPI_SILU_MUL) return 0;
     const int total_kb = (K + BK - 1) / BK, sms = sm_count();
     const long long tiles = (long long)((M + BM - 1) / BM) * ((N + 127) / 128);
     if (tiles * 2 > sms || total_kb < 16) return 0;
