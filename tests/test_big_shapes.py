@@ -68,3 +68,20 @@ def test_many_prompt_steps_of_a_few_hundred_tokens_in_a_row(tmp_path):
             assert torch.equal(out, first[n])
     torch.cuda.synchronize()
     assert fast_gemm.pipeline_error() == 0
+
+
+def test_recorded_decode_steps_of_more_than_128_sequences(tmp_path):
+    """136 sequences decode together: above 128 rows the projections of a step run on the prefill kernels, the output
+    and down projections split along K, all of it inside the recorded step.  Recorded and eager steps give the same
+    tokens."""
+    from fastgguf_b200.engine.api import Engine
+    cfg_dict = dict(TINY_B, num_hidden_layers=2, vocab_size=515, max_position_embeddings=4096, hidden_size=2048,
+                    num_attention_heads=32, num_key_value_heads=8, head_dim=64, intermediate_size=8192)
+    cfg_dict["rope_scaling"] = dict(TINY_B["rope_scaling"], factor=8.0, original_max_position_embeddings=128)
+    model_dir = make_model_dir(tmp_path, cfg_dict, 13, torch.bfloat16)
+    B = 136
+    engine = Engine.from_dir(model_dir, dtype="bfloat16", max_tokens=B * 128, max_batch=B, max_seq_len=256)
+    prompts = [random_tokens(3 + (7 * i) % 40, cfg_dict["vocab_size"], 500 + i) for i in range(B)]
+    runs = [engine.generate(prompts, temp=0.0, max_tokens=12, ignore_eos=True, batch_size=B, use_graphs=g) for g in (True, False)]
+    assert [c.tokens for c in runs[0]] == [c.tokens for c in runs[1]]
+    assert all(len(c.tokens) == 12 for c in runs[0])
