@@ -34,7 +34,7 @@
 #define FG_ERR_TENSORMAP 10004
 #define PAGE 64
 #define ROWS 128
-#define ATT_THREADS 192
+#define ATT_THREADS(PP) ((PP) ? 320 : 192)      // producer warp, issuer warp, four softmax warps (eight: PP)
 #define WAIT_LIMIT_CYCLES 2000000000ll
 #define WAIT_SHORT_CYCLES 1000000ll
 #define LOG2E 1.4426950408889634f
@@ -183,8 +183,13 @@ __device__ __forceinline__ void softmax_chunk(const float (&v)[32], int key, int
 // iteration j + 1 is computed while the softmax of iteration j runs and P V of iteration j while the softmax of j + 1
 // runs: the iterations of a CTA no longer add S + softmax + P V, and the heaviest tile of a long sequence (which bounds
 // the kernel) takes about the time of its softmaxes.
-template <int HD, bool PIPE>
-__global__ void __launch_bounds__(ATT_THREADS, 2)                  // two CTAs share an SM and overlap
+// PP (with PIPE, head size 64): two sets of four softmax warps take the iterations in turn - set 0 the even ones with
+// score tile, P tile and O accumulator 0, set 1 the odd ones with those of index 1 - each with a running maximum and sum
+// of its own, so that nothing orders the softmax of one iteration behind the one before it; the two partial results
+// of a row (O, maximum, sum) are combined at the end.  Four softmax streams an SM instead of two keep the exponential
+// unit busier.
+template <int HD, bool PIPE, bool PP>
+__global__ void __launch_bounds__(ATT_THREADS(PP), 2)              // two CTAs share an SM and overlap
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                        const bf16 *__restrict__ q, int ldq, bf16 *__restrict__ out, int ldo,
                        const int *__restrict__ cu_rows, const int *__restrict__ seq_start,
@@ -194,12 +199,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     constexpr int KEYS = PIPE ? 64 : (HD > 64 ? 64 : 128), NPG = KEYS / PAGE;      // keys and pages per iteration
     constexpr int NS = PIPE ? 2 : 1;                   // score tiles in tensor memory, P tiles in shared memory
     constexpr int Q_BYTES = ROWS * HD * 2, KV_TILE = KEYS * HD * 2, P_TILE = ROWS * KEYS * 2;
-    constexpr uint32_t TMEM_COLS = 256;                // S tiles: columns 0..NS*KEYS-1, O: the HD columns after them
+    constexpr uint32_t TMEM_COLS = 256;                // S tiles: columns 0..NS*KEYS-1, O: the HD columns after them (PP: twice)
     constexpr uint32_t O_COL = NS * KEYS;
+    static_assert(!PP || (PIPE && O_COL + 2 * HD <= TMEM_COLS), "two accumulators need two score tiles and head size 64");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) uint64_t bars[9];
+    __shared__ __align__(8) uint64_t bars[10];
+    __shared__ float x_ml[2][ROWS][2];                 // PP: a set's final maximum and sum of each row
     __shared__ uint32_t tmem_base_s;
 
     const int warp = warp_index(), lane = threadIdx.x & 31;
@@ -216,7 +223,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 
     if (threadIdx.x == 0) {
         mbar_init(k_full, 1); mbar_init(k_empty, 1); mbar_init(v_full, 1); mbar_init(v_empty, 1);
-        mbar_init(s_full, 1); mbar_init(s_full + 8, 1); mbar_init(p_full, ROWS); mbar_init(p_full + 8, ROWS); mbar_init(o_full, 1);
+        mbar_init(s_full, 1); mbar_init(s_full + 8, 1); mbar_init(p_full, ROWS); mbar_init(p_full + 8, ROWS); mbar_init(o_full, 1); mbar_init(o_full + 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -250,7 +257,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         lo = !valid ? INT_MIN : (window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0;
         const bf16 *src = q + (size_t)(row0 + q0 + t_row) * ldq + (size_t)(kvh * G + g_row) * HD;
 #pragma unroll
-        for (int c = 0; c < HD / 8; c++) {
+        for (int c = (warp < 6 ? 0 : HD / 8); c < HD / 8; c++) {       // (PP: the first set brings the tile)
             uint4 v = valid ? *(const uint4 *)(src + c * 8) : make_uint4(0, 0, 0, 0);
             uint32_t dst = qs + (c >> 3) * (ROWS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
@@ -336,9 +343,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                         // A = P: 64-key chunk ks / 4, 32 B inside its swizzle row; B = V: 16 keys = two 8-key groups
                         uint64_t adesc = desc_k_major(ps + tile_of(j) * P_TILE + (ks >> 2) * (ROWS * 128) + (ks & 3) * 32);
                         uint64_t bdesc = desc_mn_major(vt + ks * 2048, KEYS * 128);
-                        tc_mma_bf16(tmem_base + O_COL, adesc, bdesc, idesc_o, (j | ks) != 0);     // O accumulates over the iterations
+                        // O accumulates over the iterations (PP: over those of the iteration's set, in that set's columns)
+                        if (PP) tc_mma_bf16(tmem_base + O_COL + (j & 1) * HD, adesc, bdesc, idesc_o, ((j >> 1) | ks) != 0);
+                        else tc_mma_bf16(tmem_base + O_COL, adesc, bdesc, idesc_o, (j | ks) != 0);
                     }
-                    tc_commit(o_full);
+                    tc_commit(PP ? o_full + 8 * (j & 1) : o_full);
                     tc_commit(v_empty);
                 }
                 __syncwarp();
@@ -347,12 +356,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             }
         }
     } else {
-        // ------------------------------------------------------------ softmax, one thread per row
-        const int r = (warp & 3) * 32 + lane;
-        const uint32_t trow = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        // ------------------------------------------------------------ softmax, one thread per row (PP: and set)
+        const int lg = warp & 3, r = lg * 32 + lane, set = PP ? (warp - 2) >> 2 : 0;
+        const int step = PP ? 2 : 1;                    // this thread's iterations: set, set + step, ...
+        const uint32_t trow = tmem_base + ((uint32_t)(lg * 32) << 16);
+        const uint32_t ocol = O_COL + set * HD, my_o_full = o_full + 8 * set;
+        // the wait for the P V of this thread's previous iteration names a phase by its parity: PP counts the set's own
+        auto o_parity = [&](int j_prev) { return (uint32_t)((PP ? j_prev >> 1 : j_prev) & 1); };
         float m = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < n_iter; j++) {
+        int j_last = -1;
+        for (int j = set; j < n_iter; j += step) {
             const int key0 = (p_begin + NPG * j) * PAGE;
             const bool masked = key0 + KEYS - 1 > hi || key0 < lo;
             if (!mbar_wait(s_full + 8 * tile_of(j), use_parity(j))) { raise_error(4); ok = false; break; }
@@ -381,10 +395,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                                      ::"r"(dst), "r"(w[4 * k]), "r"(w[4 * k + 1]), "r"(w[4 * k + 2]), "r"(w[4 * k + 3]) : "memory");
                     }
                 };
-                if (PIPE) {
+                if (PIPE && !PP) {
                     // The scores of the second 32 keys are on their way from tensor memory while the first 32 are worked
                     // on: 4 to 6 % off prompts of 4,096 tokens and more at head size 64 (32,768 tokens: 6.53 -> 6.14 ms),
-                    // nothing at 128.  With one score tile (four chunks an iteration) it gains nothing.
+                    // nothing at 128.  With one score tile (four chunks an iteration) it gains nothing.  (PP: 320 threads
+                    // and two CTAs an SM leave no registers for it.)
                     uint32_t raw[2][32];
                     tc_ld32_issue(srow, raw[0]);
 #pragma unroll
@@ -436,36 +451,59 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             l = l * corr + sum;
             m = m_keep;
             // With two score tiles a row could run two P V ahead of what it has seen complete, and a wait names a phase
-            // by its parity only: every row watches every P V finish, in order (P V of iteration j - 1 is long done
-            // when the softmax of iteration j ends, so this costs nothing).
-            if (PIPE && j > 0 && !mbar_wait(o_full, (j - 1) & 1)) { raise_error(5); ok = false; break; }
-            if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+            // by its parity only: every row watches every P V (PP: of its set) finish, in order (the one before this
+            // iteration's is long done when the softmax of this iteration ends, so this costs nothing).
+            if (PIPE && j_last >= 0 && !mbar_wait(my_o_full, o_parity(j_last))) { raise_error(5); ok = false; break; }
+            if (j_last >= 0 && __any_sync(0xffffffffu, corr != 1.f)) {
                 // a base moved: the rows of O so far are rescaled in tensor memory, once the MMAs before this
                 // iteration have finished (the next P V is not issued before every row has arrived below)
-                if (!PIPE && !mbar_wait(o_full, (j - 1) & 1)) { raise_error(5); ok = false; break; }
+                if (!PIPE && !mbar_wait(my_o_full, o_parity(j_last))) { raise_error(5); ok = false; break; }
                 tc_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < HD / 32; c++) {
                     float v[32];
-                    tc_ld32(trow + O_COL + c * 32, v);
+                    tc_ld32(trow + ocol + c * 32, v);
 #pragma unroll
                     for (int i = 0; i < 32; i++) v[i] *= corr;
-                    tc_st32(trow + O_COL + c * 32, v);
+                    tc_st32(trow + ocol + c * 32, v);
                 }
             }
             tc_fence_before();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(p_full + 8 * tile_of(j));
+            j_last = j;
         }
-        if (ok && n_iter > 0 && !mbar_wait(o_full, (n_iter - 1) & 1)) { raise_error(5); ok = false; }
+        if (ok && j_last >= 0 && !mbar_wait(my_o_full, o_parity(j_last))) { raise_error(5); ok = false; }
+        float w_own = 1.f, w_other = 0.f;
+        const int n_other = PP ? (n_iter + set) / 2 : 0;               // iterations of the other set: (n + 1) / 2 even ones, n / 2 odd ones
+        if (PP) {
+            // The other set's last P V: complete or one behind when this set's is (the MMAs run in iteration order), so
+            // the parity names the right phase.  Then the two sets exchange each row's maximum and sum.
+            if (ok && n_other > 0 && !mbar_wait(o_full + 8 * (set ^ 1), (uint32_t)((n_other - 1) & 1))) { raise_error(5); ok = false; }
+            x_ml[set][r][0] = m; x_ml[set][r][1] = l;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + lg) : "memory");       // the two warps of these 32 rows
+            const float m2 = x_ml[set ^ 1][r][0], l2 = x_ml[set ^ 1][r][1], mm = fmaxf(m, m2);
+            w_own = m == -INFINITY ? 0.f : ex2(m - mm);
+            w_other = m2 == -INFINITY ? 0.f : ex2(m2 - mm);
+            l = l * w_own + l2 * w_other;
+        }
         tc_fence_after();
         if (n_iter > 0 && __all_sync(0xffffffffu, ok)) {           // the tensor-memory loads are warp-wide: every lane takes part
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             bf16 *dst = out + (size_t)(row0 + q0 + t_row) * ldo + (size_t)(kvh * G + g_row) * HD;
+            // (PP: each set stores half of the row's columns, from both accumulators)
 #pragma unroll 1
-            for (int c = 0; c < HD / 32; c++) {
+            for (int c = PP ? set * (HD / 64) : 0; c < (PP ? (set + 1) * (HD / 64) : HD / 32); c++) {
                 float v[32];
-                tc_ld32(trow + O_COL + c * 32, v);
+                if (!PP) tc_ld32(trow + O_COL + c * 32, v);
+                else {
+                    float a[32], b2[32];
+                    tc_ld32(trow + O_COL + set * HD + c * 32, a);              // this set's accumulator (set 0 always has one)
+                    const bool have_own = set == 0 || n_iter > 1, have_other = n_other > 0;
+                    if (have_other) tc_ld32(trow + O_COL + (set ^ 1) * HD + c * 32, b2);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) v[i] = (have_own ? a[i] * w_own : 0.f) + (have_other ? b2[i] * w_other : 0.f);
+                }
                 if (!valid) continue;
 #pragma unroll
                 for (int k8 = 0; k8 < 4; k8++) {
@@ -519,7 +557,7 @@ static int pool_map(CUtensorMap *map, const void *pool, long long rows, int hd) 
     return r == CUDA_SUCCESS ? 0 : FG_ERR_TENSORMAP;
 }
 
-template <int HD, bool PIPE>
+template <int HD, bool PIPE, bool PP>
 static int launch_tc(const CUtensorMap &tmK, const CUtensorMap &tmV, const void *q, int ldq, void *out, int ldo,
                      const int *cu_rows, const int *seq_start, const int *block_table, int table_width, int n_seq,
                      int max_new, int H, int KV, float scale, int window, cudaStream_t stream) {
@@ -530,14 +568,14 @@ static int launch_tc(const CUtensorMap &tmK, const CUtensorMap &tmV, const void 
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FG_ERR_BAD_SIZE;
     if (!configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, PIPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, PIPE, PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
-        cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, PIPE>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, PIPE, PP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         configured[dev] = true;
     }
     int G = H / KV, Gc = G < 16 ? G : 16, TQ = ROWS / Gc;
     dim3 grid(KV * ((G + Gc - 1) / Gc), (max_new + TQ - 1) / TQ, n_seq);
-    return fg_launch(attn_prefill_tc_kernel<HD, PIPE>, grid, dim3(ATT_THREADS), (size_t)smem, stream, tmK, tmV, (const bf16 *)q, ldq,
+    return fg_launch(attn_prefill_tc_kernel<HD, PIPE, PP>, grid, dim3(ATT_THREADS(PP)), (size_t)smem, stream, tmK, tmV, (const bf16 *)q, ldq,
                      (bf16 *)out, ldo, cu_rows, seq_start, block_table, table_width, KV, G, scale * LOG2E, window, g_test_skip_copy);
 }
 
@@ -557,19 +595,20 @@ extern "C" int fg_attention_prefill_tc(const void *q, int ldq, void *out, int ld
     if (e) return e;
     e = pool_map(&tmV, v_pool, rows, hd);
     if (e) return e;
-    // The variant with two score tiles: at head size 128 it takes a fifth off the kernel (3B shapes, 2,048 tokens: 81 ->
-    // 62 us a layer).  At head size 64, where the other variant already walks 128 keys an iteration, it is slower on one
-    // prompt of 2,048 tokens (55 against 45 us: the heaviest tile's chain of iterations bounds the kernel) and faster
-    // where many tiles share the GPU: 4,096 tokens 126 against 133 us, 32,768 tokens 6.54 against 6.77 ms, eight prompts
-    // of 2,048 tokens 270 against 315 us - so it runs from 4,096 rows of new tokens on.  FASTGGUF_ATTN_PIPE or
-    // fg_attention_prefill_tc_variant override (bit 0: head size 64, bit 1: head size 128; negative: this rule).
+    // Which form runs.  Two score tiles (S of iteration j + 1 under the softmax of iteration j, P V of iteration j under
+    // the softmax of j + 1): always - at head size 128 it took a fifth off the kernel (3B shapes, 2,048 tokens: 81 -> 62
+    // us a layer); at head size 64, 64 keys an iteration instead of 128, 38 against 43 us on one prompt of 2,048 tokens,
+    // 6.16 against 6.68 ms at 32,768, 283 against 312 us on eight prompts of 2,048.  Two sets of softmax warps at head
+    // size 64: from 3,072 rows of new tokens on (3,000 tokens: 70 against 73 us; 32,768: 5.78 against 6.16 ms; one
+    // prompt of 2,048: 39.5 against 38.2).  FASTGGUF_ATTN_PIPE or fg_attention_prefill_tc_variant override (bit 0 / 1:
+    // two score tiles at head size 64 / 128; bit 2: two softmax sets; negative: this rule); the tests run every form.
     if (g_variant == -2) { const char *e = getenv("FASTGGUF_ATTN_PIPE"); g_variant = e ? atoi(e) : -1; }
-    const bool pipe = g_variant >= 0 ? ((g_variant >> (hd == 64 ? 0 : 1)) & 1) != 0
-                                     : hd == 128 || (long long)n_seq * max_new >= 4096;
-#define TC_RUN(HD, PIPE) launch_tc<HD, PIPE>(tmK, tmV, q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, n_seq, \
-                                             max_new, H, KV, scale, window, stream)
-    if (hd == 64) return pipe ? TC_RUN(64, true) : TC_RUN(64, false);
-    return pipe ? TC_RUN(128, true) : TC_RUN(128, false);
+    const bool pipe = g_variant >= 0 ? ((g_variant >> (hd == 64 ? 0 : 1)) & 1) != 0 : true;
+    const bool pp = hd == 64 && pipe && (g_variant >= 0 ? (g_variant & 4) != 0 : (long long)n_seq * max_new >= 3072);
+#define TC_RUN(HD, PIPE, PP) launch_tc<HD, PIPE, PP>(tmK, tmV, q, ldq, out, ldo, cu_rows, seq_start, block_table, table_width, \
+                                                     n_seq, max_new, H, KV, scale, window, stream)
+    if (hd == 64) return pipe ? (pp ? TC_RUN(64, true, true) : TC_RUN(64, true, false)) : TC_RUN(64, false, false);
+    return pipe ? TC_RUN(128, true, false) : TC_RUN(128, false, false);
 #undef TC_RUN
 }
 
@@ -585,7 +624,7 @@ extern "C" int fg_attention_prefill_tc_test_hook(long long wait_limit_cycles, in
 
 // Which variant runs: see fg_attention_prefill_tc.  Negative: chosen by head size and step shape (the default).
 extern "C" int fg_attention_prefill_tc_variant(int bits) {
-    g_variant = bits < 0 ? -1 : (bits & 3);
+    g_variant = bits < 0 ? -1 : (bits & 7);
     return 0;
 }
 

@@ -110,7 +110,8 @@ def attention_prefill_tc(q, cu_rows, seq_start, block_table, k_pool, v_pool, n_s
 
 def prefill_tc_variant(bits: int) -> None:
     """Which form of the tcgen05 prefill attention runs: bit 0 / bit 1 = two score tiles in tensor memory at head
-    size 64 / 128; negative = chosen by head size and step shape (the default)."""
+    size 64 / 128, bit 2 = with them at head size 64 two sets of softmax warps that take the iterations in turn;
+    negative = chosen by head size and step shape (the default)."""
     check(lib("attn").fg_attention_prefill_tc_variant(int(bits)), "attention_prefill_tc_variant")
 
 

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 PAGE = 64
 
 
-@pytest.fixture(params=[0, 3], ids=["one-score-tile", "two-score-tiles"])
+@pytest.fixture(params=[0, 3, 7], ids=["one-score-tile", "two-score-tiles", "two-score-tiles-two-softmax-sets"])
 def tc_variant(request):
     """Both forms of the tcgen05 prefill kernel at both head sizes, whatever the step's shape would choose."""
     from fastgguf_b200.ops import fast_attention
