@@ -3,12 +3,16 @@
     python -m fastgguf_b200.kernel_bench attention_prefill [--head-dim 64] [--heads 32] [--kv-heads 8]
     python -m fastgguf_b200.kernel_bench attention_decode  [--head-dim 64] [--heads 32] [--kv-heads 8]
     python -m fastgguf_b200.kernel_bench gemm [--hidden 2048] [--qkv 3072] [--ffn 8192]
+    python -m fastgguf_b200.kernel_bench prompt_steps [--hidden 2048 --layers 16 --heads 32 --kv-heads 8 --head-dim 64
+                                                       --ffn 8192 --vocab 128256]
 
 Each line is one shape: the median of CUDA-event timings after warm-up launches, the work it stands for and the
 fraction of the measured peak (``MEASURED_PEAKS.json`` beside the package's parent folder if present, else 6,650 GB/s
 and 1,590 TFLOP/s).  The decode-attention and contraction timings write a buffer larger than L2 between launches; the
 prefill attention is timed back to back (its K and V exceed L2 only at the longest prompts, as in a real prompt step).
 A timing of one launch carries the launch itself (a few microseconds), which a graph-replayed step hides.
+``prompt_steps`` is the whole engine instead: one prompt of 1 to 4,096 tokens through a model of random weights with
+the given layer sizes (defaults: Llama 3.2 1B), host tokens in, the last position's logits out.
 """
 import argparse
 import json
@@ -131,6 +135,36 @@ def gemm(args):
         raise RuntimeError("a bounded wait of a contraction ran out")
 
 
+def prompt_steps(args):
+    """Time to the first token's logits over prompt lengths: one sequence, one step, its slot given back after it."""
+    import numpy as np
+    from .engine.api import Engine
+    from .engine.batch import StepEntry
+    from .registry import config_from_dict
+    cfg = {"architectures": ["LlamaForCausalLM"], "hidden_size": args.hidden, "num_hidden_layers": args.layers,
+           "num_attention_heads": args.heads, "num_key_value_heads": args.kv_heads, "head_dim": args.head_dim,
+           "intermediate_size": args.ffn, "vocab_size": args.vocab, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+           "max_position_embeddings": 8192, "tie_word_embeddings": True}
+    engine = Engine.from_random(config_from_dict(cfg), 0, dtype="bfloat16", max_tokens=4096 + 64, max_batch=1, max_seq_len=4096)
+    rng = np.random.default_rng(0)
+    for T in (1, 16, 64, 65, 128, 129, 192, 256, 384, 512, 768, 1024, 1536, 2048, 4096):
+        tokens = rng.integers(0, args.vocab, size=T).tolist()
+        times = []
+        for i in range(6):
+            slot = engine.acquire()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            engine.step_host([StepEntry(slot, tokens, [T - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            engine.release(slot)
+            if i >= 2:
+                times.append(a.elapsed_time(b))
+        ms = sorted(times)[len(times) // 2]
+        print(f"prompt_steps tokens {T:5d}: {ms:8.3f} ms  {T / ms:9.1f} tokens/ms", flush=True)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="python -m fastgguf_b200.kernel_bench", description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="what", required=True)
@@ -143,10 +177,15 @@ def main(argv=None):
     p.add_argument("--hidden", type=int, default=2048)
     p.add_argument("--qkv", type=int, default=3072)
     p.add_argument("--ffn", type=int, default=8192)
+    p = sub.add_parser("prompt_steps")
+    for name, default in (("hidden", 2048), ("layers", 16), ("heads", 32), ("kv-heads", 8), ("head-dim", 64), ("ffn", 8192),
+                          ("vocab", 128256)):
+        p.add_argument("--" + name, type=int, default=default)
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("kernel_bench needs a GPU")
-    {"attention_prefill": attention_prefill, "attention_decode": attention_decode, "gemm": gemm}[args.what](args)
+    {"attention_prefill": attention_prefill, "attention_decode": attention_decode, "gemm": gemm,
+     "prompt_steps": prompt_steps}[args.what](args)
 
 
 if __name__ == "__main__":
