@@ -47,10 +47,21 @@ def test_decode_contraction_gives_up_and_the_next_launch_is_correct():
     assert fast_gemm.pipeline_error() == 0 and torch.equal(again, want)
 
 
-def test_prefill_attention_gives_up_and_the_next_launch_is_correct():
+@pytest.mark.parametrize("variant", [1, 5], ids=["two-score-tiles", "two-score-tiles-two-softmax-sets"])
+def test_prefill_attention_gives_up_and_the_next_launch_is_correct(variant):
+    """(In the form with two sets of softmax warps each row's two threads meet at a barrier after their loops: every
+    thread gets there, whichever of its waits ran out.)"""
     from fastgguf_b200 import ops
     from fastgguf_b200.ops import fast_attention
     from test_kernels_attention import _err, make_case, plain
+    fast_attention.prefill_tc_variant(variant)
+    try:
+        _attention_gives_up(ops, fast_attention, _err, make_case, plain)
+    finally:
+        fast_attention.prefill_tc_variant(-1)
+
+
+def _attention_gives_up(ops, fast_attention, _err, make_case, plain):
     H, KV, hd = 4, 2, 64
     new = [130]
     case = make_case([70], new, H, KV, hd, torch.bfloat16, 31)
