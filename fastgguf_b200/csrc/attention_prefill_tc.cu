@@ -7,10 +7,16 @@
 // Grid (kv head x head chunk, query tile, sequence): CTAs are dispatched x first, so the tiles that see the most
 // keys (the late ones, y = 0) all start before any light one and the tail of the kernel is short.  A CTA owns 128 rows = TQ consecutive new
 // tokens x Gc query heads of one KV head (Gc = min(G, 16), row r = token r / Gc, head r % Gc) and
-// walks the sequence's pages, two at a time (128 keys) at head size 64 and one at a time at head size 128, so
-// that two CTAs fit on an SM at either size and the softmax of one runs under the MMAs of the other.  At head size 128
-// the kernel keeps TWO score tiles in tensor memory and two P tiles in shared memory (template parameter PIPE): S of
-// iteration j + 1 is computed during the softmax of iteration j, P V of iteration j during the softmax of j + 1.
+// walks the sequence's pages so that two CTAs fit on an SM and the softmax of one runs under the MMAs of the other.
+// Three forms (template parameters; fg_attention_prefill_tc says which runs when):
+//   one score tile     two pages (128 keys) an iteration at head size 64, one (64 keys) at 128; S, softmax and P V of an
+//                      iteration follow one another
+//   PIPE               one page an iteration, TWO score tiles in tensor memory and two P tiles in shared memory: S of
+//                      iteration j + 1 is computed during the softmax of iteration j, P V of iteration j during the
+//                      softmax of j + 1 (the form that runs by default)
+//   PIPE + PP          head size 64: two sets of softmax warps (2-5 and 6-9) take the iterations in turn, each with its
+//                      own score tile, P tile, O accumulator, running maximum and sum; the two partial results of a row
+//                      are combined at the end (long prompts)
 //
 //   warp 0             TMA (one elected lane issues): the K tile and the V tile of an iteration (128B
 //                      swizzle); the next K tile is fetched as soon as S has consumed the current one,
